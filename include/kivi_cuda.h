@@ -1,0 +1,205 @@
+/*
+ * kivi_cuda.h — C ABI of libkivi_cuda.so, the B200 (sm_100a) implementation of
+ * the KIVI 2-bit KV-cache hot path.
+ *
+ * Plain pointers and sizes only; every pointer marked "device" must be CUDA
+ * device memory on the current device; `stream` is a cudaStream_t passed as
+ * void* (NULL = the legacy default stream).  Every entry point validates its
+ * arguments on the host, enqueues its kernels on `stream` and returns without
+ * synchronising.  Return value: KIVI_OK or a KIVI_ERR_* code;
+ * kivi_last_error() gives the message of the calling thread's last failure.
+ * There is no CPU fallback anywhere in this library.
+ *
+ * "reference" below = the kivi_sycl project this library is a drop-in for;
+ * citations are path:line inside that project.
+ */
+#ifndef KIVI_CUDA_H_
+#define KIVI_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KIVI_OK 0
+#define KIVI_ERR_INVALID_ARGUMENT 1 /* host-side validation failed, nothing launched */
+#define KIVI_ERR_CUDA 2             /* a CUDA runtime call failed */
+#define KIVI_ERR_UNSUPPORTED 3      /* valid arguments this build has no kernel for */
+
+/* element types of activations (inputs, queries, residual window, outputs) */
+#define KIVI_F32 0
+#define KIVI_BF16 1
+
+/* how (x-min)/scale exactly halfway between two codes is rounded.
+ * HALF_AWAY is what the reference's device kernel does (sycl::round,
+ * src/csrc/kernels/internal/quant_tile.hpp:64,85); HALF_EVEN is what the
+ * reference's torch mirror does (torch.round, examples/cpu_sim.py:42). */
+#define KIVI_ROUND_HALF_AWAY 0
+#define KIVI_ROUND_HALF_EVEN 1
+
+const char* kivi_last_error(void);
+int kivi_version(void); /* major*10000 + minor*100 + patch */
+
+/* ------------------------------------------------------------------------
+ * Operators on the flat packed layout of the reference.
+ *
+ * Every operator works on consecutive runs of `group_size` elements of the
+ * flat input: run g gives scales[g] = (max-min)/3.0f + 1e-10f, zeros[g] = min,
+ * and group_size/4 bytes q0|q1<<2|q2<<4|q3<<6 with
+ * q = clamp(round((x-min)/scale), 0, 3).  Dequantize is float(q)*scale+zero
+ * with a separate multiply and add.  in_dtype KIVI_BF16 upcasts each element
+ * to fp32 first (the reference upcasts with .float(), cache/manager.py:210-214).
+ * group_size must be a positive multiple of 4.
+ * ---------------------------------------------------------------------- */
+
+/* replaces quantize_keys_per_channel_submit, src/csrc/kernels/quantize_kernels.cpp:24-54
+ * input  device [num_channels*group_size] (keys transposed to [B,H,D,S], groups along S)
+ * output device [num_channels*group_size/4] u8; scales, zeros device [num_channels] f32 */
+int kivi_quantize_keys_per_channel(const void* input, int in_dtype, uint8_t* output,
+                                   float* scales, float* zeros, int64_t num_channels,
+                                   int group_size, int rounding, void* stream);
+
+/* replaces quantize_values_per_token_submit, src/csrc/kernels/quantize_kernels.cpp:69-106
+ * input device [num_tokens*head_dim]; output [num_tokens*head_dim/4];
+ * scales, zeros [num_tokens*head_dim/group_size]; head_dim % group_size == 0 */
+int kivi_quantize_values_per_token(const void* input, int in_dtype, uint8_t* output,
+                                   float* scales, float* zeros, int64_t num_tokens,
+                                   int head_dim, int group_size, int rounding, void* stream);
+
+/* replaces dequantize_keys_per_channel_submit, src/csrc/kernels/dequantize_kernels.cpp:32-64 */
+int kivi_dequantize_keys_per_channel(const uint8_t* input, const float* scales,
+                                     const float* zeros, float* output,
+                                     int64_t num_channels, int group_size, void* stream);
+
+/* replaces dequantize_values_per_token_submit, src/csrc/kernels/dequantize_kernels.cpp:79-111 */
+int kivi_dequantize_values_per_token(const uint8_t* input, const float* scales,
+                                     const float* zeros, float* output,
+                                     int64_t num_groups, int group_size, void* stream);
+
+/* replaces quant_dequant_roundtrip_keys_submit, src/csrc/kernels/roundtrip_kernels.cpp:14-38 */
+int kivi_quant_dequant_roundtrip_keys(const void* input, int in_dtype, float* output,
+                                      int64_t num_channels, int group_size, int rounding,
+                                      void* stream);
+
+/* replaces quant_dequant_roundtrip_values_submit, src/csrc/kernels/roundtrip_kernels.cpp:50-80 */
+int kivi_quant_dequant_roundtrip_values(const void* input, int in_dtype, float* output,
+                                        int64_t num_tokens, int head_dim, int group_size,
+                                        int rounding, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Device-resident cache of one layer on one GPU.
+ *
+ * Replaces the storage side of KiviCache (src/kivi_sycl/cache/manager.py:100-117):
+ * the reference keeps an fp32 residual on the CPU and a dequantized fp32
+ * history; here the residual is a ring in device memory and the history is
+ * kept packed.  A "unit" is one (batch, kv_head) pair; units are independent.
+ *
+ * Quantized store of one unit, token group g (tokens g*G .. g*G+G-1):
+ *   k_codes  + (u*max_groups + g) * (D*G/4): one key block.  With Q = G/4 and
+ *            W = min(D,64), the byte at  (d/W)*Q*W + j*W + d%W  (0<=j<Q) holds
+ *            the codes of channel d for tokens j, j+Q, j+2Q, j+3Q of the group
+ *            in bits 0-1, 2-3, 4-5, 6-7.
+ *   k_scales, k_zeros + (u*max_groups + g) * D : fp32 per channel of the group
+ *            (one per-channel group of the reference, quantize_kernels.hpp:36-42).
+ *   v_codes  + (u*max_tokens + t) * (D/4): the reference's value layout, byte b
+ *            = channels 4b..4b+3 of token t (quantize_kernels.hpp:55-60).
+ *   v_scales, v_zeros + (u*max_tokens + t) * (D/G): fp32 per channel group.
+ * Residual ring of one unit: k_res, v_res + u*R*D elements of res_dtype; the
+ * live window is slots (res_start + i) % R for 0 <= i < res_len, oldest first.
+ * The three counters (quant_len, res_start, res_len) are kept by the caller;
+ * kivi_cache_update returns their new values and never reads device memory
+ * back.
+ * ---------------------------------------------------------------------- */
+typedef struct kivi_layer {
+    int32_t num_units;    /* B * Hkv held by this GPU */
+    int32_t head_dim;     /* D; multiple of group_size; D <= 64 or D % 64 == 0 */
+    int32_t group_size;   /* G; >= 4, multiple of 4 */
+    int32_t residual_cap; /* R; >= G */
+    int64_t max_tokens;   /* capacity of the quantized store, multiple of G */
+    int32_t res_dtype;    /* KIVI_F32 or KIVI_BF16 */
+    int32_t reserved;
+    uint8_t* k_codes;
+    float* k_scales;
+    float* k_zeros;
+    uint8_t* v_codes;
+    float* v_scales;
+    float* v_zeros;
+    void* k_res;
+    void* v_res;
+} kivi_layer;
+
+/* Flush policy of the reference (append everything, then move the oldest G
+ * tokens to the quantized store while the window holds >= R tokens,
+ * cache/manager.py:226-243).  Pure host arithmetic. */
+int kivi_cache_plan(int64_t quant_len, int res_len, int n_new, int group_size,
+                    int residual_cap, int* n_flush_groups, int64_t* quant_len_out,
+                    int* res_len_out);
+
+/* replaces KiviCache.add_tokens + _flush_group, cache/manager.py:162-249, 309-374.
+ * new_k/new_v: device, n_new tokens per unit of new_dtype; token t of unit u at
+ * element offset u*unit_stride + t*tok_stride, head_dim contiguous elements.
+ * Groups are cut from the sequence [live ring tokens, then the new tokens],
+ * keys quantized per channel over the G tokens of a group, values per token
+ * over runs of G channels, written at group index quant_len/G onwards; what is
+ * left goes to the ring.  Fails if the store would overflow. */
+int kivi_cache_update(const kivi_layer* layer, int64_t quant_len, int res_start, int res_len,
+                      const void* new_k, const void* new_v, int new_dtype,
+                      int64_t unit_stride_k, int64_t tok_stride_k,
+                      int64_t unit_stride_v, int64_t tok_stride_v, int n_new,
+                      int rounding, int64_t* quant_len_out, int* res_start_out,
+                      int* res_len_out, void* stream);
+
+/* replaces the serving half of KiviCache.get_full_cache, cache/manager.py:251-290
+ * (compatibility path; the attention below never needs it).  Writes fp32
+ * [num_units][quant_len + res_len][D] keys and values: dequantized history
+ * followed by the residual window in age order. */
+int kivi_cache_materialize(const kivi_layer* layer, int64_t quant_len, int res_start,
+                           int res_len, float* k_out, float* v_out, void* stream);
+
+/* Re-lays keys quantized by kivi_quantize_keys_per_channel (channel-major
+ * [num_units][D][S/4] codes, [num_units][D][S/G] scales and zeros, the layout of
+ * README.md:122-128 with S/G groups per channel) into the key blocks of
+ * `layer` at groups 0 .. S/G-1.  No reference counterpart: the reference never
+ * keeps packed keys (cache/manager.py:100-109). */
+int kivi_cache_import_keys(const kivi_layer* layer, const uint8_t* packed,
+                           const float* scales, const float* zeros, int64_t seq_len,
+                           void* stream);
+
+/* ------------------------------------------------------------------------
+ * Fused decode attention over the packed cache.
+ *
+ * No counterpart kernel in the reference: it serves a dequantized fp32 cache to
+ * a third-party model (cache/manager.py:251-290, generation/generate.py:75-77)
+ * and states the math once, tests/integration/test_attention_fix.py:40-43:
+ *   out = softmax(q K^T * head_dim^-0.5) V  over  [history || residual].
+ * q, out: device [num_units][n_rep][D] (n_rep = query heads per KV head; with
+ * units ordered (b, kv_head) this is the contiguous [B, Hq, D] tensor).
+ * sm_scale <= 0 means head_dim^-0.5.
+ * workspace: device scratch of at least kivi_decode_attention_workspace()
+ * bytes, holding split partials (running max, sum and unnormalised output per
+ * split); contents need not be preserved between calls.
+ * num_splits: how many pieces the quantized history of a unit is cut into;
+ * 0 = choose from the SM count.  path: KIVI_ATTN_AUTO picks the tensor-core
+ * kernel when the shape allows it and the CUDA-core fp32 kernel otherwise.
+ * ---------------------------------------------------------------------- */
+#define KIVI_ATTN_AUTO 0
+#define KIVI_ATTN_FP32 1 /* CUDA-core fp32 kernel, any supported shape */
+#define KIVI_ATTN_MMA 2  /* tensor-core kernel: D=128, G=32, n_rep<=4, bf16 or f32 q */
+
+size_t kivi_decode_attention_workspace(int num_units, int n_rep, int head_dim, int num_splits);
+int kivi_decode_attention_max_splits(void);
+
+int kivi_decode_attention(const kivi_layer* layer, int64_t quant_len, int res_start,
+                          int res_len, const void* q, int q_dtype, void* out, int out_dtype,
+                          int n_rep, float sm_scale, void* workspace, size_t workspace_bytes,
+                          int num_splits, int path, void* stream);
+
+/* number of kernels the last successful call on this thread launched */
+int kivi_last_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KIVI_CUDA_H_ */

@@ -1,0 +1,242 @@
+"""ctypes binding of libkivi_cuda.so (include/kivi_cuda.h) for torch tensors.
+
+This is the raw C ABI: device pointers, sizes and a stream handle.  Tensors are
+only used to obtain ``data_ptr()`` and the current CUDA stream.  Any non-zero
+return code raises RuntimeError carrying ``kivi_last_error()``.  Importing this
+module fails loudly when the library is missing and cannot be built: there is
+no CPU fallback.
+"""
+import ctypes
+import os
+
+import torch
+
+from . import _build
+
+F32, BF16 = 0, 1
+ROUND_HALF_AWAY, ROUND_HALF_EVEN = 0, 1
+ATTN_AUTO, ATTN_FP32, ATTN_MMA = 0, 1, 2
+
+_c = ctypes
+_i64, _int, _vp, _f = _c.c_int64, _c.c_int, _c.c_void_p, _c.c_float
+
+
+class Layer(_c.Structure):
+    """struct kivi_layer of include/kivi_cuda.h."""
+    _fields_ = [("num_units", _c.c_int32), ("head_dim", _c.c_int32), ("group_size", _c.c_int32),
+                ("residual_cap", _c.c_int32), ("max_tokens", _c.c_int64), ("res_dtype", _c.c_int32),
+                ("reserved", _c.c_int32), ("k_codes", _vp), ("k_scales", _vp), ("k_zeros", _vp),
+                ("v_codes", _vp), ("v_scales", _vp), ("v_zeros", _vp), ("k_res", _vp), ("v_res", _vp)]
+
+
+SIGNATURES = {
+    "kivi_last_error": (_c.c_char_p, []),
+    "kivi_version": (_int, []),
+    "kivi_last_launch_count": (_int, []),
+    "kivi_quantize_keys_per_channel": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _int, _int, _vp]),
+    "kivi_quantize_values_per_token": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _int, _int, _int, _vp]),
+    "kivi_dequantize_keys_per_channel": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _vp]),
+    "kivi_dequantize_values_per_token": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _vp]),
+    "kivi_quant_dequant_roundtrip_keys": (_int, [_vp, _int, _vp, _i64, _int, _int, _vp]),
+    "kivi_quant_dequant_roundtrip_values": (_int, [_vp, _int, _vp, _i64, _int, _int, _int, _vp]),
+    "kivi_cache_plan": (_int, [_i64, _int, _int, _int, _int, _c.POINTER(_int), _c.POINTER(_i64), _c.POINTER(_int)]),
+    "kivi_cache_update": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _vp, _int, _i64, _i64, _i64, _i64,
+                                 _int, _int, _c.POINTER(_i64), _c.POINTER(_int), _c.POINTER(_int), _vp]),
+    "kivi_cache_materialize": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _vp, _vp]),
+    "kivi_cache_import_keys": (_int, [_c.POINTER(Layer), _vp, _vp, _vp, _i64, _vp]),
+    "kivi_decode_attention_workspace": (_c.c_size_t, [_int, _int, _int, _int]),
+    "kivi_decode_attention_max_splits": (_int, []),
+    "kivi_decode_attention": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _int, _vp, _int, _int, _f,
+                                     _vp, _c.c_size_t, _int, _int, _vp]),
+}
+
+
+def _load():
+    path = _build.LIB
+    if not os.path.exists(path):
+        try:
+            _build.build_cuda_lib()
+        except Exception as exc:  # pragma: no cover - build box only
+            raise ImportError(
+                f"{path} is missing and could not be built with nvcc ({exc}). "
+                "Run `python -m intel_kivi_hybrid_b200._build`; there is no CPU fallback.") from exc
+    lib = ctypes.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)   # AttributeError = header and library out of sync
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
+lib = _load()
+
+
+def _check(rc):
+    if rc != 0:
+        raise RuntimeError(f"kivi_cuda error {rc}: {lib.kivi_last_error().decode()}")
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise RuntimeError(f"unsupported dtype {t.dtype}: expected float32 or bfloat16")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev(*ts):
+    for t in ts:
+        if not t.is_cuda:
+            raise RuntimeError("tensor must be on a CUDA device")
+        if not t.is_contiguous():
+            raise RuntimeError("tensor must be contiguous")
+
+
+def quantize_keys(x, packed, scales, zeros, group_size, rounding=ROUND_HALF_AWAY):
+    _dev(x, packed, scales, zeros)
+    _check(lib.kivi_quantize_keys_per_channel(x.data_ptr(), _dt(x), packed.data_ptr(), scales.data_ptr(),
+                                              zeros.data_ptr(), scales.numel(), group_size, rounding, _stream()))
+
+
+def quantize_values(x, packed, scales, zeros, head_dim, group_size, rounding=ROUND_HALF_AWAY):
+    _dev(x, packed, scales, zeros)
+    _check(lib.kivi_quantize_values_per_token(x.data_ptr(), _dt(x), packed.data_ptr(), scales.data_ptr(),
+                                              zeros.data_ptr(), x.numel() // head_dim, head_dim, group_size,
+                                              rounding, _stream()))
+
+
+def dequantize_keys(packed, scales, zeros, out, group_size):
+    _dev(packed, scales, zeros, out)
+    _check(lib.kivi_dequantize_keys_per_channel(packed.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                                out.data_ptr(), scales.numel(), group_size, _stream()))
+
+
+def dequantize_values(packed, scales, zeros, out, group_size):
+    _dev(packed, scales, zeros, out)
+    _check(lib.kivi_dequantize_values_per_token(packed.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                                out.data_ptr(), scales.numel(), group_size, _stream()))
+
+
+def roundtrip_keys(x, out, group_size, rounding=ROUND_HALF_AWAY):
+    _dev(x, out)
+    _check(lib.kivi_quant_dequant_roundtrip_keys(x.data_ptr(), _dt(x), out.data_ptr(), x.numel() // group_size,
+                                                 group_size, rounding, _stream()))
+
+
+def roundtrip_values(x, out, head_dim, group_size, rounding=ROUND_HALF_AWAY):
+    _dev(x, out)
+    _check(lib.kivi_quant_dequant_roundtrip_values(x.data_ptr(), _dt(x), out.data_ptr(), x.numel() // head_dim,
+                                                   head_dim, group_size, rounding, _stream()))
+
+
+def cache_plan(quant_len, res_len, n_new, G, R):
+    f, ql, rl = _int(), _i64(), _int()
+    _check(lib.kivi_cache_plan(quant_len, res_len, n_new, G, R, _c.byref(f), _c.byref(ql), _c.byref(rl)))
+    return f.value, ql.value, rl.value
+
+
+class LayerStore:
+    """Device buffers of one layer + the three host counters.  Thin owner of a
+    ``struct kivi_layer``; all arithmetic happens in the library."""
+
+    def __init__(self, num_units, head_dim, group_size, residual_cap, max_tokens, dtype, device):
+        G, D = group_size, head_dim
+        max_tokens = -(-max_tokens // G) * G
+        self.num_units, self.D, self.G, self.R, self.max_tokens = num_units, D, G, residual_cap, max_tokens
+        self.dtype, self.device = dtype, torch.device(device)
+        mg = max_tokens // G
+        kw = dict(device=self.device)
+        self.k_codes = torch.zeros(num_units, mg, D * G // 4, dtype=torch.uint8, **kw)
+        self.k_scales = torch.zeros(num_units, mg, D, dtype=torch.float32, **kw)
+        self.k_zeros = torch.zeros(num_units, mg, D, dtype=torch.float32, **kw)
+        self.v_codes = torch.zeros(num_units, max_tokens, D // 4, dtype=torch.uint8, **kw)
+        self.v_scales = torch.zeros(num_units, max_tokens, D // G, dtype=torch.float32, **kw)
+        self.v_zeros = torch.zeros(num_units, max_tokens, D // G, dtype=torch.float32, **kw)
+        self.k_res = torch.zeros(num_units, residual_cap, D, dtype=dtype, **kw)
+        self.v_res = torch.zeros(num_units, residual_cap, D, dtype=dtype, **kw)
+        self.quant_len, self.res_start, self.res_len = 0, 0, 0
+        self.c = Layer(num_units, D, G, residual_cap, max_tokens, F32 if dtype == torch.float32 else BF16, 0,
+                       self.k_codes.data_ptr(), self.k_scales.data_ptr(), self.k_zeros.data_ptr(),
+                       self.v_codes.data_ptr(), self.v_scales.data_ptr(), self.v_zeros.data_ptr(),
+                       self.k_res.data_ptr(), self.v_res.data_ptr())
+        self._ws = None
+
+    def reset(self):
+        self.quant_len, self.res_start, self.res_len = 0, 0, 0
+
+    def update(self, new_k, new_v, rounding=ROUND_HALF_AWAY):
+        """new_k/new_v: [num_units, n_new, D] (a view with a unit and a token
+        stride is fine as long as the last dim is contiguous)."""
+        assert new_k.is_cuda and new_v.is_cuda and new_k.dtype == new_v.dtype
+        assert new_k.shape == new_v.shape and new_k.shape[0] == self.num_units and new_k.shape[2] == self.D
+        if new_k.stride(2) != 1:
+            new_k = new_k.contiguous()
+        if new_v.stride(2) != 1:
+            new_v = new_v.contiguous()
+        ql, rs, rl = _i64(), _int(), _int()
+        _check(lib.kivi_cache_update(_c.byref(self.c), self.quant_len, self.res_start, self.res_len,
+                                     new_k.data_ptr(), new_v.data_ptr(), _dt(new_k),
+                                     new_k.stride(0), new_k.stride(1), new_v.stride(0), new_v.stride(1),
+                                     new_k.shape[1], rounding, _c.byref(ql), _c.byref(rs), _c.byref(rl), _stream()))
+        self.quant_len, self.res_start, self.res_len = ql.value, rs.value, rl.value
+
+    def materialize(self):
+        T = self.quant_len + self.res_len
+        k = torch.empty(self.num_units, T, self.D, dtype=torch.float32, device=self.device)
+        v = torch.empty_like(k)
+        if T:
+            _check(lib.kivi_cache_materialize(_c.byref(self.c), self.quant_len, self.res_start, self.res_len,
+                                              k.data_ptr(), v.data_ptr(), _stream()))
+        return k, v
+
+    def import_keys(self, packed, scales, zeros, seq_len):
+        _dev(packed, scales, zeros)
+        _check(lib.kivi_cache_import_keys(_c.byref(self.c), packed.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                          seq_len, _stream()))
+
+    def workspace(self, n_rep, num_splits=0):
+        need = lib.kivi_decode_attention_workspace(self.num_units, n_rep, self.D, num_splits)
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+        return self._ws
+
+    def attention(self, q, out=None, n_rep=None, sm_scale=0.0, num_splits=0, path=ATTN_AUTO, out_dtype=None):
+        """q: [num_units, n_rep, D] (or anything contiguous with that many elements)."""
+        _dev(q)
+        n_rep = n_rep or q.numel() // (self.num_units * self.D)
+        if out is None:
+            out = torch.empty(q.shape, dtype=out_dtype or q.dtype, device=q.device)
+        ws = self.workspace(n_rep, num_splits)
+        _check(lib.kivi_decode_attention(_c.byref(self.c), self.quant_len, self.res_start, self.res_len,
+                                         q.data_ptr(), _dt(q), out.data_ptr(), _dt(out), n_rep, float(sm_scale),
+                                         ws.data_ptr(), ws.numel(), num_splits, path, _stream()))
+        return out
+
+
+def load_state(store: "LayerStore", k_all, v_all, n_quant, rounding=ROUND_HALF_AWAY):
+    """Put ``store`` into the state "first n_quant tokens quantized, the rest in
+    the ring" for [num_units, T, D] device tensors.  The quantized part goes
+    through kivi_cache_update on a view of the layer whose window is one group
+    long (so every token is flushed); the ring is then filled directly.  Used to
+    build benchmark states such as a full ring, which add_tokens never leaves
+    behind (the reference flushes as soon as the window holds R tokens)."""
+    G = store.G
+    assert n_quant % G == 0 and k_all.shape[1] - n_quant <= store.R
+    store.reset()
+    if n_quant:
+        shadow = Layer.from_buffer_copy(store.c)
+        shadow.residual_cap = G
+        ql, rs, rl = _i64(), _int(), _int()
+        kq, vq = k_all[:, :n_quant], v_all[:, :n_quant]
+        _check(lib.kivi_cache_update(_c.byref(shadow), 0, 0, 0, kq.data_ptr(), vq.data_ptr(), _dt(kq),
+                                     kq.stride(0), kq.stride(1), vq.stride(0), vq.stride(1), n_quant, rounding,
+                                     _c.byref(ql), _c.byref(rs), _c.byref(rl), _stream()))
+        assert ql.value == n_quant and rl.value == 0
+    n_res = k_all.shape[1] - n_quant
+    if n_res:
+        store.k_res[:, :n_res] = k_all[:, n_quant:].to(store.dtype)
+        store.v_res[:, :n_res] = v_all[:, n_quant:].to(store.dtype)
+    store.quant_len, store.res_start, store.res_len = n_quant, 0, n_res

@@ -1,0 +1,308 @@
+// Fused decode attention over the packed KIVI cache: CUDA-core fp32 kernel.
+//
+//   out = softmax(q K^T * D^-0.5) V   over [quantized history || residual ring]
+// (formula: tests/integration/test_attention_fix.py:40-43; the operand is what
+// cache/manager.py:263-286 would serve, but nothing is ever dequantized to
+// memory).  Every number is fp32: codes are unpacked in registers, turned into
+// k = code*scale + zero, and fed to fp32 FMAs, so this kernel holds the 1e-5
+// tolerance of fp32 activations and covers every supported shape.  The
+// tensor-core kernel in attn_mma.cu is the fast path for the Llama shape.
+//
+// Work split: grid = (splits, units).  The quantized history of a unit is cut
+// into `nq_splits` runs of whole token groups; the residual ring is one more
+// split.  Inside a CTA each warp walks its own groups with a private running
+// (max, sum, output); warps are merged through shared memory and the CTA writes
+// one partial (max, sum, unnormalised output) per query head to the workspace.
+// merge_splits_kernel folds the partials (the only scratch memory of the op).
+//
+// Per 32-token chunk a warp does: lane = token for the q.k scores (each lane
+// walks the D channels of its token), a warp max, exp2, then lane = 4 channels
+// for p.V (each lane walks the chunk's tokens).
+#include "kivi_common.cuh"
+
+namespace kivi {
+
+
+namespace {
+
+constexpr int kWarps = 4;
+
+template <int NREP, int DB>
+__global__ void __launch_bounds__(kWarps * 32)
+attn_fp32_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
+                 const void* __restrict__ q, int q_dtype, float scale_log2,
+                 int nq_splits, int groups_per_split,
+                 float* __restrict__ part_o, float* __restrict__ part_ml) {
+    const int D = L.head_dim, G = L.group_size, Q = G / 4, W = D < 64 ? D : 64, ng = D / G;
+    const int u = blockIdx.y, split = blockIdx.x, n_splits = gridDim.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t max_groups = L.max_tokens / G;
+
+    extern __shared__ __align__(16) float smem[];
+    float* q_s = smem;                                   // [NREP][D]
+    float* sz_s = q_s + NREP * D + warp * 2 * D;         // per warp: scales[D], zeros[D]
+    float* p_s = q_s + NREP * D + kWarps * 2 * D + warp * 32 * NREP;   // per warp [32][NREP]
+    float* red_s = q_s + NREP * D + kWarps * 2 * D + kWarps * 32 * NREP;  // [kWarps][NREP][2] + [NREP][DB*128]
+
+    for (int i = threadIdx.x; i < NREP * D; i += blockDim.x)
+        q_s[i] = load_as_float(q, q_dtype, (int64_t)u * NREP * D + i);
+    __syncthreads();
+
+    float m[NREP], l[NREP], o[NREP][DB][4];
+#pragma unroll
+    for (int h = 0; h < NREP; ++h) {
+        m[h] = -INFINITY; l[h] = 0.0f;
+#pragma unroll
+        for (int b = 0; b < DB; ++b)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[h][b][i] = 0.0f;
+    }
+
+    // softmax update for one chunk of <= 32 tokens whose raw scores sit in acc[]
+    auto absorb_scores = [&](float (&acc)[NREP], bool valid) {
+#pragma unroll
+        for (int h = 0; h < NREP; ++h) {
+            float s = valid ? acc[h] * scale_log2 : -INFINITY;
+            float mx = s;
+#pragma unroll
+            for (int o_ = 16; o_ > 0; o_ >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o_));
+            const float m_new = fmaxf(m[h], mx);            // finite: every chunk has >= 1 token
+            const float alpha = exp2f(m[h] - m_new);        // exp2(-inf) = 0 on the first chunk
+            const float p = valid ? exp2f(s - m_new) : 0.0f;
+            m[h] = m_new;
+            l[h] = l[h] * alpha + p;
+#pragma unroll
+            for (int b = 0; b < DB; ++b)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o[h][b][i] *= alpha;
+            p_s[lane * NREP + h] = p;
+        }
+        __syncwarp();
+    };
+
+    if (split < nq_splits) {
+        const int64_t n_groups = quant_len / G;
+        const int64_t g_begin = (int64_t)split * groups_per_split;
+        int64_t g_end = g_begin + groups_per_split;
+        if (g_end > n_groups) g_end = n_groups;
+        for (int64_t g = g_begin + warp; g < g_end; g += kWarps) {
+            const int64_t gb = (int64_t)u * max_groups + g;
+            const uint8_t* kb = L.k_codes + gb * (D * Q);
+            __syncwarp();
+            for (int d = lane; d < D; d += 32) {
+                sz_s[d] = __ldg(L.k_scales + gb * D + d);
+                sz_s[D + d] = __ldg(L.k_zeros + gb * D + d);
+            }
+            __syncwarp();
+            for (int c0 = 0; c0 < G; c0 += 32) {
+                const int tt = c0 + lane;
+                const bool valid = tt < G;
+                float acc[NREP];
+#pragma unroll
+                for (int h = 0; h < NREP; ++h) acc[h] = 0.0f;
+                if (valid) {
+                    const int j = tt % Q, e = tt / Q;
+                    for (int d0 = 0; d0 < D; d0 += 4) {
+                        const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(kb + kblock_offset(d0, j, Q, W)));
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float code = (float)((w >> (8 * i + 2 * e)) & 3u);
+                            const float k = fmaf(code, sz_s[d0 + i], sz_s[D + d0 + i]);
+#pragma unroll
+                            for (int h = 0; h < NREP; ++h) acc[h] = fmaf(q_s[h * D + d0 + i], k, acc[h]);
+                        }
+                    }
+                }
+                absorb_scores(acc, valid);
+                const int ntok = G - c0 < 32 ? G - c0 : 32;
+                const int64_t t0 = g * G + c0;
+                const int64_t tb = (int64_t)u * L.max_tokens + t0;
+                for (int tk = 0; tk < ntok; ++tk) {
+                    float p[NREP];
+#pragma unroll
+                    for (int h = 0; h < NREP; ++h) p[h] = p_s[tk * NREP + h];
+#pragma unroll
+                    for (int b = 0; b < DB; ++b) {
+                        const int byte = lane + 32 * b;
+                        if (byte < D / 4) {
+                            const uint32_t vb = __ldg(L.v_codes + (tb + tk) * (D / 4) + byte);
+                            const int gd = (4 * byte) / G;
+                            const float s = __ldg(L.v_scales + (tb + tk) * ng + gd);
+                            const float z = __ldg(L.v_zeros + (tb + tk) * ng + gd);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float v = fmaf((float)((vb >> (2 * i)) & 3u), s, z);
+#pragma unroll
+                                for (int h = 0; h < NREP; ++h) o[h][b][i] = fmaf(p[h], v, o[h][b][i]);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // residual ring, full precision (cache/manager.py:275-278)
+        const int R = L.residual_cap;
+        for (int c0 = warp * 32; c0 < res_len; c0 += kWarps * 32) {
+            const int r = c0 + lane;
+            const bool valid = r < res_len;
+            float acc[NREP];
+#pragma unroll
+            for (int h = 0; h < NREP; ++h) acc[h] = 0.0f;
+            if (valid) {
+                const int slot = (res_start + r) % R;
+                const int64_t base = ((int64_t)u * R + slot) * D;
+                for (int d = 0; d < D; ++d) {
+                    const float k = load_as_float(L.k_res, L.res_dtype, base + d);
+#pragma unroll
+                    for (int h = 0; h < NREP; ++h) acc[h] = fmaf(q_s[h * D + d], k, acc[h]);
+                }
+            }
+            absorb_scores(acc, valid);
+            const int ntok = res_len - c0 < 32 ? res_len - c0 : 32;
+            for (int tk = 0; tk < ntok; ++tk) {
+                const int slot = (res_start + c0 + tk) % R;
+                const int64_t base = ((int64_t)u * R + slot) * D;
+                float p[NREP];
+#pragma unroll
+                for (int h = 0; h < NREP; ++h) p[h] = p_s[tk * NREP + h];
+#pragma unroll
+                for (int b = 0; b < DB; ++b) {
+                    const int byte = lane + 32 * b;
+                    if (byte < D / 4) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float v = load_as_float(L.v_res, L.res_dtype, base + 4 * byte + i);
+#pragma unroll
+                            for (int h = 0; h < NREP; ++h) o[h][b][i] = fmaf(p[h], v, o[h][b][i]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+        }
+    }
+
+    // ---- merge the warps of this CTA -------------------------------------
+    float* ml_s = red_s;                         // [kWarps][NREP][2]
+    float* o_s = red_s + kWarps * NREP * 2;      // [NREP][DB*128]
+#pragma unroll
+    for (int h = 0; h < NREP; ++h) {
+        float ls = l[h];
+#pragma unroll
+        for (int o_ = 16; o_ > 0; o_ >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o_);
+        if (lane == 0) { ml_s[(warp * NREP + h) * 2] = m[h]; ml_s[(warp * NREP + h) * 2 + 1] = ls; }
+    }
+    for (int i = threadIdx.x; i < NREP * DB * 128; i += blockDim.x) o_s[i] = 0.0f;
+    __syncthreads();
+    float M[NREP];
+#pragma unroll
+    for (int h = 0; h < NREP; ++h) {
+        float mm = -INFINITY;
+        for (int w = 0; w < kWarps; ++w) mm = fmaxf(mm, ml_s[(w * NREP + h) * 2]);
+        M[h] = mm;
+    }
+    for (int w = 0; w < kWarps; ++w) {
+        if (warp == w) {
+#pragma unroll
+            for (int h = 0; h < NREP; ++h) {
+                const float f = (m[h] == -INFINITY) ? 0.0f : exp2f(m[h] - M[h]);
+#pragma unroll
+                for (int b = 0; b < DB; ++b)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        o_s[h * DB * 128 + (lane + 32 * b) * 4 + i] += o[h][b][i] * f;
+            }
+        }
+        __syncthreads();
+    }
+    const int64_t pbase = ((int64_t)u * n_splits + split) * NREP;
+    for (int i = threadIdx.x; i < NREP * D; i += blockDim.x) {
+        const int h = i / D, d = i % D;
+        part_o[(pbase + h) * D + d] = o_s[h * DB * 128 + d];
+    }
+    if (threadIdx.x < NREP) {
+        const int h = threadIdx.x;
+        float ls = 0.0f;
+        for (int w = 0; w < kWarps; ++w) {
+            const float mw = ml_s[(w * NREP + h) * 2];
+            if (mw != -INFINITY) ls += ml_s[(w * NREP + h) * 2 + 1] * exp2f(mw - M[h]);
+        }
+        part_ml[(pbase + h) * 2] = M[h];
+        part_ml[(pbase + h) * 2 + 1] = ls;
+    }
+}
+
+}  // namespace
+
+// out[u][h][:] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
+// grid = (units, n_rep); partials laid out [(u*n_splits + s)*n_rep + h].
+__global__ void __launch_bounds__(256)
+merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                    void* __restrict__ out, int out_dtype, int n_splits, int D) {
+    extern __shared__ float w_s[];                   // [n_splits] weights
+    __shared__ float denom_s;
+    const int u = blockIdx.x, h = blockIdx.y, nrep = gridDim.y;
+    const int64_t row0 = (int64_t)u * n_splits * nrep + h;   // + s*nrep
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(row0 + (int64_t)s * nrep) * 2]);
+    if (threadIdx.x == 0) {
+        float den = 0.0f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = part_ml[(row0 + (int64_t)s * nrep) * 2];
+            const float wgt = (ms == -INFINITY) ? 0.0f : exp2f(ms - M);
+            w_s[s] = wgt;
+            den += wgt * part_ml[(row0 + (int64_t)s * nrep) * 2 + 1];
+        }
+        denom_s = den;
+    }
+    __syncthreads();
+    const float inv = 1.0f / denom_s;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < n_splits; ++s)
+            acc = fmaf(part_o[(row0 + (int64_t)s * nrep) * D + d], w_s[s], acc);
+        store_from_float(out, out_dtype, ((int64_t)u * nrep + h) * D + d, acc * inv);
+    }
+}
+
+template <int NREP>
+static int launch_fp32(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
+                       const void* q, int q_dtype, float scale_log2, int nq_splits, int gps,
+                       int n_splits, float* part_o, float* part_ml, cudaStream_t st) {
+    const int D = L->head_dim;
+    const int DB = D > 128 ? 2 : 1;
+    const size_t smem = sizeof(float) * ((size_t)NREP * D + kWarps * 2 * D + kWarps * 32 * NREP +
+                                         kWarps * NREP * 2 + (size_t)NREP * DB * 128);
+    dim3 grid((unsigned)n_splits, (unsigned)L->num_units);
+    if (DB == 1) {
+        if (smem > 48 * 1024) KIVI_CUDA_OK(cudaFuncSetAttribute(attn_fp32_kernel<NREP, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attn_fp32_kernel<NREP, 1><<<grid, kWarps * 32, smem, st>>>(*L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, gps, part_o, part_ml);
+    } else {
+        if (smem > 48 * 1024) KIVI_CUDA_OK(cudaFuncSetAttribute(attn_fp32_kernel<NREP, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attn_fp32_kernel<NREP, 2><<<grid, kWarps * 32, smem, st>>>(*L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, gps, part_o, part_ml);
+    }
+    KIVI_LAUNCH_OK();
+    return KIVI_OK;
+}
+
+int run_attn_fp32(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
+                  const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
+                  int n_splits, float* part_o, float* part_ml, cudaStream_t st) {
+    switch (n_rep) {
+        case 1: return launch_fp32<1>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st);
+        case 2: return launch_fp32<2>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st);
+        case 3: return launch_fp32<3>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st);
+        case 4: return launch_fp32<4>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st);
+        case 5: return launch_fp32<5>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st);
+        case 6: return launch_fp32<6>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st);
+        case 7: return launch_fp32<7>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st);
+        case 8: return launch_fp32<8>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st);
+        default: break;
+    }
+    set_error("n_rep (%d) outside 1..8", n_rep);
+    return KIVI_ERR_UNSUPPORTED;
+}
+
+}  // namespace kivi

@@ -1,0 +1,368 @@
+// Device-resident KIVI cache of one layer: on-device flush of whole token
+// groups into the packed store, ring append, compatibility materialisation.
+//
+// Replaces the storage side of the reference's KiviCache
+// (src/kivi_sycl/cache/manager.py:162-249 add_tokens, :309-374 _flush_group):
+// there the residual lives on the CPU and each flush is an H2D copy, a blocking
+// kernel, a D2H copy and an O(T) concatenation; here the host only does the
+// counter arithmetic and enqueues kernels.
+//
+// A flush reads its tokens from the "virtual sequence" [live ring tokens in age
+// order, then the new tokens], so one launch covers both a single decode flush
+// (all G tokens in the ring) and a bulk prefill (thousands of groups cut
+// straight out of the model's [units, S, D] tensor, the rest appended).
+#include "kivi_common.cuh"
+
+namespace kivi {
+namespace {
+
+struct TokenSource {
+    const void* ring;     // [units][R][D] of ring_dtype
+    const void* fresh;    // new tokens
+    int ring_dtype, fresh_dtype;
+    int R, D;
+    int res_start, res_len;
+    int64_t unit_stride, tok_stride;   // of `fresh`, in elements
+};
+
+// element d of virtual token tau of unit u
+__device__ __forceinline__ float src_load(const TokenSource& s, int u, int64_t tau, int d) {
+    if (tau < s.res_len) {
+        int slot = (int)((s.res_start + tau) % s.R);
+        return load_as_float(s.ring, s.ring_dtype, ((int64_t)u * s.R + slot) * s.D + d);
+    }
+    return load_as_float(s.fresh, s.fresh_dtype, (int64_t)u * s.unit_stride + (tau - s.res_len) * s.tok_stride + d);
+}
+
+// Keys of one token group of one unit: thread d owns channel d, reads the G
+// tokens of its channel (a warp reads 32 consecutive channels of one token per
+// instruction), quantizes them over the token axis, and the CTA writes one key
+// block.  Grid: (groups, units).  GT > 0 keeps the group in registers.
+template <int GT, bool HALF_EVEN>
+__global__ void __launch_bounds__(256)
+flush_keys_kernel(TokenSource src, uint8_t* __restrict__ k_codes, float* __restrict__ k_scales,
+                  float* __restrict__ k_zeros, int64_t max_groups, int64_t group0, int G) {
+    extern __shared__ __align__(16) uint8_t s_block[];   // D*G/4 bytes
+    const int D = src.D;
+    const int u = blockIdx.y;
+    const int64_t g = group0 + blockIdx.x;                // destination group index
+    const int64_t tau0 = (int64_t)blockIdx.x * G;         // first virtual token
+    const int Q = G / 4, W = D < 64 ? D : 64;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float mn = 1e30f, mx = -1e30f;
+        float x[GT > 0 ? GT : 1];
+        if (GT > 0) {
+#pragma unroll
+            for (int t = 0; t < GT; ++t) x[t] = src_load(src, u, tau0 + t, d);
+#pragma unroll
+            for (int t = 0; t < GT; ++t) { mn = fminf(mn, x[t]); mx = fmaxf(mx, x[t]); }
+        } else {
+            for (int t = 0; t < G; ++t) {
+                float v = src_load(src, u, tau0 + t, d);
+                mn = fminf(mn, v); mx = fmaxf(mx, v);
+            }
+        }
+        const float scale = group_scale(mn, mx);
+        k_scales[((int64_t)u * max_groups + g) * D + d] = scale;
+        k_zeros[((int64_t)u * max_groups + g) * D + d] = mn;
+        if (GT > 0) {
+#pragma unroll
+            for (int j = 0; j < GT / 4; ++j) {
+                float q0 = code_of<HALF_EVEN>(x[j], mn, scale);
+                float q1 = code_of<HALF_EVEN>(x[j + GT / 4], mn, scale);
+                float q2 = code_of<HALF_EVEN>(x[j + 2 * (GT / 4)], mn, scale);
+                float q3 = code_of<HALF_EVEN>(x[j + 3 * (GT / 4)], mn, scale);
+                s_block[kblock_offset(d, j, Q, W)] =
+                    (uint8_t)__float2int_rn(fmaf(q3, 64.0f, fmaf(q2, 16.0f, fmaf(q1, 4.0f, q0))));
+            }
+        } else {
+            for (int j = 0; j < Q; ++j) {
+                uint32_t byte = 0;
+                for (int e = 0; e < 4; ++e) {
+                    float q = code_of<HALF_EVEN>(src_load(src, u, tau0 + j + e * Q, d), mn, scale);
+                    byte |= (uint32_t)__float2int_rn(q) << (2 * e);
+                }
+                s_block[kblock_offset(d, j, Q, W)] = (uint8_t)byte;
+            }
+        }
+    }
+    __syncthreads();
+    const int block_bytes = D * Q;
+    uint8_t* dst = k_codes + ((int64_t)u * max_groups + g) * block_bytes;
+    if (block_bytes % 16 == 0) {
+        for (int i = threadIdx.x * 16; i < block_bytes; i += blockDim.x * 16)
+            *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(s_block + i);
+    } else {
+        for (int i = threadIdx.x; i < block_bytes; i += blockDim.x) dst[i] = s_block[i];
+    }
+}
+
+// Values: one thread per (token, channel group); groups of G consecutive
+// channels of one token (quantize_kernels.cpp:88-103).  Lanes of a warp take
+// consecutive channel groups, so a warp covers 32*G consecutive elements.
+template <bool HALF_EVEN>
+__global__ void __launch_bounds__(256)
+flush_values_kernel(TokenSource src, uint8_t* __restrict__ v_codes, float* __restrict__ v_scales,
+                    float* __restrict__ v_zeros, int64_t max_tokens, int64_t tok0,
+                    int64_t n_tok, int G) {
+    const int D = src.D, ng = D / G;
+    const int u = blockIdx.y;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // (token, group)
+    if (idx >= n_tok * ng) return;
+    const int64_t tau = idx / ng;
+    const int gd = (int)(idx % ng);
+    float mn = 1e30f, mx = -1e30f;
+    for (int i = 0; i < G; ++i) {
+        float v = src_load(src, u, tau, gd * G + i);
+        mn = fminf(mn, v); mx = fmaxf(mx, v);
+    }
+    const float scale = group_scale(mn, mx);
+    const int64_t t = tok0 + tau;
+    v_scales[((int64_t)u * max_tokens + t) * ng + gd] = scale;
+    v_zeros[((int64_t)u * max_tokens + t) * ng + gd] = mn;
+    uint8_t* dst = v_codes + ((int64_t)u * max_tokens + t) * (D / 4) + gd * (G / 4);
+    for (int i = 0; i < G; i += 4) {
+        uint32_t byte = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float q = code_of<HALF_EVEN>(src_load(src, u, tau, gd * G + i + e), mn, scale);
+            byte |= (uint32_t)__float2int_rn(q) << (2 * e);
+        }
+        dst[i / 4] = (uint8_t)byte;
+    }
+}
+
+// Copies virtual tokens [tau_from, tau_to) of the new tensor into their ring
+// slots (slot = (res_start + tau) % R); tokens already in the ring stay put.
+__global__ void __launch_bounds__(256)
+ring_append_kernel(TokenSource src, void* __restrict__ k_ring, void* __restrict__ v_ring,
+                   const void* __restrict__ fresh_v, int64_t unit_stride_v, int64_t tok_stride_v,
+                   int64_t tau_from, int64_t tau_to) {
+    const int D = src.D;
+    const int u = blockIdx.y;
+    const int64_t n = (tau_to - tau_from) * D;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t tau = tau_from + i / D;
+        const int d = (int)(i % D);
+        const int slot = (int)((src.res_start + tau) % src.R);
+        const int64_t o = ((int64_t)u * src.R + slot) * D + d;
+        const int64_t tn = tau - src.res_len;
+        float kv = load_as_float(src.fresh, src.fresh_dtype, (int64_t)u * src.unit_stride + tn * src.tok_stride + d);
+        float vv = load_as_float(fresh_v, src.fresh_dtype, (int64_t)u * unit_stride_v + tn * tok_stride_v + d);
+        store_from_float(k_ring, src.ring_dtype, o, kv);
+        store_from_float(v_ring, src.ring_dtype, o, vv);
+    }
+}
+
+// fp32 [units][T][D] keys and values: dequantized history then the window.
+__global__ void __launch_bounds__(256)
+materialize_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
+                   float* __restrict__ k_out, float* __restrict__ v_out) {
+    const int D = L.head_dim, G = L.group_size, Q = G / 4, W = D < 64 ? D : 64, ng = D / G;
+    const int u = blockIdx.y;
+    const int64_t T = quant_len + res_len;
+    const int64_t max_groups = L.max_tokens / G;
+    const int64_t n = T * D;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / D;
+        const int d = (int)(i % D);
+        float kv, vv;
+        if (t < quant_len) {
+            const int64_t g = t / G;
+            const int tt = (int)(t % G);
+            const int j = tt % Q, e = tt / Q;
+            const int64_t gb = (int64_t)u * max_groups + g;
+            uint32_t kb = L.k_codes[gb * (D * Q) + kblock_offset(d, j, Q, W)];
+            kv = dequant((float)((kb >> (2 * e)) & 3u), L.k_scales[gb * D + d], L.k_zeros[gb * D + d]);
+            const int64_t tb = (int64_t)u * L.max_tokens + t;
+            uint32_t vb = L.v_codes[tb * (D / 4) + d / 4];
+            vv = dequant((float)((vb >> (2 * (d % 4))) & 3u), L.v_scales[tb * ng + d / G], L.v_zeros[tb * ng + d / G]);
+        } else {
+            const int slot = (int)((res_start + (t - quant_len)) % L.residual_cap);
+            const int64_t o = ((int64_t)u * L.residual_cap + slot) * D + d;
+            kv = load_as_float(L.k_res, L.res_dtype, o);
+            vv = load_as_float(L.v_res, L.res_dtype, o);
+        }
+        k_out[(int64_t)u * n + i] = kv;
+        v_out[(int64_t)u * n + i] = vv;
+    }
+}
+
+// channel-major operator layout -> key blocks
+__global__ void __launch_bounds__(256)
+import_keys_kernel(kivi_layer L, const uint8_t* __restrict__ packed, const float* __restrict__ scales,
+                   const float* __restrict__ zeros, int64_t S) {
+    const int D = L.head_dim, G = L.group_size, Q = G / 4, W = D < 64 ? D : 64;
+    const int u = blockIdx.y;
+    const int64_t n_groups = S / G, max_groups = L.max_tokens / G;
+    const int64_t n = n_groups * D;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t g = i / D;
+        const int d = (int)(i % D);
+        const int64_t gb = (int64_t)u * max_groups + g;
+        L.k_scales[gb * D + d] = scales[((int64_t)u * D + d) * n_groups + g];
+        L.k_zeros[gb * D + d] = zeros[((int64_t)u * D + d) * n_groups + g];
+        // operator bytes of this (channel, group): byte b = tokens 4b..4b+3
+        const uint8_t* row = packed + ((int64_t)u * D + d) * (S / 4) + g * Q;
+        for (int j = 0; j < Q; ++j) {
+            uint32_t byte = 0;
+            for (int e = 0; e < 4; ++e) {
+                const int tt = j + e * Q;
+                byte |= ((row[tt / 4] >> (2 * (tt % 4))) & 3u) << (2 * e);
+            }
+            L.k_codes[gb * (D * Q) + kblock_offset(d, j, Q, W)] = (uint8_t)byte;
+        }
+    }
+}
+
+}  // namespace
+
+int validate_layer(const kivi_layer* L) {
+    KIVI_REQUIRE(L != nullptr, "layer is null");
+    KIVI_REQUIRE(L->num_units > 0, "num_units must be positive, got %d", L->num_units);
+    KIVI_REQUIRE(L->group_size >= 4 && L->group_size % 4 == 0,
+                 "group_size (%d) must be >= 4 and divisible by 4", L->group_size);
+    KIVI_REQUIRE(L->head_dim > 0 && L->head_dim % L->group_size == 0,
+                 "head_dim (%d) must be divisible by group_size (%d)", L->head_dim, L->group_size);
+    KIVI_REQUIRE(L->head_dim <= 64 || L->head_dim % 64 == 0,
+                 "head_dim (%d) must be <= 64 or a multiple of 64", L->head_dim);
+    KIVI_REQUIRE(L->head_dim <= 256, "head_dim (%d) above 256 is not supported", L->head_dim);
+    KIVI_REQUIRE(L->group_size <= L->residual_cap,
+                 "group_size (%d) must not exceed residual_length (%d)", L->group_size, L->residual_cap);
+    KIVI_REQUIRE(L->max_tokens >= 0 && L->max_tokens % L->group_size == 0,
+                 "max_tokens (%lld) must be a multiple of group_size", (long long)L->max_tokens);
+    KIVI_REQUIRE(L->res_dtype == KIVI_F32 || L->res_dtype == KIVI_BF16, "res_dtype must be KIVI_F32 or KIVI_BF16");
+    KIVI_REQUIRE(L->k_res && L->v_res, "residual ring pointers are null");
+    if (L->max_tokens > 0)
+        KIVI_REQUIRE(L->k_codes && L->k_scales && L->k_zeros && L->v_codes && L->v_scales && L->v_zeros,
+                     "quantized store pointers are null");
+    return KIVI_OK;
+}
+
+int validate_state(const kivi_layer* L, int64_t quant_len, int res_start, int res_len) {
+    KIVI_REQUIRE(quant_len >= 0 && quant_len % L->group_size == 0 && quant_len <= L->max_tokens,
+                 "quant_len (%lld) must be a multiple of group_size within max_tokens (%lld)",
+                 (long long)quant_len, (long long)L->max_tokens);
+    KIVI_REQUIRE(res_len >= 0 && res_len <= L->residual_cap, "res_len (%d) outside [0, %d]", res_len, L->residual_cap);
+    KIVI_REQUIRE(res_start >= 0 && res_start < L->residual_cap, "res_start (%d) outside [0, %d)", res_start, L->residual_cap);
+    return KIVI_OK;
+}
+
+}  // namespace kivi
+
+using namespace kivi;
+
+extern "C" int kivi_cache_plan(int64_t quant_len, int res_len, int n_new, int G, int R,
+                               int* n_flush_groups, int64_t* quant_len_out, int* res_len_out) {
+    KIVI_REQUIRE(G >= 4 && G % 4 == 0 && G <= R, "need 4 <= group_size <= residual_cap, group_size %% 4 == 0");
+    KIVI_REQUIRE(quant_len >= 0 && res_len >= 0 && n_new >= 0, "negative length");
+    const int64_t total = (int64_t)res_len + n_new;
+    // while (len >= R) flush G  ==  floor((total - R) / G) + 1 flushes when total >= R
+    const int64_t f = total >= R ? (total - R) / G + 1 : 0;
+    if (n_flush_groups) *n_flush_groups = (int)f;
+    if (quant_len_out) *quant_len_out = quant_len + f * G;
+    if (res_len_out) *res_len_out = (int)(total - f * G);
+    return KIVI_OK;
+}
+
+extern "C" int kivi_cache_update(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
+                                 const void* new_k, const void* new_v, int new_dtype,
+                                 int64_t unit_stride_k, int64_t tok_stride_k,
+                                 int64_t unit_stride_v, int64_t tok_stride_v, int n_new,
+                                 int rounding, int64_t* quant_len_out, int* res_start_out,
+                                 int* res_len_out, void* stream) {
+    if (int rc = validate_layer(L)) return rc;
+    if (int rc = validate_state(L, quant_len, res_start, res_len)) return rc;
+    KIVI_REQUIRE(n_new > 0, "the forward pass produced no new tokens (n_new = %d)", n_new);
+    KIVI_REQUIRE(new_k && new_v, "new_k / new_v are null");
+    KIVI_REQUIRE(new_dtype == KIVI_F32 || new_dtype == KIVI_BF16, "new_dtype must be KIVI_F32 or KIVI_BF16");
+    KIVI_REQUIRE(rounding == KIVI_ROUND_HALF_AWAY || rounding == KIVI_ROUND_HALF_EVEN, "unknown rounding %d", rounding);
+    KIVI_REQUIRE(tok_stride_k >= L->head_dim && tok_stride_v >= L->head_dim, "token stride smaller than head_dim");
+    const int G = L->group_size, R = L->residual_cap, D = L->head_dim;
+    int f = 0, rl_out = 0;
+    int64_t ql_out = 0;
+    kivi_cache_plan(quant_len, res_len, n_new, G, R, &f, &ql_out, &rl_out);
+    KIVI_REQUIRE(ql_out <= L->max_tokens, "quantized store overflow: need %lld tokens, capacity %lld",
+                 (long long)ql_out, (long long)L->max_tokens);
+    cudaStream_t st = (cudaStream_t)stream;
+    int launches = 0;
+    TokenSource sk{L->k_res, new_k, L->res_dtype, new_dtype, R, D, res_start, res_len, unit_stride_k, tok_stride_k};
+    TokenSource sv{L->v_res, new_v, L->res_dtype, new_dtype, R, D, res_start, res_len, unit_stride_v, tok_stride_v};
+    const int64_t max_groups = L->max_tokens / G;
+    if (f > 0) {
+        const int64_t group0 = quant_len / G;
+        KIVI_REQUIRE(f <= 0x7fffffff && L->num_units <= 65535, "grid too large");
+        dim3 grid((unsigned)f, (unsigned)L->num_units);
+        const int threads = D >= 256 ? 256 : (D >= 128 ? 128 : (D >= 64 ? 64 : 32));
+        const size_t smem = (size_t)D * G / 4;
+        const bool he = rounding == KIVI_ROUND_HALF_EVEN;
+        if (G == 32) {
+            if (he) flush_keys_kernel<32, true><<<grid, threads, smem, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0, G);
+            else flush_keys_kernel<32, false><<<grid, threads, smem, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0, G);
+        } else {
+            if (he) flush_keys_kernel<0, true><<<grid, threads, smem, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0, G);
+            else flush_keys_kernel<0, false><<<grid, threads, smem, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0, G);
+        }
+        KIVI_LAUNCH_OK();
+        const int64_t n_tok = (int64_t)f * G;
+        const int64_t items = n_tok * (D / G);
+        dim3 gridv((unsigned)((items + 255) / 256), (unsigned)L->num_units);
+        if (he) flush_values_kernel<true><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, n_tok, G);
+        else flush_values_kernel<false><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, n_tok, G);
+        KIVI_LAUNCH_OK();
+        launches += 2;
+    }
+    // tokens of the virtual sequence that stay: [f*G, res_len + n_new); those
+    // with tau >= res_len come from the new tensor and must be copied in.
+    const int64_t total = (int64_t)res_len + n_new;
+    const int64_t tau_from = (int64_t)f * G > res_len ? (int64_t)f * G : res_len;
+    if (tau_from < total) {
+        const int64_t n = (total - tau_from) * D;
+        unsigned bx = (unsigned)((n + 255) / 256);
+        if (bx > 64) bx = 64;
+        dim3 grid(bx, (unsigned)L->num_units);
+        ring_append_kernel<<<grid, 256, 0, st>>>(sk, L->k_res, L->v_res, new_v, unit_stride_v, tok_stride_v, tau_from, total);
+        KIVI_LAUNCH_OK();
+        launches += 1;
+    }
+    if (quant_len_out) *quant_len_out = ql_out;
+    if (res_start_out) *res_start_out = (int)((res_start + (int64_t)f * G) % R);
+    if (res_len_out) *res_len_out = rl_out;
+    note_launches(launches);
+    return KIVI_OK;
+}
+
+extern "C" int kivi_cache_materialize(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
+                                      float* k_out, float* v_out, void* stream) {
+    if (int rc = validate_layer(L)) return rc;
+    if (int rc = validate_state(L, quant_len, res_start, res_len)) return rc;
+    KIVI_REQUIRE(k_out && v_out, "output pointers are null");
+    const int64_t n = (quant_len + res_len) * L->head_dim;
+    if (n == 0) { note_launches(0); return KIVI_OK; }
+    unsigned bx = (unsigned)((n + 255) / 256);
+    if (bx > 1024) bx = 1024;
+    dim3 grid(bx, (unsigned)L->num_units);
+    materialize_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(*L, quant_len, res_start, res_len, k_out, v_out);
+    KIVI_LAUNCH_OK();
+    note_launches(1);
+    return KIVI_OK;
+}
+
+extern "C" int kivi_cache_import_keys(const kivi_layer* L, const uint8_t* packed, const float* scales,
+                                      const float* zeros, int64_t seq_len, void* stream) {
+    if (int rc = validate_layer(L)) return rc;
+    KIVI_REQUIRE(packed && scales && zeros, "packed / scales / zeros are null");
+    KIVI_REQUIRE(seq_len > 0 && seq_len % L->group_size == 0 && seq_len <= L->max_tokens,
+                 "seq_len (%lld) must be a positive multiple of group_size within max_tokens", (long long)seq_len);
+    const int64_t n = seq_len / L->group_size * L->head_dim;
+    unsigned bx = (unsigned)((n + 255) / 256);
+    if (bx > 1024) bx = 1024;
+    dim3 grid(bx, (unsigned)L->num_units);
+    import_keys_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(*L, packed, scales, zeros, seq_len);
+    KIVI_LAUNCH_OK();
+    note_launches(1);
+    return KIVI_OK;
+}

@@ -1,0 +1,188 @@
+// extern "C" surface of libkivi_cuda: error state, operator wrappers, and the
+// decode-attention dispatcher (split planning, workspace carve-up, merge).
+#include <math.h>
+#include <stdarg.h>
+#include <string.h>
+
+#include "kivi_common.cuh"
+
+namespace kivi {
+
+static thread_local char g_err[512] = "";
+static thread_local int g_launches = 0;
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+void note_launches(int n) { g_launches = n; }
+
+int num_sms() {
+    static thread_local int cached_dev = -1, cached = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev != cached_dev) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached = n;
+        cached_dev = dev;
+    }
+    return cached;
+}
+
+constexpr int kMaxSplitsC = 128;
+
+int run_group_quant(const void* in, int in_dtype, uint8_t* packed, float* scales, float* zeros,
+                    float* rt, int64_t num_groups, int G, int rounding, int mode, cudaStream_t st);
+int run_group_dequant(const uint8_t* packed, const float* scales, const float* zeros, float* out,
+                      int64_t num_groups, int G, cudaStream_t st);
+int validate_layer(const kivi_layer* L);
+int validate_state(const kivi_layer* L, int64_t quant_len, int res_start, int res_len);
+int run_attn_fp32(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
+                  const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
+                  int n_splits, float* part_o, float* part_ml, cudaStream_t st);
+bool attn_mma_supported(const kivi_layer* L, int n_rep, int q_dtype);
+int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
+                 const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
+                 int n_splits, float* part_o, float* part_ml, cudaStream_t st);
+__global__ void merge_splits_kernel(const float* part_o, const float* part_ml, void* out,
+                                    int out_dtype, int n_splits, int D);
+
+}  // namespace kivi
+
+using namespace kivi;
+
+extern "C" const char* kivi_last_error(void) { return g_err; }
+extern "C" int kivi_version(void) { return 100; }
+extern "C" int kivi_last_launch_count(void) { return g_launches; }
+
+static int check_values_args(int64_t num_tokens, int head_dim, int group_size) {
+    KIVI_REQUIRE(group_size > 0 && group_size % 4 == 0, "group_size must be positive and divisible by 4");
+    KIVI_REQUIRE(head_dim > 0 && head_dim % group_size == 0, "head_dim must be positive and divisible by group_size");
+    KIVI_REQUIRE(num_tokens > 0, "input must be non-empty");
+    return KIVI_OK;
+}
+
+extern "C" int kivi_quantize_keys_per_channel(const void* input, int in_dtype, uint8_t* output,
+                                              float* scales, float* zeros, int64_t num_channels,
+                                              int group_size, int rounding, void* stream) {
+    return run_group_quant(input, in_dtype, output, scales, zeros, nullptr, num_channels, group_size,
+                           rounding, 0, (cudaStream_t)stream);
+}
+
+extern "C" int kivi_quantize_values_per_token(const void* input, int in_dtype, uint8_t* output,
+                                              float* scales, float* zeros, int64_t num_tokens,
+                                              int head_dim, int group_size, int rounding, void* stream) {
+    if (int rc = check_values_args(num_tokens, head_dim, group_size)) return rc;
+    return run_group_quant(input, in_dtype, output, scales, zeros, nullptr,
+                           num_tokens * (head_dim / group_size), group_size, rounding, 0, (cudaStream_t)stream);
+}
+
+extern "C" int kivi_dequantize_keys_per_channel(const uint8_t* input, const float* scales,
+                                                const float* zeros, float* output,
+                                                int64_t num_channels, int group_size, void* stream) {
+    return run_group_dequant(input, scales, zeros, output, num_channels, group_size, (cudaStream_t)stream);
+}
+
+extern "C" int kivi_dequantize_values_per_token(const uint8_t* input, const float* scales,
+                                                const float* zeros, float* output,
+                                                int64_t num_groups, int group_size, void* stream) {
+    return run_group_dequant(input, scales, zeros, output, num_groups, group_size, (cudaStream_t)stream);
+}
+
+extern "C" int kivi_quant_dequant_roundtrip_keys(const void* input, int in_dtype, float* output,
+                                                 int64_t num_channels, int group_size, int rounding,
+                                                 void* stream) {
+    return run_group_quant(input, in_dtype, nullptr, nullptr, nullptr, output, num_channels, group_size,
+                           rounding, 1, (cudaStream_t)stream);
+}
+
+extern "C" int kivi_quant_dequant_roundtrip_values(const void* input, int in_dtype, float* output,
+                                                   int64_t num_tokens, int head_dim, int group_size,
+                                                   int rounding, void* stream) {
+    if (int rc = check_values_args(num_tokens, head_dim, group_size)) return rc;
+    return run_group_quant(input, in_dtype, nullptr, nullptr, nullptr, output,
+                           num_tokens * (head_dim / group_size), group_size, rounding, 1, (cudaStream_t)stream);
+}
+
+// ---- decode attention ------------------------------------------------------
+
+extern "C" int kivi_decode_attention_max_splits(void) { return kMaxSplitsC; }
+
+// partial outputs [units][splits+1][n_rep][D] + (max, sum) [units][splits+1][n_rep][2];
+// the +1 is the residual-ring split.
+extern "C" size_t kivi_decode_attention_workspace(int num_units, int n_rep, int head_dim, int num_splits) {
+    if (num_units <= 0 || n_rep <= 0 || head_dim <= 0) return 0;
+    if (num_splits <= 0 || num_splits > kMaxSplitsC) num_splits = kMaxSplitsC;
+    return (size_t)num_units * (num_splits + 1) * n_rep * (head_dim + 2) * sizeof(float);
+}
+
+static int plan_splits(int num_units, int64_t n_groups, int requested) {
+    if (n_groups <= 0) return 0;
+    int s = requested;
+    if (s <= 0) {
+        // aim at ~8 CTAs of 128 threads per SM, never below 4 token groups per CTA
+        const int64_t target = (int64_t)num_sms() * 8;
+        s = (int)((target + num_units - 1) / num_units);
+        const int64_t cap = (n_groups + 3) / 4;
+        if (s > cap) s = (int)cap;
+    }
+    if (s > kMaxSplitsC) s = kMaxSplitsC;
+    if (s > n_groups) s = (int)n_groups;
+    if (s < 1) s = 1;
+    return s;
+}
+
+extern "C" int kivi_decode_attention(const kivi_layer* L, int64_t quant_len, int res_start,
+                                     int res_len, const void* q, int q_dtype, void* out, int out_dtype,
+                                     int n_rep, float sm_scale, void* workspace, size_t workspace_bytes,
+                                     int num_splits, int path, void* stream) {
+    if (int rc = validate_layer(L)) return rc;
+    if (int rc = validate_state(L, quant_len, res_start, res_len)) return rc;
+    KIVI_REQUIRE(q && out, "q / out are null");
+    KIVI_REQUIRE(q_dtype == KIVI_F32 || q_dtype == KIVI_BF16, "q dtype must be KIVI_F32 or KIVI_BF16");
+    KIVI_REQUIRE(out_dtype == KIVI_F32 || out_dtype == KIVI_BF16, "out dtype must be KIVI_F32 or KIVI_BF16");
+    KIVI_REQUIRE(n_rep >= 1 && n_rep <= 8, "n_rep (%d) outside 1..8", n_rep);
+    KIVI_REQUIRE(quant_len + res_len > 0, "the cache is empty: nothing to attend to");
+    KIVI_REQUIRE(num_splits >= 0 && num_splits <= kMaxSplitsC, "num_splits (%d) outside 0..%d", num_splits, kMaxSplitsC);
+    KIVI_REQUIRE(path == KIVI_ATTN_AUTO || path == KIVI_ATTN_FP32 || path == KIVI_ATTN_MMA, "unknown path %d", path);
+    KIVI_REQUIRE(L->num_units <= 65535, "num_units (%d) above 65535", L->num_units);
+    const int D = L->head_dim, G = L->group_size;
+    const int64_t n_groups = quant_len / G;
+    const int nq_splits = plan_splits(L->num_units, n_groups, num_splits);
+    const int gps = nq_splits > 0 ? (int)((n_groups + nq_splits - 1) / nq_splits) : 0;
+    const int n_splits = nq_splits + (res_len > 0 ? 1 : 0);
+    const size_t need = (size_t)L->num_units * n_splits * n_rep * (D + 2) * sizeof(float);
+    KIVI_REQUIRE(workspace != nullptr && workspace_bytes >= need,
+                 "workspace too small: %zu bytes given, %zu needed", workspace_bytes, need);
+    float* part_o = reinterpret_cast<float*>(workspace);
+    float* part_ml = part_o + (size_t)L->num_units * n_splits * n_rep * D;
+    if (sm_scale <= 0.0f) sm_scale = 1.0f / sqrtf((float)D);
+    const float scale_log2 = sm_scale * 1.4426950408889634f;
+    cudaStream_t st = (cudaStream_t)stream;
+
+    bool use_mma = false;
+    if (path == KIVI_ATTN_MMA) {
+        if (!attn_mma_supported(L, n_rep, q_dtype)) {
+            set_error("tensor-core path needs head_dim 128, group_size 32, n_rep <= 4 (got %d, %d, %d)", D, G, n_rep);
+            return KIVI_ERR_UNSUPPORTED;
+        }
+        use_mma = true;
+    } else if (path == KIVI_ATTN_AUTO) {
+        // fp32 queries keep the all-fp32 kernel (1e-5 tolerance); bf16 queries take
+        // the tensor-core kernel when the shape allows it
+        use_mma = q_dtype == KIVI_BF16 && attn_mma_supported(L, n_rep, q_dtype);
+    }
+    int rc = use_mma
+        ? run_attn_mma(L, quant_len, res_start, res_len, q, q_dtype, n_rep, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st)
+        : run_attn_fp32(L, quant_len, res_start, res_len, q, q_dtype, n_rep, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st);
+    if (rc) return rc;
+    dim3 grid((unsigned)L->num_units, (unsigned)n_rep);
+    merge_splits_kernel<<<grid, D >= 256 ? 256 : 128, n_splits * sizeof(float), st>>>(part_o, part_ml, out, out_dtype, n_splits, D);
+    KIVI_LAUNCH_OK();
+    note_launches(2);
+    return KIVI_OK;
+}

@@ -1,0 +1,89 @@
+// Shared host/device helpers of libkivi_cuda (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "kivi_cuda.h"
+
+namespace kivi {
+
+// ---- error plumbing ---------------------------------------------------------
+void set_error(const char* fmt, ...);
+void note_launches(int n);
+int num_sms();
+
+#define KIVI_REQUIRE(cond, ...)                        \
+    do {                                               \
+        if (!(cond)) {                                 \
+            ::kivi::set_error(__VA_ARGS__);            \
+            return KIVI_ERR_INVALID_ARGUMENT;          \
+        }                                              \
+    } while (0)
+
+#define KIVI_CUDA_OK(expr)                                                          \
+    do {                                                                            \
+        cudaError_t e_ = (expr);                                                    \
+        if (e_ != cudaSuccess) {                                                    \
+            ::kivi::set_error("%s failed: %s", #expr, cudaGetErrorString(e_));      \
+            return KIVI_ERR_CUDA;                                                   \
+        }                                                                           \
+    } while (0)
+
+#define KIVI_LAUNCH_OK()  KIVI_CUDA_OK(cudaGetLastError())
+
+// ---- arithmetic that must match the reference bit for bit ------------------
+// scale = (max - min) / 3.0f + 1e-10f      (quantize_kernels.cpp:46)
+__device__ __forceinline__ float group_scale(float mn, float mx) {
+    return __fadd_rn(__fdiv_rn(__fsub_rn(mx, mn), 3.0f), 1e-10f);
+}
+
+// q = clamp(round((x - min) / scale), 0, 3) as a float in {0,1,2,3}
+// (quant_tile.hpp:61-66).  IEEE division; HALF_EVEN selects rintf.
+template <bool HALF_EVEN>
+__device__ __forceinline__ float code_of(float x, float mn, float scale) {
+    const float t = __fdiv_rn(__fsub_rn(x, mn), scale);
+    float r;
+    if (HALF_EVEN) {
+        r = rintf(t);
+    } else {
+        // t >= 0 here, so "half away from zero" is floor(t) + (frac(t) >= 0.5);
+        // t - floor(t) is exact, unlike floor(t + 0.5f).
+        const float fl = floorf(t);
+        r = (__fsub_rn(t, fl) >= 0.5f) ? fl + 1.0f : fl;
+    }
+    return fminf(fmaxf(r, 0.0f), 3.0f);
+}
+
+// out = float(q) * scale + zero with a separate multiply and add
+// (dequantize_kernels.cpp:23-25)
+__device__ __forceinline__ float dequant(float q, float scale, float zero) {
+    return __fadd_rn(__fmul_rn(q, scale), zero);
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t hi16) {
+    return __uint_as_float(hi16 << 16);
+}
+
+__device__ __forceinline__ float load_as_float(const void* p, int dtype, int64_t i) {
+    if (dtype == KIVI_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+    return reinterpret_cast<const float*>(p)[i];
+}
+
+__device__ __forceinline__ void store_from_float(void* p, int dtype, int64_t i, float v) {
+    if (dtype == KIVI_BF16) reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+    else reinterpret_cast<float*>(p)[i] = v;
+}
+
+// ---- key block layout --------------------------------------------------------
+// Byte offset inside one key block of the codes of channel d, token lane j
+// (tokens j, j+Q, j+2Q, j+3Q of the group; Q = G/4); W = min(D, 64).
+__host__ __device__ __forceinline__ int kblock_offset(int d, int j, int Q, int W) {
+    return (d / W) * Q * W + j * W + (d % W);
+}
+
+__host__ __device__ __forceinline__ int elem_size(int dtype) { return dtype == KIVI_BF16 ? 2 : 4; }
+
+}  // namespace kivi

@@ -1,0 +1,187 @@
+"""GPU parity of the device-resident cache and the fused decode attention,
+through the C ABI, against the oracle and the reference-made golden vectors.
+
+Tolerances (relative = max|out-ref| / max|ref| per (unit, head) row):
+fp32 activations 1e-5; bf16 activations 2e-3."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import kivi_oracle as ko
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-5
+TOL_BF16 = 2e-3
+
+
+@pytest.fixture(scope="module")
+def cabi():
+    from intel_kivi_hybrid_b200 import cabi as m
+    return m
+
+
+def rel_err(out, ref):
+    out, ref = out.float().cpu(), ref.float().cpu()
+    num = (out - ref).abs().amax(dim=-1)
+    den = ref.abs().amax(dim=-1).clamp_min(1e-30)
+    return float((num / den).max())
+
+
+def units(x):            # [B,H,T,D] -> [B*H,T,D]
+    return x.reshape(x.shape[0] * x.shape[1], *x.shape[2:])
+
+
+def test_state_machine_matches_reference_cache(cabi, golden_dir):
+    sm = np.load(os.path.join(golden_dir, "state_machine_vectors.npz"))
+    K, V = torch.from_numpy(sm["long__K"]), torch.from_numpy(sm["long__V"])
+    st = cabi.LayerStore(3, 64, 32, 128, 512, torch.float32, "cuda")
+    Kc, Vc = units(K).cuda(), units(V).cuda()
+    st.update(Kc[:, :200], Vc[:, :200], cabi.ROUND_HALF_EVEN)
+    assert (st.quant_len, st.res_len) == (96, 104)
+    for t in range(200, 300):
+        st.update(Kc[:, t:t + 1], Vc[:, t:t + 1], cabi.ROUND_HALF_EVEN)
+    assert st.quant_len == int(sm["long__quant_tokens"])
+    k, v = st.materialize()
+    assert torch.equal(k.cpu().reshape(1, 3, -1, 64), torch.from_numpy(sm["long__served_k"]))
+    assert torch.equal(v.cpu().reshape(1, 3, -1, 64), torch.from_numpy(sm["long__served_v"]))
+
+
+def test_small_g_state_machine_matches_reference_cache(cabi, golden_dir):
+    sm = np.load(os.path.join(golden_dir, "state_machine_vectors.npz"))
+    steps, prefill, G, R, D, layers, heads = [int(v) for v in sm["params"]]
+    for i in range(layers):
+        truth = torch.from_numpy(sm[f"in_place__truth_k{i}"])
+        tk = units(truth).cuda()
+        tv = (2 * torch.arange(truth.shape[2]).view(1, 1, -1, 1).float() - truth)
+        tv = units(tv).cuda()
+        st = cabi.LayerStore(heads, D, G, R, 64, torch.float32, "cuda")
+        st.update(tk[:, :prefill], tv[:, :prefill], cabi.ROUND_HALF_EVEN)
+        for t in range(prefill, prefill + steps):
+            st.update(tk[:, t:t + 1], tv[:, t:t + 1], cabi.ROUND_HALF_EVEN)
+        k, _ = st.materialize()
+        assert torch.equal(k.cpu().reshape(1, heads, -1, D), torch.from_numpy(sm[f"in_place__served_k{i}"]))
+        assert st.quant_len == int(sm["in_place__quant_tokens"][i])
+
+
+def test_packed_store_matches_oracle_flush_by_flush(cabi):
+    B, H, D, G, R = 1, 4, 64, 32, 128
+    K = ko.make_keys(B, H, 300, D, seed=21)
+    V = ko.make_values(B, H, 300, D, seed=21)
+    oc = ko.OracleCache(D, G, R, rounding="half_away")
+    st = cabi.LayerStore(B * H, D, G, R, 512, torch.float32, "cuda")
+    Kc, Vc = units(K).cuda(), units(V).cuda()
+    oc.append(K[:, :, :150], V[:, :, :150]); st.update(Kc[:, :150], Vc[:, :150])
+    for t in range(150, 300):
+        oc.append(K[:, :, t:t + 1], V[:, :, t:t + 1]); st.update(Kc[:, t:t + 1], Vc[:, t:t + 1])
+    assert st.quant_len == oc.quantized_len and st.res_len == oc.residual_len
+    ng = st.quant_len // G
+    ks = torch.stack(oc.k_scales, dim=2).reshape(B * H, ng, D)
+    kz = torch.stack(oc.k_zeros, dim=2).reshape(B * H, ng, D)
+    assert torch.equal(st.k_scales[:, :ng].cpu(), ks) and torch.equal(st.k_zeros[:, :ng].cpu(), kz)
+    vs = torch.cat(oc.v_scales, dim=2).reshape(B * H, ng * G, D // G)
+    assert torch.equal(st.v_scales[:, :ng * G].cpu(), vs)
+    vp = torch.cat(oc.v_packed, dim=2).reshape(B * H, ng * G, D // 4)
+    assert torch.equal(st.v_codes[:, :ng * G].cpu(), vp)
+    # key blocks hold the same codes as the reference layout, re-laid out
+    kc = ko.unpack_codes(torch.stack(oc.k_packed, dim=2).reshape(B * H, ng, D, G // 4))   # [u,g,D,G]
+    blk = st.k_codes[:, :ng].cpu().reshape(B * H, ng, G // 4, D)                            # D <= 64: [j][d]
+    Q = G // 4
+    for e in range(4):
+        got = (blk >> (2 * e)) & 3                       # tokens j + e*Q
+        assert torch.equal(got.transpose(2, 3), kc[..., e * Q:(e + 1) * Q].to(torch.uint8))
+    # served tensors: history round trip + exact residual
+    k, v = st.materialize()
+    sk, sv = oc.served()
+    assert torch.equal(k.cpu(), units(sk)) and torch.equal(v.cpu(), units(sv))
+
+
+def test_import_keys_from_operator_layout(cabi):
+    B, H, D, G, S = 1, 2, 128, 32, 96
+    K = ko.make_keys(B, H, S, D, seed=3)
+    kt = units(K).transpose(1, 2).contiguous().cuda()          # [u, D, S]
+    packed = torch.empty(B * H, D, S // 4, dtype=torch.uint8, device="cuda")
+    scales = torch.empty(B * H, D, S // G, device="cuda")
+    zeros = torch.empty(B * H, D, S // G, device="cuda")
+    cabi.quantize_keys(kt, packed, scales, zeros, G)
+    a = cabi.LayerStore(B * H, D, G, 128, S, torch.float32, "cuda")
+    a.import_keys(packed, scales, zeros, S)
+    b = cabi.LayerStore(B * H, D, G, 128, S, torch.float32, "cuda")
+    cabi.load_state(b, units(K).cuda(), units(K).cuda(), S)
+    assert torch.equal(a.k_codes, b.k_codes) and torch.equal(a.k_scales, b.k_scales) and torch.equal(a.k_zeros, b.k_zeros)
+
+
+def _attention_case(cabi, B, Hkv, n_rep, D, G, R, n_quant, n_res, dtype, seed, path, num_splits=0,
+                    res_start=0, out_dtype=torch.float32):
+    T = n_quant + n_res
+    K = ko.make_keys(B, Hkv, T, D, seed).to(dtype)
+    V = ko.make_values(B, Hkv, T, D, seed).to(dtype)
+    q = ko.make_queries(B, Hkv * n_rep, D, seed).to(dtype)
+    ref = ko.kivi_decode_attention(q, K, V, n_quant, G, "half_away")
+    ref64 = ko.kivi_decode_attention(q, K, V, n_quant, G, "half_away", dtype=torch.float64)
+    st = cabi.LayerStore(B * Hkv, D, G, R, max(n_quant, G), dtype, "cuda")
+    cabi.load_state(st, units(K).cuda(), units(V).cuda(), n_quant)
+    if res_start:                       # rotate the ring: same window, different slots
+        st.k_res.copy_(torch.roll(st.k_res, res_start, dims=1))
+        st.v_res.copy_(torch.roll(st.v_res, res_start, dims=1))
+        st.res_start = res_start % R
+    out = st.attention(q.cuda().contiguous(), n_rep=n_rep, num_splits=num_splits, path=path, out_dtype=out_dtype)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    return rel_err(out, ref64.float()), rel_err(ref, ref64.float()), out, ref64
+
+
+def test_attention_golden_seed42(cabi, golden_dir):
+    av = np.load(os.path.join(golden_dir, "attention_vectors.npz"))
+    q, k, v = (torch.from_numpy(av[n]) for n in ("query", "key", "value"))
+    st = cabi.LayerStore(2, 64, 32, 128, 32, torch.float32, "cuda")
+    cabi.load_state(st, units(k).cuda(), units(v).cuda(), 32, cabi.ROUND_HALF_EVEN)
+    for i in range(q.shape[2]):
+        out = st.attention(q[:, :, i].contiguous().cuda(), n_rep=1)
+        assert rel_err(out, torch.from_numpy(av["out_kivi"])[:, :, i]) < TOL_F32
+
+
+@pytest.mark.parametrize("n_quant,n_res,res_start", [(416, 96, 0), (608, 104, 40), (0, 77, 0), (96, 0, 0), (32, 1, 127)])
+def test_attention_fp32_gpt2_shapes(cabi, n_quant, n_res, res_start):
+    # config 0: B=1, H=12 (MHA), D=64, fp32, R=128, G=32
+    err, oerr, _, _ = _attention_case(cabi, 1, 12, 1, 64, 32, 128, n_quant, n_res, torch.float32, 7,
+                                      cabi.ATTN_FP32, res_start=res_start)
+    print(f"[attn fp32 cfg0 q={n_quant} r={n_res}] rel err {err:.2e} (fp32 oracle vs fp64: {oerr:.2e})")
+    assert err < TOL_F32
+
+
+@pytest.mark.parametrize("D,G,n_rep", [(128, 32, 4), (128, 64, 2), (64, 16, 1), (128, 128, 8), (256, 32, 2), (32, 4, 3)])
+def test_attention_fp32_shapes(cabi, D, G, n_rep):
+    err, _, _, _ = _attention_case(cabi, 2, 2, n_rep, D, G, max(G, 64), 4 * G, max(G, 64) - 3, torch.float32, 11,
+                                   cabi.ATTN_FP32)
+    assert err < TOL_F32
+
+
+@pytest.mark.parametrize("splits", [1, 2, 7, 31])
+def test_attention_split_count_does_not_change_result(cabi, splits):
+    err, _, out, _ = _attention_case(cabi, 1, 2, 4, 128, 32, 128, 31 * 32, 128, torch.float32, 5,
+                                     cabi.ATTN_FP32, num_splits=splits)
+    assert err < TOL_F32
+
+
+def test_attention_bf16_llama_shape_fp32_kernel(cabi):
+    # config 1 slice: GQA 4:1, D=128, bf16 activations, full ring
+    err, _, _, _ = _attention_case(cabi, 2, 8, 4, 128, 32, 128, 3968, 128, torch.bfloat16, 13, cabi.ATTN_FP32)
+    print(f"[attn bf16 cfg1 slice, fp32 kernel] rel err {err:.2e}")
+    assert err < TOL_BF16
+    err, _, _, _ = _attention_case(cabi, 2, 8, 4, 128, 32, 128, 3968, 128, torch.bfloat16, 13, cabi.ATTN_FP32,
+                                   out_dtype=torch.bfloat16)
+    assert err < 2 * TOL_BF16          # + half an ulp of the bf16 output itself
+
+
+def test_attention_errors(cabi):
+    st = cabi.LayerStore(2, 64, 32, 128, 64, torch.float32, "cuda")
+    q = torch.randn(2, 1, 64, device="cuda")
+    with pytest.raises(RuntimeError, match="empty"):
+        st.attention(q)
+    with pytest.raises(RuntimeError, match="no new tokens"):
+        st.update(torch.empty(2, 0, 64, device="cuda"), torch.empty(2, 0, 64, device="cuda"))
+    with pytest.raises(RuntimeError, match="overflow"):
+        st.update(torch.randn(2, 400, 64, device="cuda"), torch.randn(2, 400, 64, device="cuda"))
