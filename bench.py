@@ -1,0 +1,325 @@
+#!/usr/bin/env python
+"""Benchmark of the KIVI 2-bit decode-attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload cfg2|cfg1|cfg3|small] [--path auto|fp32|mma]
+
+One "step" = one layer-step of fused decode attention over the packed cache of
+the workload (B*Hkv units, Sq quantized + Sr residual tokens each).  At N GPUs
+every rank holds the workload's units (weak scaling: global batch = N * B) and
+the per-layer outputs are all-gathered over NCCL.  Prints ONE JSON line.
+
+metric: 2-bit KV decode-attention HBM GB/s = algorithmic bytes / time, where
+algorithmic bytes = units*[Sq*(D/2 + 16*D/G) + Sr*2*D*T] + 2*B*Hq*D*T.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, Hkv, n_rep, D, G, R, n_quant, n_res)
+    "cfg2": (64, 8, 4, 128, 32, 128, 32640, 128),    # BASELINE configs[2]: B=64, 32k context
+    "cfg1": (16, 8, 4, 128, 32, 128, 3968, 128),     # configs[1]: B=16, 4096 context
+    "cfg3": (4, 8, 4, 128, 32, 128, 131072, 128),    # configs[3]: B=4, 128k context
+    "small": (2, 8, 4, 128, 32, 128, 992, 128),
+}
+LAYERS = 32          # Llama-3-8B depth, for the tokens/s figure
+
+
+def alg_bytes(B, Hkv, n_rep, D, G, n_quant, n_res, tbytes=2):
+    return B * Hkv * (n_quant * (D // 2 + 16 * D // G) + n_res * 2 * D * tbytes) + 2 * B * Hkv * n_rep * D * tbytes
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            p = [x.strip() for x in line.split(",")]
+            if len(p) < 7:
+                continue
+            try:
+                sm.append(float(p[0])); mx.append(float(p[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, p[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_unit_tensors(B, Hkv, T, D, seed, device, dtype):
+    """Seeded synthetic K/V [B*Hkv, T, D] generated on the device: N(0,1); keys
+    with 4 outlier channels per head x10, values with 2% of tokens x8."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    U = B * Hkv
+    k = torch.empty(U, T, D, device=device, dtype=dtype)
+    v = torch.empty(U, T, D, device=device, dtype=dtype)
+    step = max(1, (1 << 28) // (T * D))
+    for u0 in range(0, U, step):
+        u1 = min(U, u0 + step)
+        kk = torch.randn(u1 - u0, T, D, device=device, generator=g)
+        ch = torch.rand(u1 - u0, D, device=device, generator=g).argsort(dim=1)[:, :4]
+        mul = torch.ones(u1 - u0, D, device=device)
+        mul.scatter_(1, ch, 10.0)
+        k[u0:u1] = (kk * mul[:, None, :]).to(dtype)
+        vv = torch.randn(u1 - u0, T, D, device=device, generator=g)
+        tokm = (torch.rand(u1 - u0, T, device=device, generator=g) < 0.02).float() * 7.0 + 1.0
+        v[u0:u1] = (vv * tokm[:, :, None]).to(dtype)
+        del kk, vv
+    return k, v
+
+
+def cpu_attention_sample(B_s, Hkv, n_rep, D, G, n_quant, n_res, iters, threads):
+    """The reference's CPU path for one decode layer-step on a slice of the
+    batch: attention over the served fp32 cache (already round-tripped history
+    || residual, cache/manager.py:263-286), plus 1/G of a flush round trip."""
+    from oracle import kivi_oracle as ko
+    torch.set_num_threads(threads)
+    T = n_quant + n_res
+    K = ko.make_keys(B_s, Hkv, T, D, seed=1).to(torch.bfloat16)
+    V = ko.make_values(B_s, Hkv, T, D, seed=1).to(torch.bfloat16)
+    q = ko.make_queries(B_s, Hkv * n_rep, D, seed=1).to(torch.bfloat16).float()
+    kf, vf = K.float(), V.float()
+    kq = ko.roundtrip_groups(kf[:, :, :n_quant].reshape(B_s, Hkv, n_quant // G, G, D).transpose(3, 4).contiguous(), G)
+    kf[:, :, :n_quant] = kq.transpose(3, 4).reshape(B_s, Hkv, n_quant, D)
+    vf[:, :, :n_quant] = ko.roundtrip_groups(vf[:, :, :n_quant].contiguous(), G)
+    chunk_k = kf[:, :, :G].transpose(2, 3).contiguous()
+    chunk_v = vf[:, :, :G].contiguous()
+    ko.attention(q.unsqueeze(2), kf, vf)
+    ts = []
+    for _ in range(iters):
+        t0 = time.perf_counter()
+        ko.attention(q.unsqueeze(2), kf, vf)
+        t1 = time.perf_counter()
+        ko.roundtrip_groups(chunk_k, G); ko.roundtrip_groups(chunk_v, G)
+        t2 = time.perf_counter()
+        ts.append((t1 - t0) + (t2 - t1) / G)
+    return statistics.median(ts)
+
+
+def run_reference(args, wl):
+    """--impl reference: the reference's CPU path (oracle port of its torch
+    mirror + attention formula) on the host cores, one bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    B, Hkv, n_rep, D, G, R, n_quant, n_res = wl
+    threads = os.cpu_count() or 1
+    B_s = 1                                   # one batch row of the workload per step
+    iters = max(1, args.steps)
+    for _ in range(max(0, args.warmup - 1)):
+        cpu_attention_sample(B_s, Hkv, n_rep, D, G, n_quant, n_res, 1, threads)
+    t = cpu_attention_sample(B_s, Hkv, n_rep, D, G, n_quant, n_res, iters, threads)
+    by = alg_bytes(B_s, Hkv, n_rep, D, G, n_quant, n_res)
+    gbs = by / t / 1e9
+    sample = f"B={B_s} of {B} batch rows (Hkv={Hkv}, {n_quant}+{n_res} tokens), scaled by bytes"
+    line = {"impl": "reference", "metric": "kivi_2bit_decode_attention_hbm_gbs", "value": gbs, "unit": "GB/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": t * 1e3 * (B / B_s), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "B": B, "Hkv": Hkv, "Hq": Hkv * n_rep, "D": D, "G": G,
+                       "n_quant": n_quant, "n_res": n_res},
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def run_ours(args, wl):
+    from intel_kivi_hybrid_b200 import cabi
+    import torch.distributed as dist
+    B, Hkv, n_rep, D, G, R, n_quant, n_res = wl
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    dtype = torch.bfloat16
+    path = {"auto": cabi.ATTN_AUTO, "fp32": cabi.ATTN_FP32, "mma": cabi.ATTN_MMA}[args.path]
+    U = B * Hkv
+    T = n_quant + n_res
+    # two layer-sized stores are rotated so no step finds its inputs in L2
+    n_buf = 2 if alg_bytes(*wl[:5], n_quant, n_res) > (1 << 29) else 8
+    stores = []
+    k, v = make_unit_tensors(B, Hkv, T, D, 1000 + rank, dev, dtype)
+    for i in range(n_buf):
+        st = cabi.LayerStore(U, D, G, R, n_quant, dtype, dev)
+        if i == 0:
+            cabi.load_state(st, k, v, n_quant)
+        else:                                  # same bytes, different addresses
+            for name in ("k_codes", "k_scales", "k_zeros", "v_codes", "v_scales", "v_zeros", "k_res", "v_res"):
+                getattr(st, name).copy_(getattr(stores[0], name))
+            st.quant_len, st.res_start, st.res_len = n_quant, 0, n_res
+        stores.append(st)
+    del k, v
+    torch.cuda.empty_cache()
+    q = torch.randn(U, n_rep, D, device=dev, generator=torch.Generator(device=dev).manual_seed(7)).to(dtype)
+    out = torch.empty_like(q)
+    gathered = torch.empty(world * U, n_rep, D, device=dev, dtype=dtype) if world > 1 else None
+
+    def step(i):
+        stores[i % n_buf].attention(q, out=out, n_rep=n_rep, path=path, num_splits=args.splits)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    launches_per_step = cabi.lib.kivi_last_launch_count()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev[0].record()
+    for i in range(args.steps):
+        step(i)
+        ev[i + 1].record()
+    barrier()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    clocks = sampler.stop() if sampler else None
+    ms_step = total_ms / args.steps
+    by = alg_bytes(B, Hkv, n_rep, D, G, n_quant, n_res)
+    value = world * by / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end: host q + host new K/V token in, host out, every step ----
+    h_q = q.cpu().pin_memory()
+    h_kv = torch.randn(2, U, 1, D).to(dtype).pin_memory()
+    h_out = torch.empty(U, n_rep, D, dtype=dtype).pin_memory()
+    d_kv = torch.empty(2, U, 1, D, device=dev, dtype=dtype)
+    e2e_store = stores[-1]
+    # start from "n_quant quantized + (R - G) in the ring" so flushes happen at the real rate (1 step in G)
+    e2e_store.quant_len, e2e_store.res_start, e2e_store.res_len = n_quant - G, 0, R - G
+    n_e2e = max(args.steps, G)
+
+    def e2e_step():
+        q.copy_(h_q, non_blocking=True)
+        d_kv.copy_(h_kv, non_blocking=True)
+        e2e_store.update(d_kv[0], d_kv[1])
+        e2e_store.attention(q, out=out, n_rep=n_rep, path=path, num_splits=args.splits)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+        h_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_store.quant_len, e2e_store.res_start, e2e_store.res_len = n_quant - G, 0, R - G
+        e2e_step()
+    e2e_store.quant_len, e2e_store.res_start, e2e_store.res_len = n_quant - G, 0, R - G
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n_e2e):
+        if e2e_store.quant_len + G > e2e_store.max_tokens and e2e_store.res_len == R - 1:
+            e2e_store.quant_len, e2e_store.res_start, e2e_store.res_len = n_quant - G, 0, R - G
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / n_e2e
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_val = world * by / (e2e_ms * 1e-3) / 1e9
+
+    if rank == 0:
+        peak, which = peaks()
+        achieved = by / (statistics.median(per) * 1e-3) / 1e9
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            threads = os.cpu_count() or 1
+            t_cpu = cpu_attention_sample(1, Hkv, n_rep, D, G, n_quant, n_res, 3, threads)
+            cpu = {"value": alg_bytes(1, Hkv, n_rep, D, G, n_quant, n_res) / t_cpu / 1e9, "unit": "GB/s",
+                   "cores": threads, "kind": "port",
+                   "sample": f"B=1 of {B} batch rows, 3 timed passes of the reference CPU path (fp32 attention over "
+                             f"the served cache + 1/G flush round trip), median"}
+        line = {"metric": "kivi_2bit_decode_attention_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": args.workload, "B_per_gpu": B, "Hkv": Hkv, "Hq": Hkv * n_rep, "D": D, "G": G,
+                           "n_quant": n_quant, "n_res": n_res, "path": args.path, "layer_buffers_rotated": n_buf,
+                           "l2": "inputs larger than L2 (layer buffers rotated)",
+                           "parallelism": f"(batch,kv_head) units x{world}, all-gather of outputs"},
+                "decode_tokens_per_s": world * B / (LAYERS * ms_step * 1e-3),
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                             "peak_source": which, "traffic": None,
+                             "note": "achieved = algorithmic bytes / median per-step CUDA-event time (attention kernel + split merge)"},
+                "cpu_baseline": cpu,
+                "e2e": {"value": e2e_val, "unit": "GB/s", "ms_per_step": e2e_ms,
+                        "h2d_bytes_per_step": h_q.numel() * 2 + h_kv.numel() * 2, "d2h_bytes_per_step": h_out.numel() * 2,
+                        "note": "host q + new K/V token -> cache update (flush every G steps) -> attention -> host out"},
+                "gpu_launches": args.steps * launches_per_step,
+                "clocks": clocks}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--path", default="auto", choices=["auto", "fp32", "mma"])
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, wl)
+    else:
+        run_ours(args, wl)
+
+
+if __name__ == "__main__":
+    main()
