@@ -196,6 +196,11 @@ int kivi_decode_attention(const kivi_layer* layer, int64_t quant_len, int res_st
                           int n_rep, float sm_scale, void* workspace, size_t workspace_bytes,
                           int num_splits, int path, void* stream);
 
+/* Reads (and synchronises with) the device fault word: non-zero once any wait
+ * inside a kernel of this library ran out (a bulk copy that never completed).
+ * Such a kernel returns normally and reports the affected split as empty. */
+int kivi_device_fault(int* word_out);
+
 /* number of kernels the last successful call on this thread launched */
 int kivi_last_launch_count(void);
 

@@ -33,6 +33,7 @@ SIGNATURES = {
     "kivi_last_error": (_c.c_char_p, []),
     "kivi_version": (_int, []),
     "kivi_last_launch_count": (_int, []),
+    "kivi_device_fault": (_int, [_c.POINTER(_int)]),
     "kivi_quantize_keys_per_channel": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _int, _int, _vp]),
     "kivi_quantize_values_per_token": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _int, _int, _int, _vp]),
     "kivi_dequantize_keys_per_channel": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _vp]),
@@ -130,6 +131,12 @@ def roundtrip_values(x, out, head_dim, group_size, rounding=ROUND_HALF_AWAY):
     _dev(x, out)
     _check(lib.kivi_quant_dequant_roundtrip_values(x.data_ptr(), _dt(x), out.data_ptr(), x.numel() // head_dim,
                                                    head_dim, group_size, rounding, _stream()))
+
+
+def device_fault() -> int:
+    w = _int()
+    _check(lib.kivi_device_fault(_c.byref(w)))
+    return w.value
 
 
 def cache_plan(quant_len, res_len, n_new, G, R):

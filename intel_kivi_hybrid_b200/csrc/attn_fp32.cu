@@ -31,10 +31,10 @@ template <int NREP, int DB>
 __global__ void __launch_bounds__(kWarps * 32)
 attn_fp32_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
                  const void* __restrict__ q, int q_dtype, float scale_log2,
-                 int nq_splits, int groups_per_split,
+                 int nq_splits, int groups_per_split, int split_base, int n_splits,
                  float* __restrict__ part_o, float* __restrict__ part_ml) {
     const int D = L.head_dim, G = L.group_size, Q = G / 4, W = D < 64 ? D : 64, ng = D / G;
-    const int u = blockIdx.y, split = blockIdx.x, n_splits = gridDim.x;
+    const int u = blockIdx.y, split = blockIdx.x + split_base;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t max_groups = L.max_tokens / G;
 
@@ -270,21 +270,38 @@ merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ 
 template <int NREP>
 static int launch_fp32(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
                        const void* q, int q_dtype, float scale_log2, int nq_splits, int gps,
-                       int n_splits, float* part_o, float* part_ml, cudaStream_t st) {
+                       int n_splits, float* part_o, float* part_ml, cudaStream_t st,
+                       int split_base = 0, int grid_x = -1) {
     const int D = L->head_dim;
     const int DB = D > 128 ? 2 : 1;
     const size_t smem = sizeof(float) * ((size_t)NREP * D + kWarps * 2 * D + kWarps * 32 * NREP +
                                          kWarps * NREP * 2 + (size_t)NREP * DB * 128);
-    dim3 grid((unsigned)n_splits, (unsigned)L->num_units);
+    dim3 grid((unsigned)(grid_x < 0 ? n_splits : grid_x), (unsigned)L->num_units);
     if (DB == 1) {
         if (smem > 48 * 1024) KIVI_CUDA_OK(cudaFuncSetAttribute(attn_fp32_kernel<NREP, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attn_fp32_kernel<NREP, 1><<<grid, kWarps * 32, smem, st>>>(*L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, gps, part_o, part_ml);
+        attn_fp32_kernel<NREP, 1><<<grid, kWarps * 32, smem, st>>>(*L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, gps, split_base, n_splits, part_o, part_ml);
     } else {
         if (smem > 48 * 1024) KIVI_CUDA_OK(cudaFuncSetAttribute(attn_fp32_kernel<NREP, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attn_fp32_kernel<NREP, 2><<<grid, kWarps * 32, smem, st>>>(*L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, gps, part_o, part_ml);
+        attn_fp32_kernel<NREP, 2><<<grid, kWarps * 32, smem, st>>>(*L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, gps, split_base, n_splits, part_o, part_ml);
     }
     KIVI_LAUNCH_OK();
     return KIVI_OK;
+}
+
+// only the residual-ring split (slot nq_splits), for callers whose quantized
+// splits run in another kernel
+int run_attn_fp32_residual(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
+                           const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits,
+                           int n_splits, float* part_o, float* part_ml, cudaStream_t st) {
+    switch (n_rep) {
+        case 1: return launch_fp32<1>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, 0, n_splits, part_o, part_ml, st, nq_splits, 1);
+        case 2: return launch_fp32<2>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, 0, n_splits, part_o, part_ml, st, nq_splits, 1);
+        case 3: return launch_fp32<3>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, 0, n_splits, part_o, part_ml, st, nq_splits, 1);
+        case 4: return launch_fp32<4>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, 0, n_splits, part_o, part_ml, st, nq_splits, 1);
+        default: break;
+    }
+    set_error("n_rep (%d) outside 1..4", n_rep);
+    return KIVI_ERR_UNSUPPORTED;
 }
 
 int run_attn_fp32(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,

@@ -1,14 +1,450 @@
-// Tensor-core decode attention (placeholder until the kernel lands).
+// Fused decode attention over the packed KIVI cache: tensor-core kernel for
+// head_dim 128, group_size 32, up to 4 query heads per KV head (sm_100a).
+//
+// Decode attention over 2-bit codes is instruction-bound before it is HBM-bound:
+// one quantized (token, kv_head) is 128 bytes of HBM but 256 codes that each
+// feed 4 query heads.  The GQA query-group tile therefore runs on the tensor
+// cores (mma.sync m16n8k16, fp32 accumulate) with the codes as the exact
+// operand, and everything that depends on scales and zeros is folded into the
+// small operand:
+//
+//   q.k   score[t,h] = sum_d (q[h,d]*s[g,d]) * c[d,t]  +  sum_d q[h,d]*z[g,d]
+//         A = codes of 16 tokens x 16 channels, encoded as bf16 (1 + c/4) by one
+//         shift and one logic op per register pair; B = q*s split into bf16
+//         hi + lo parts (the 8 columns are 4 heads x {hi, lo}), so B carries
+//         16 significant bits.  The "+1" of the encoding is removed exactly by
+//         a second MMA with an all-ones A on the same B; the zero term is an
+//         fp32 dot product per (group, head).
+//   p.v   out[h,d]   = sum_t (p[h,t]*s[t,gd]) * c[t,d]  +  sum_t p[h,t]*z[t,gd]
+//         A = codes of 16 channels x 16 tokens as fp16 (1 + c/4); B = 4*p*s in
+//         fp16 (rounding errors of independent tokens average out); the "+1" is
+//         again removed by an all-ones MMA, the zero term accumulates in fp32.
+//
+// Data movement: every warp streams its own token groups from HBM into a
+// private shared-memory ring with bulk asynchronous copies (cp.async.bulk,
+// completion on an mbarrier), two groups (8 KB) per stage, and unpacks codes in
+// registers.  Nothing dequantized is ever written anywhere.  The residual ring
+// (full precision) is one extra split handled with fp32 FMAs.
+//
+// Every wait on an mbarrier is bounded; on expiry the warp raises the device
+// fault word, stops consuming and its partial is written as "empty".
 #include "kivi_common.cuh"
 
+#include <cuda_fp16.h>
+
 namespace kivi {
+namespace {
 
-bool attn_mma_supported(const kivi_layer*, int, int) { return false; }
+constexpr int kD = 128, kG = 32;
+constexpr int kWarps = 4;              // warps per CTA, each with a private pipeline
+constexpr int kGPS = 2;                // token groups per pipeline stage
+constexpr int kStages = 3;
+constexpr int kGroupBytes = 4096;      // kc 1024 | ks 512 | kz 512 | vc 1024 | vs 512 | vz 512
+constexpr int kStageBytes = kGPS * kGroupBytes;
+constexpr uint32_t kSpinLimit = 1u << 22;
 
-int run_attn_mma(const kivi_layer*, int64_t, int, int, const void*, int, int, float, int, int, int,
-                 float*, float*, cudaStream_t) {
-    set_error("tensor-core decode attention is not built");
-    return KIVI_ERR_UNSUPPORTED;
+__device__ int g_fault_word = 0;
+
+// ---- PTX wrappers ------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false if the barrier did not complete within kSpinLimit polls
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// {lo16, hi16} = {bf16_rz(lo), bf16_rz(hi)}
+__device__ __forceinline__ uint32_t pack_bf16_rz(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rz.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_f16_rn(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+
+// ---- code -> MMA operand encodings --------------------------------------------
+// key word w: bytes = 4 consecutive channels, bit pair e of each byte = token
+// lane + 8e of the group.  Returns bf16x2 {1 + c/4 of byte 0 | byte 2} (lo) or
+// {byte 1 | byte 3} (hi) for token index e.
+template <int E> __device__ __forceinline__ uint32_t enc_k_lo(uint32_t w) {
+    const uint32_t x = (E < 3) ? (w << (5 - 2 * E)) : (w >> 1);
+    return (x & 0x00600060u) | 0x3F803F80u;
+}
+template <int E> __device__ __forceinline__ uint32_t enc_k_hi(uint32_t w) {
+    return ((w >> (3 + 2 * E)) & 0x00600060u) | 0x3F803F80u;
+}
+// value word x: byte 0 = one token, byte 2 = another; bit pair I = channel.
+// Returns f16x2 {1 + c/4, 1 + c/4}.
+template <int I> __device__ __forceinline__ uint32_t enc_v(uint32_t x) {
+    return ((x << (8 - 2 * I)) & 0x03000300u) | 0x3C003C00u;
+}
+
+struct WarpState {
+    float m, l;            // running max / sum of head `tig` (score layout)
+    float o[8][4];         // p.v accumulators, 8 channel tiles
+    float o1[4][4];        // all-ones accumulators per channel group
+    float oz[4];           // zero-point term, head gid>>1, partial over lanes
+};
+
+// One token group (32 tokens) from shared memory.
+__device__ __forceinline__ void process_group(
+    const uint8_t* __restrict__ kc, const float* __restrict__ ks, const float* __restrict__ kz,
+    const uint8_t* __restrict__ vc, const float* __restrict__ vs, const float* __restrict__ vz,
+    const float (&qreg)[32], uint32_t part_mask, float keep4, int part, int gid, int tig, int lane,
+    WarpState& st) {
+    // ---------------- q.k ----------------
+    uint32_t w[8];
+    {
+        const uint4 a = *reinterpret_cast<const uint4*>(kc + gid * 64 + tig * 16);
+        const uint4 b = *reinterpret_cast<const uint4*>(kc + 512 + gid * 64 + tig * 16);
+        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+    }
+    uint32_t bk[8][2];
+    float qz = 0.0f;
+#pragma unroll
+    for (int kt = 0; kt < 8; ++kt) {
+        const int ch = 64 * (kt >> 2) + 16 * tig + 4 * (kt & 3);
+        const float4 s4 = *reinterpret_cast<const float4*>(ks + ch);
+        const float4 z4 = *reinterpret_cast<const float4*>(kz + ch);
+        const float x0 = qreg[4 * kt + 0] * s4.x, x1 = qreg[4 * kt + 1] * s4.y;
+        const float x2 = qreg[4 * kt + 2] * s4.z, x3 = qreg[4 * kt + 3] * s4.w;
+        qz = fmaf(qreg[4 * kt + 0], z4.x, qz); qz = fmaf(qreg[4 * kt + 1], z4.y, qz);
+        qz = fmaf(qreg[4 * kt + 2], z4.z, qz); qz = fmaf(qreg[4 * kt + 3], z4.w, qz);
+        // hi lanes keep trunc_bf16(x); lo lanes keep x - trunc_bf16(x)
+        const float r0 = x0 - __uint_as_float(__float_as_uint(x0) & part_mask);
+        const float r1 = x1 - __uint_as_float(__float_as_uint(x1) & part_mask);
+        const float r2 = x2 - __uint_as_float(__float_as_uint(x2) & part_mask);
+        const float r3 = x3 - __uint_as_float(__float_as_uint(x3) & part_mask);
+        bk[kt][0] = pack_bf16_rz(r0, r2);
+        bk[kt][1] = pack_bf16_rz(r1, r3);
+    }
+    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f}, cone[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint32_t ones_bf16[4] = {0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u};
+#pragma unroll
+    for (int kt = 0; kt < 8; ++kt) {
+        uint32_t a[4];
+        a[0] = enc_k_lo<0>(w[kt]); a[1] = enc_k_lo<1>(w[kt]); a[2] = enc_k_hi<0>(w[kt]); a[3] = enc_k_hi<1>(w[kt]);
+        mma_bf16(c0, a, bk[kt][0], bk[kt][1]);
+        a[0] = enc_k_lo<2>(w[kt]); a[1] = enc_k_lo<3>(w[kt]); a[2] = enc_k_hi<2>(w[kt]); a[3] = enc_k_hi<3>(w[kt]);
+        mma_bf16(c1, a, bk[kt][0], bk[kt][1]);
+        mma_bf16(cone, ones_bf16, bk[kt][0], bk[kt][1]);
+    }
+    // zero term of head gid>>1 (lanes of one gid pair hold the same partial); the
+    // query was pre-multiplied by 4, undo that here.
+    qz += __shfl_xor_sync(0xffffffffu, qz, 1);
+    qz += __shfl_xor_sync(0xffffffffu, qz, 2);
+    const float qz_t = 0.25f * __shfl_sync(0xffffffffu, qz, 8 * tig);
+    const float base = qz_t - (cone[0] + cone[1]);
+    float s[4];
+    s[0] = c0[0] + c0[1] + base;   // token gid
+    s[1] = c0[2] + c0[3] + base;   // token gid + 8
+    s[2] = c1[0] + c1[1] + base;   // token gid + 16
+    s[3] = c1[2] + c1[3] + base;   // token gid + 24
+    float gmax = fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3]));
+    gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, 4));
+    gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, 8));
+    gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, 16));
+    if (__any_sync(0xffffffffu, gmax > st.m)) {
+        const float m_new = fmaxf(st.m, gmax);
+        const float alpha = ex2(st.m - m_new);         // 0 when st.m == -inf
+        st.m = m_new;
+        st.l *= alpha;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) st.o[mt][i] *= alpha;
+#pragma unroll
+        for (int gd = 0; gd < 4; ++gd) { st.o1[gd][0] *= alpha; st.o1[gd][1] *= alpha; }
+        const float alpha_b = __shfl_sync(0xffffffffu, alpha, (lane & ~3) | (gid >> 1));
+#pragma unroll
+        for (int gd = 0; gd < 4; ++gd) st.oz[gd] *= alpha_b;
+    }
+    float p[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { p[e] = ex2(s[e] - st.m); st.l += p[e]; }
+
+    // ---------------- p.v ----------------
+    const uint32_t ones_f16[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
+#pragma unroll
+    for (int kap = 0; kap < 2; ++kap) {
+        const int tok0 = 4 * kap + tig;                 // tokens tok0 + 8e, e = 0..3
+        const int src = 4 * tok0 + (gid >> 1);          // lane holding their p for head gid>>1
+        float pe[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) pe[e] = __shfl_sync(0xffffffffu, p[e], src);
+        float4 sv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sv[e] = *reinterpret_cast<const float4*>(vs + (tok0 + 8 * e) * 4);
+        {   // zero term: hi lanes take e = 0,1, lo lanes e = 2,3
+            const float pa = part ? pe[2] : pe[0], pb = part ? pe[3] : pe[1];
+            const int ta = tok0 + 16 * part;
+            const float4 za = *reinterpret_cast<const float4*>(vz + ta * 4);
+            const float4 zb = *reinterpret_cast<const float4*>(vz + (ta + 8) * 4);
+            st.oz[0] = fmaf(pa, za.x, fmaf(pb, zb.x, st.oz[0]));
+            st.oz[1] = fmaf(pa, za.y, fmaf(pb, zb.y, st.oz[1]));
+            st.oz[2] = fmaf(pa, za.z, fmaf(pb, zb.z, st.oz[2]));
+            st.oz[3] = fmaf(pa, za.w, fmaf(pb, zb.w, st.oz[3]));
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) pe[e] *= keep4;     // 4*p on hi lanes, 0 on lo lanes
+        const uint8_t* vrow = vc + tok0 * 32 + gid;
+#pragma unroll
+        for (int gd = 0; gd < 4; ++gd) {
+            const float s0 = gd == 0 ? sv[0].x : gd == 1 ? sv[0].y : gd == 2 ? sv[0].z : sv[0].w;
+            const float s1 = gd == 0 ? sv[1].x : gd == 1 ? sv[1].y : gd == 2 ? sv[1].z : sv[1].w;
+            const float s2 = gd == 0 ? sv[2].x : gd == 1 ? sv[2].y : gd == 2 ? sv[2].z : sv[2].w;
+            const float s3 = gd == 0 ? sv[3].x : gd == 1 ? sv[3].y : gd == 2 ? sv[3].z : sv[3].w;
+            const uint32_t b0 = pack_f16_rn(pe[0] * s0, pe[1] * s1);
+            const uint32_t b1 = pack_f16_rn(pe[2] * s2, pe[3] * s3);
+            const uint32_t x01 = (uint32_t)vrow[8 * gd] | ((uint32_t)vrow[8 * 32 + 8 * gd] << 16);
+            const uint32_t x23 = (uint32_t)vrow[16 * 32 + 8 * gd] | ((uint32_t)vrow[24 * 32 + 8 * gd] << 16);
+            uint32_t a[4];
+            a[0] = enc_v<0>(x01); a[1] = enc_v<1>(x01); a[2] = enc_v<0>(x23); a[3] = enc_v<1>(x23);
+            mma_f16(st.o[2 * gd], a, b0, b1);
+            a[0] = enc_v<2>(x01); a[1] = enc_v<3>(x01); a[2] = enc_v<2>(x23); a[3] = enc_v<3>(x23);
+            mma_f16(st.o[2 * gd + 1], a, b0, b1);
+            mma_f16(st.o1[gd], ones_f16, b0, b1);
+        }
+    }
+}
+
+// grid = (nq_splits, units); block = kWarps warps.  Split `blockIdx.x` of unit
+// `blockIdx.y` covers token groups [split*gps, min((split+1)*gps, n_groups));
+// its partial goes to slot blockIdx.x of n_splits_total.
+__global__ void __launch_bounds__(kWarps * 32, 2)
+attn_mma_kernel(kivi_layer L, int64_t quant_len, const void* __restrict__ q, int q_dtype,
+                float scale_log2, int n_rep, int gps, int n_splits_total,
+                float* __restrict__ part_o, float* __restrict__ part_ml) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t* stage_mem = smem_raw;                                               // [kWarps][kStages][kStageBytes]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + kWarps * kStages * kStageBytes);  // [kWarps][kStages]
+    float* ml_s = reinterpret_cast<float*>(bars + kWarps * kStages);             // [kWarps][4][2]
+    float* o_s = ml_s + kWarps * 4 * 2;                                          // [4][128]
+
+    const int u = blockIdx.y, split = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int part = gid & 1, hB = gid >> 1;
+    const int64_t max_groups = L.max_tokens / kG;
+    const int64_t n_groups = quant_len / kG;
+    const int64_t g_begin = (int64_t)split * gps;
+    int64_t g_end = g_begin + gps;
+    if (g_end > n_groups) g_end = n_groups;
+    const int n_chunks = (int)((g_end - g_begin + kGPS - 1) / kGPS);
+    const int my_n = n_chunks > warp ? (n_chunks - warp + kWarps - 1) / kWarps : 0;
+
+    uint8_t* wstage = stage_mem + warp * kStages * kStageBytes;
+    const uint32_t bar0 = smem_u32(bars + warp * kStages);
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+
+    const int64_t ubase_g = (int64_t)u * max_groups;
+    const int64_t ubase_t = (int64_t)u * L.max_tokens;
+    auto issue = [&](int i) {
+        const int64_t g0 = g_begin + (int64_t)(warp + kWarps * i) * kGPS;
+        const int ng = (int)((g_end - g0) < kGPS ? (g_end - g0) : kGPS);
+        const int s = i % kStages;
+        const uint32_t bar = bar0 + 8 * s;
+        const uint32_t dst = smem_u32(wstage + s * kStageBytes);
+        mbar_expect_tx(bar, (uint32_t)ng * kGroupBytes);
+        bulk_g2s(dst, L.k_codes + (ubase_g + g0) * 1024, ng * 1024, bar);
+        bulk_g2s(dst + kGPS * 1024, L.k_scales + (ubase_g + g0) * kD, ng * 512, bar);
+        bulk_g2s(dst + kGPS * 1536, L.k_zeros + (ubase_g + g0) * kD, ng * 512, bar);
+        bulk_g2s(dst + kGPS * 2048, L.v_codes + (ubase_t + g0 * kG) * 32, ng * 1024, bar);
+        bulk_g2s(dst + kGPS * 3072, L.v_scales + (ubase_t + g0 * kG) * 4, ng * 512, bar);
+        bulk_g2s(dst + kGPS * 3584, L.v_zeros + (ubase_t + g0 * kG) * 4, ng * 512, bar);
+    };
+    if (lane == 0) {
+        for (int i = 0; i < kStages && i < my_n; ++i) issue(i);
+    }
+
+    // query registers: channel 64*qh + 16*tig + 4*m + i at index 16*qh + 4*m + i,
+    // head hB, pre-multiplied by 4 * sm_scale * log2(e)
+    float qreg[32];
+    {
+        const float f = 4.0f * scale_log2;
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            const int ch = 64 * (r >> 4) + 16 * tig + (r & 15);
+            qreg[r] = hB < n_rep ? f * load_as_float(q, q_dtype, ((int64_t)u * n_rep + hB) * kD + ch) : 0.0f;
+        }
+    }
+    const uint32_t part_mask = part ? 0xffff0000u : 0u;
+    const float keep4 = part ? 0.0f : 4.0f;
+
+    WarpState st;
+    st.m = -INFINITY; st.l = 0.0f;
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) st.o[mt][i] = 0.0f;
+#pragma unroll
+    for (int gd = 0; gd < 4; ++gd) {
+        st.oz[gd] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) st.o1[gd][i] = 0.0f;
+    }
+
+    bool ok = true;
+    for (int i = 0; i < my_n; ++i) {
+        const int s = i % kStages;
+        if (!mbar_wait(bar0 + 8 * s, (uint32_t)(i / kStages) & 1u)) { ok = false; break; }
+        const int64_t g0 = g_begin + (int64_t)(warp + kWarps * i) * kGPS;
+        const int ng = (int)((g_end - g0) < kGPS ? (g_end - g0) : kGPS);
+        const uint8_t* sb = wstage + s * kStageBytes;
+        for (int gi = 0; gi < ng; ++gi) {
+            process_group(sb + gi * 1024,
+                          reinterpret_cast<const float*>(sb + kGPS * 1024 + gi * 512),
+                          reinterpret_cast<const float*>(sb + kGPS * 1536 + gi * 512),
+                          sb + kGPS * 2048 + gi * 1024,
+                          reinterpret_cast<const float*>(sb + kGPS * 3072 + gi * 512),
+                          reinterpret_cast<const float*>(sb + kGPS * 3584 + gi * 512),
+                          qreg, part_mask, keep4, part, gid, tig, lane, st);
+        }
+        __syncwarp();
+        if (lane == 0 && i + kStages < my_n) issue(i + kStages);
+    }
+    if (!ok) {
+        // copies still in flight target this CTA's shared memory: give them a
+        // bounded chance to land before the CTA may exit, then report empty.
+        if (lane == 0) atomicExch(&g_fault_word, 1);
+        for (int s = 0; s < kStages; ++s) mbar_wait(bar0 + 8 * s, 0);
+        st.m = -INFINITY; st.l = 0.0f;
+    }
+
+    // ---- fold the warp's lanes, then the CTA's warps ---------------------------
+    st.l += __shfl_xor_sync(0xffffffffu, st.l, 4);
+    st.l += __shfl_xor_sync(0xffffffffu, st.l, 8);
+    st.l += __shfl_xor_sync(0xffffffffu, st.l, 16);
+    float ozt[4];
+#pragma unroll
+    for (int gd = 0; gd < 4; ++gd) {
+        float z = st.oz[gd];
+        z += __shfl_xor_sync(0xffffffffu, z, 1);
+        z += __shfl_xor_sync(0xffffffffu, z, 2);
+        z += __shfl_xor_sync(0xffffffffu, z, 4);      // the other half of the tokens (lo lanes)
+        ozt[gd] = __shfl_sync(0xffffffffu, z, 8 * tig);   // head tig <- lanes with gid>>1 == tig
+    }
+    if (gid == 0) { ml_s[(warp * 4 + tig) * 2] = st.m; ml_s[(warp * 4 + tig) * 2 + 1] = st.l; }
+    for (int i = threadIdx.x; i < 4 * kD; i += blockDim.x) o_s[i] = 0.0f;
+    __syncthreads();
+    float M = -INFINITY;
+    for (int w2 = 0; w2 < kWarps; ++w2) M = fmaxf(M, ml_s[(w2 * 4 + tig) * 2]);
+    const float f = (st.m == -INFINITY) ? 0.0f : ex2(st.m - M);
+    for (int w2 = 0; w2 < kWarps; ++w2) {
+        if (warp == w2 && f != 0.0f) {
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) {
+                const int gd = mt >> 1;
+                const float one = st.o1[gd][0] + st.o1[gd][1];
+                const int ch = 32 * gd + 4 * gid + 2 * (mt & 1);
+                o_s[tig * kD + ch] += f * (st.o[mt][0] + st.o[mt][1] - one + ozt[gd]);
+                o_s[tig * kD + ch + 1] += f * (st.o[mt][2] + st.o[mt][3] - one + ozt[gd]);
+            }
+        }
+        __syncthreads();
+    }
+    const int64_t pbase = ((int64_t)u * n_splits_total + split) * n_rep;
+    for (int i = threadIdx.x; i < n_rep * kD; i += blockDim.x)
+        part_o[pbase * kD + i] = o_s[i];
+    if (threadIdx.x < n_rep) {
+        const int h = threadIdx.x;
+        float Mh = -INFINITY, ls = 0.0f;
+        for (int w2 = 0; w2 < kWarps; ++w2) Mh = fmaxf(Mh, ml_s[(w2 * 4 + h) * 2]);
+        for (int w2 = 0; w2 < kWarps; ++w2) {
+            const float mw = ml_s[(w2 * 4 + h) * 2];
+            if (mw != -INFINITY) ls += ml_s[(w2 * 4 + h) * 2 + 1] * ex2(mw - Mh);
+        }
+        part_ml[(pbase + h) * 2] = Mh;
+        part_ml[(pbase + h) * 2 + 1] = ls;
+    }
+}
+
+constexpr size_t kSmemBytes = (size_t)kWarps * kStages * kStageBytes + kWarps * kStages * 8 +
+                              kWarps * 4 * 2 * 4 + 4 * kD * 4;
+
+}  // namespace
+
+int run_attn_fp32_residual(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
+                           const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits,
+                           int n_splits, float* part_o, float* part_ml, cudaStream_t st);
+
+bool attn_mma_supported(const kivi_layer* L, int n_rep, int q_dtype) {
+    (void)q_dtype;
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    return L->head_dim == kD && L->group_size == kG && n_rep >= 1 && n_rep <= 4 &&
+           al(L->k_codes) && al(L->k_scales) && al(L->k_zeros) && al(L->v_codes) && al(L->v_scales) && al(L->v_zeros);
+}
+
+int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
+                 const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
+                 int n_splits, float* part_o, float* part_ml, cudaStream_t st) {
+    static thread_local bool attr_set = false;
+    if (!attr_set) {
+        KIVI_CUDA_OK(cudaFuncSetAttribute(attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        attr_set = true;
+    }
+    if (res_len > 0) {
+        if (int rc = run_attn_fp32_residual(L, quant_len, res_start, res_len, q, q_dtype, n_rep, scale_log2,
+                                            nq_splits, n_splits, part_o, part_ml, st)) return rc;
+    }
+    if (nq_splits > 0) {
+        dim3 grid((unsigned)nq_splits, (unsigned)L->num_units);
+        attn_mma_kernel<<<grid, kWarps * 32, kSmemBytes, st>>>(*L, quant_len, q, q_dtype, scale_log2, n_rep, gps,
+                                                             n_splits, part_o, part_ml);
+        KIVI_LAUNCH_OK();
+    }
+    return KIVI_OK;
+}
+
+int attn_mma_fault_word(int* out) {
+    KIVI_CUDA_OK(cudaMemcpyFromSymbol(out, g_fault_word, sizeof(int)));
+    return KIVI_OK;
 }
 
 }  // namespace kivi

@@ -48,6 +48,7 @@ bool attn_mma_supported(const kivi_layer* L, int n_rep, int q_dtype);
 int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
                  const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
                  int n_splits, float* part_o, float* part_ml, cudaStream_t st);
+int attn_mma_fault_word(int* out);
 __global__ void merge_splits_kernel(const float* part_o, const float* part_ml, void* out,
                                     int out_dtype, int n_splits, int D);
 
@@ -58,6 +59,10 @@ using namespace kivi;
 extern "C" const char* kivi_last_error(void) { return g_err; }
 extern "C" int kivi_version(void) { return 100; }
 extern "C" int kivi_last_launch_count(void) { return g_launches; }
+extern "C" int kivi_device_fault(int* word_out) {
+    KIVI_REQUIRE(word_out != nullptr, "word_out is null");
+    return attn_mma_fault_word(word_out);
+}
 
 static int check_values_args(int64_t num_tokens, int head_dim, int group_size) {
     KIVI_REQUIRE(group_size > 0 && group_size % 4 == 0, "group_size must be positive and divisible by 4");
@@ -183,6 +188,6 @@ extern "C" int kivi_decode_attention(const kivi_layer* L, int64_t quant_len, int
     dim3 grid((unsigned)L->num_units, (unsigned)n_rep);
     merge_splits_kernel<<<grid, D >= 256 ? 256 : 128, n_splits * sizeof(float), st>>>(part_o, part_ml, out, out_dtype, n_splits, D);
     KIVI_LAUNCH_OK();
-    note_launches(2);
+    note_launches(1 + (use_mma ? (nq_splits > 0) + (res_len > 0) : 1));
     return KIVI_OK;
 }

@@ -185,3 +185,47 @@ def test_attention_errors(cabi):
         st.update(torch.empty(2, 0, 64, device="cuda"), torch.empty(2, 0, 64, device="cuda"))
     with pytest.raises(RuntimeError, match="overflow"):
         st.update(torch.randn(2, 400, 64, device="cuda"), torch.randn(2, 400, 64, device="cuda"))
+
+
+# ---- tensor-core kernel ------------------------------------------------------
+
+@pytest.mark.parametrize("n_quant,n_res,n_rep,splits", [
+    (3968, 128, 4, 0), (32, 0, 4, 0), (64, 5, 4, 1), (96, 128, 4, 3), (2048 + 32, 100, 4, 5),
+    (992, 128, 1, 0), (992, 128, 2, 2), (992, 128, 3, 0), (13 * 32, 96, 4, 13)])
+def test_attention_mma_bf16(cabi, n_quant, n_res, n_rep, splits):
+    err, _, _, _ = _attention_case(cabi, 2, 4, n_rep, 128, 32, 128, n_quant, n_res, torch.bfloat16, 17,
+                                   cabi.ATTN_MMA, num_splits=splits)
+    print(f"[attn mma bf16 q={n_quant} r={n_res} rep={n_rep} splits={splits}] rel err {err:.2e}")
+    assert err < TOL_BF16
+    assert cabi.device_fault() == 0
+
+
+def test_attention_mma_matches_fp32_kernel_and_auto_dispatch(cabi):
+    e_mma, _, o_mma, _ = _attention_case(cabi, 2, 8, 4, 128, 32, 128, 3968, 128, torch.bfloat16, 13, cabi.ATTN_MMA)
+    e_auto, _, o_auto, _ = _attention_case(cabi, 2, 8, 4, 128, 32, 128, 3968, 128, torch.bfloat16, 13, cabi.ATTN_AUTO)
+    e_f32, _, o_f32, _ = _attention_case(cabi, 2, 8, 4, 128, 32, 128, 3968, 128, torch.bfloat16, 13, cabi.ATTN_FP32)
+    assert torch.equal(o_mma, o_auto)                 # bf16 queries dispatch to the tensor-core kernel
+    print(f"[attn cfg1 slice] mma {e_mma:.2e}  fp32 kernel {e_f32:.2e}  mma vs fp32 kernel {rel_err(o_mma, o_f32):.2e}")
+    assert e_mma < TOL_BF16 and rel_err(o_mma, o_f32) < TOL_BF16
+
+
+def test_attention_mma_fp32_queries_and_bf16_output(cabi):
+    err, _, _, _ = _attention_case(cabi, 1, 4, 4, 128, 32, 128, 1024, 64, torch.float32, 23, cabi.ATTN_MMA)
+    print(f"[attn mma fp32 activations] rel err {err:.2e}")
+    assert err < TOL_BF16
+    err, _, _, _ = _attention_case(cabi, 1, 4, 4, 128, 32, 128, 1024, 64, torch.bfloat16, 23, cabi.ATTN_MMA,
+                                   out_dtype=torch.bfloat16)
+    assert err < 2 * TOL_BF16
+
+
+def test_attention_mma_is_deterministic(cabi):
+    _, _, a, _ = _attention_case(cabi, 2, 4, 4, 128, 32, 128, 2048, 128, torch.bfloat16, 3, cabi.ATTN_MMA)
+    _, _, b, _ = _attention_case(cabi, 2, 4, 4, 128, 32, 128, 2048, 128, torch.bfloat16, 3, cabi.ATTN_MMA)
+    assert torch.equal(a, b)
+
+
+def test_attention_mma_rejects_other_shapes(cabi):
+    st = cabi.LayerStore(2, 64, 32, 128, 64, torch.float32, "cuda")
+    cabi.load_state(st, torch.randn(2, 64, 64, device="cuda"), torch.randn(2, 64, 64, device="cuda"), 64)
+    with pytest.raises(RuntimeError, match="tensor-core path"):
+        st.attention(torch.randn(2, 1, 64, device="cuda"), path=cabi.ATTN_MMA)
