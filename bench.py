@@ -31,6 +31,7 @@ WORKLOADS = {
     "cfg1": (16, 8, 4, 128, 32, 128, 3968, 128),     # configs[1]: B=16, 4096 context
     "cfg3": (4, 8, 4, 128, 32, 128, 131072, 128),    # configs[3]: B=4, 128k context
     "small": (2, 8, 4, 128, 32, 128, 992, 128),
+    "long": (2, 8, 4, 128, 32, 128, 65536, 128),     # few units, long history: profiling case
 }
 LAYERS = 32          # Llama-3-8B depth, for the tokens/s figure
 

@@ -53,7 +53,7 @@ SIGNATURES = {
 
 
 def _load():
-    path = _build.LIB
+    path = os.environ.get("KIVI_CUDA_LIB") or _build.LIB      # override: a library built elsewhere
     if not os.path.exists(path):
         try:
             _build.build_cuda_lib()

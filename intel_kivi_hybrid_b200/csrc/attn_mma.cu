@@ -9,16 +9,16 @@
 // small operand:
 //
 //   q.k   score[t,h] = sum_d (q[h,d]*s[g,d]) * c[d,t]  +  sum_d q[h,d]*z[g,d]
-//         A = codes of 16 tokens x 16 channels, encoded as bf16 (1 + c/4) by one
-//         shift and one logic op per register pair; B = q*s split into bf16
-//         hi + lo parts (the 8 columns are 4 heads x {hi, lo}), so B carries
-//         16 significant bits.  The "+1" of the encoding is removed exactly by
-//         a second MMA with an all-ones A on the same B; the zero term is an
+//         A = codes of 16 tokens x 16 channels; a code is used where it lies in
+//         its byte, as the fp16 subnormal c*4^e*2^-24 (one AND per register
+//         pair, no shift); B = q*s split into fp16 hi + lo parts (the 8 columns
+//         are 4 heads x {hi, lo}), 22 significant bits; the zero term is an
 //         fp32 dot product per (group, head).
 //   p.v   out[h,d]   = sum_t (p[h,t]*s[t,gd]) * c[t,d]  +  sum_t p[h,t]*z[t,gd]
-//         A = codes of 16 channels x 16 tokens as fp16 (1 + c/4); B = 4*p*s in
-//         fp16 (rounding errors of independent tokens average out); the "+1" is
-//         again removed by an all-ones MMA, the zero term accumulates in fp32.
+//         A = codes of 16 channels x 16 tokens, same encoding; B = p*s in fp16
+//         (rounding errors of independent tokens average out); the zero term
+//         accumulates in fp32.
+//   Requires |q*s*sm_scale*log2(e)| and p*s below 65504 (fp16 range).
 //
 // Data movement: every warp streams its own token groups from HBM into a
 // private shared-memory ring with bulk asynchronous copies (cp.async.bulk,
@@ -36,9 +36,21 @@ namespace kivi {
 namespace {
 
 constexpr int kD = 128, kG = 32;
-constexpr int kWarps = 4;              // warps per CTA, each with a private pipeline
-constexpr int kGPS = 2;                // token groups per pipeline stage
-constexpr int kStages = 3;
+#ifndef KIVI_MMA_WARPS
+#define KIVI_MMA_WARPS 4
+#endif
+#ifndef KIVI_MMA_GPS
+#define KIVI_MMA_GPS 2
+#endif
+#ifndef KIVI_MMA_STAGES
+#define KIVI_MMA_STAGES 2
+#endif
+#ifndef KIVI_MMA_MIN_CTAS
+#define KIVI_MMA_MIN_CTAS 3
+#endif
+constexpr int kWarps = KIVI_MMA_WARPS;     // warps per CTA, each with a private pipeline
+constexpr int kGPS = KIVI_MMA_GPS;         // token groups per pipeline stage
+constexpr int kStages = KIVI_MMA_STAGES;
 constexpr int kGroupBytes = 4096;      // kc 1024 | ks 512 | kz 512 | vc 1024 | vs 512 | vz 512
 constexpr int kStageBytes = kGPS * kGroupBytes;
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -74,20 +86,15 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
 __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// {lo16, hi16} = {bf16_rz(lo), bf16_rz(hi)}
-__device__ __forceinline__ uint32_t pack_bf16_rz(float lo, float hi) {
+// {lo16, hi16} = {f16(lo), f16(hi)}
+__device__ __forceinline__ uint32_t pack_f16_rz(float lo, float hi) {
     uint32_t r;
-    asm("cvt.rz.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
 __device__ __forceinline__ uint32_t pack_f16_rn(float lo, float hi) {
@@ -102,27 +109,24 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 
-// ---- code -> MMA operand encodings --------------------------------------------
-// key word w: bytes = 4 consecutive channels, bit pair e of each byte = token
-// lane + 8e of the group.  Returns bf16x2 {1 + c/4 of byte 0 | byte 2} (lo) or
-// {byte 1 | byte 3} (hi) for token index e.
-template <int E> __device__ __forceinline__ uint32_t enc_k_lo(uint32_t w) {
-    const uint32_t x = (E < 3) ? (w << (5 - 2 * E)) : (w >> 1);
-    return (x & 0x00600060u) | 0x3F803F80u;
+// ---- code -> MMA operand encoding ----------------------------------------------
+// A 2-bit code c sitting at bits 2e..2e+1 of the low byte of a 16-bit half is,
+// read as an fp16 bit pattern with a zero exponent field, the subnormal number
+// c * 4^e * 2^-24 -- exactly.  So one AND per register pair turns packed codes
+// into a tensor-core operand: no shift, no offset.  The factor 4^e * 2^-24
+// belongs to a whole accumulator row and is undone (exactly, a power of two)
+// when the accumulator is read.
+template <int E> __device__ __forceinline__ uint32_t code_pair(uint32_t w) {
+    return w & (0x00030003u << (2 * E));
 }
-template <int E> __device__ __forceinline__ uint32_t enc_k_hi(uint32_t w) {
-    return ((w >> (3 + 2 * E)) & 0x00600060u) | 0x3F803F80u;
-}
-// value word x: byte 0 = one token, byte 2 = another; bit pair I = channel.
-// Returns f16x2 {1 + c/4, 1 + c/4}.
-template <int I> __device__ __forceinline__ uint32_t enc_v(uint32_t x) {
-    return ((x << (8 - 2 * I)) & 0x03000300u) | 0x3C003C00u;
-}
+constexpr float kRow0 = 16777216.0f;          // 2^24 * 4^-0
+constexpr float kRow1 = 4194304.0f;           // 2^24 * 4^-1
+constexpr float kRow2 = 1048576.0f;           // 2^24 * 4^-2
+constexpr float kRow3 = 262144.0f;            // 2^24 * 4^-3
 
 struct WarpState {
     float m, l;            // running max / sum of head `tig` (score layout)
-    float o[8][4];         // p.v accumulators, 8 channel tiles
-    float o1[4][4];        // all-ones accumulators per channel group
+    float o[8][4];         // p.v accumulators, 8 channel tiles (rows still carry 4^I * 2^-24)
     float oz[4];           // zero-point term, head gid>>1, partial over lanes
 };
 
@@ -130,7 +134,7 @@ struct WarpState {
 __device__ __forceinline__ void process_group(
     const uint8_t* __restrict__ kc, const float* __restrict__ ks, const float* __restrict__ kz,
     const uint8_t* __restrict__ vc, const float* __restrict__ vs, const float* __restrict__ vz,
-    const float (&qreg)[32], uint32_t part_mask, float keep4, int part, int gid, int tig, int lane,
+    const float (&qreg)[32], uint32_t part_mask, float keep, int part, int gid, int tig, int lane,
     WarpState& st) {
     // ---------------- q.k ----------------
     uint32_t w[8];
@@ -139,7 +143,7 @@ __device__ __forceinline__ void process_group(
         const uint4 b = *reinterpret_cast<const uint4*>(kc + 512 + gid * 64 + tig * 16);
         w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
     }
-    uint32_t bk[8][2];
+    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
     float qz = 0.0f;
 #pragma unroll
     for (int kt = 0; kt < 8; ++kt) {
@@ -150,36 +154,30 @@ __device__ __forceinline__ void process_group(
         const float x2 = qreg[4 * kt + 2] * s4.z, x3 = qreg[4 * kt + 3] * s4.w;
         qz = fmaf(qreg[4 * kt + 0], z4.x, qz); qz = fmaf(qreg[4 * kt + 1], z4.y, qz);
         qz = fmaf(qreg[4 * kt + 2], z4.z, qz); qz = fmaf(qreg[4 * kt + 3], z4.w, qz);
-        // hi lanes keep trunc_bf16(x); lo lanes keep x - trunc_bf16(x)
+        // fp16 hi/lo split of q*s: hi lanes keep x truncated to 11 significant
+        // bits, lo lanes keep the remainder (part_mask = 0 on hi lanes)
         const float r0 = x0 - __uint_as_float(__float_as_uint(x0) & part_mask);
         const float r1 = x1 - __uint_as_float(__float_as_uint(x1) & part_mask);
         const float r2 = x2 - __uint_as_float(__float_as_uint(x2) & part_mask);
         const float r3 = x3 - __uint_as_float(__float_as_uint(x3) & part_mask);
-        bk[kt][0] = pack_bf16_rz(r0, r2);
-        bk[kt][1] = pack_bf16_rz(r1, r3);
-    }
-    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f}, cone[4] = {0.f, 0.f, 0.f, 0.f};
-    const uint32_t ones_bf16[4] = {0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u};
-#pragma unroll
-    for (int kt = 0; kt < 8; ++kt) {
+        const uint32_t b0 = pack_f16_rz(r0, r2);
+        const uint32_t b1 = pack_f16_rz(r1, r3);
+        const uint32_t we = w[kt], wo = w[kt] >> 8;
         uint32_t a[4];
-        a[0] = enc_k_lo<0>(w[kt]); a[1] = enc_k_lo<1>(w[kt]); a[2] = enc_k_hi<0>(w[kt]); a[3] = enc_k_hi<1>(w[kt]);
-        mma_bf16(c0, a, bk[kt][0], bk[kt][1]);
-        a[0] = enc_k_lo<2>(w[kt]); a[1] = enc_k_lo<3>(w[kt]); a[2] = enc_k_hi<2>(w[kt]); a[3] = enc_k_hi<3>(w[kt]);
-        mma_bf16(c1, a, bk[kt][0], bk[kt][1]);
-        mma_bf16(cone, ones_bf16, bk[kt][0], bk[kt][1]);
+        a[0] = code_pair<0>(we); a[1] = code_pair<1>(we); a[2] = code_pair<0>(wo); a[3] = code_pair<1>(wo);
+        mma_f16(c0, a, b0, b1);
+        a[0] = code_pair<2>(we); a[1] = code_pair<3>(we); a[2] = code_pair<2>(wo); a[3] = code_pair<3>(wo);
+        mma_f16(c1, a, b0, b1);
     }
-    // zero term of head gid>>1 (lanes of one gid pair hold the same partial); the
-    // query was pre-multiplied by 4, undo that here.
+    // zero term of head gid>>1 (both lanes of a gid pair hold the same partial)
     qz += __shfl_xor_sync(0xffffffffu, qz, 1);
     qz += __shfl_xor_sync(0xffffffffu, qz, 2);
-    const float qz_t = 0.25f * __shfl_sync(0xffffffffu, qz, 8 * tig);
-    const float base = qz_t - (cone[0] + cone[1]);
+    const float qz_t = __shfl_sync(0xffffffffu, qz, 8 * tig);
     float s[4];
-    s[0] = c0[0] + c0[1] + base;   // token gid
-    s[1] = c0[2] + c0[3] + base;   // token gid + 8
-    s[2] = c1[0] + c1[1] + base;   // token gid + 16
-    s[3] = c1[2] + c1[3] + base;   // token gid + 24
+    s[0] = fmaf(c0[0] + c0[1], kRow0, qz_t);   // token gid
+    s[1] = fmaf(c0[2] + c0[3], kRow1, qz_t);   // token gid + 8
+    s[2] = fmaf(c1[0] + c1[1], kRow2, qz_t);   // token gid + 16
+    s[3] = fmaf(c1[2] + c1[3], kRow3, qz_t);   // token gid + 24
     float gmax = fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3]));
     gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, 4));
     gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, 8));
@@ -193,8 +191,6 @@ __device__ __forceinline__ void process_group(
         for (int mt = 0; mt < 8; ++mt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) st.o[mt][i] *= alpha;
-#pragma unroll
-        for (int gd = 0; gd < 4; ++gd) { st.o1[gd][0] *= alpha; st.o1[gd][1] *= alpha; }
         const float alpha_b = __shfl_sync(0xffffffffu, alpha, (lane & ~3) | (gid >> 1));
 #pragma unroll
         for (int gd = 0; gd < 4; ++gd) st.oz[gd] *= alpha_b;
@@ -204,7 +200,6 @@ __device__ __forceinline__ void process_group(
     for (int e = 0; e < 4; ++e) { p[e] = ex2(s[e] - st.m); st.l += p[e]; }
 
     // ---------------- p.v ----------------
-    const uint32_t ones_f16[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
 #pragma unroll
     for (int kap = 0; kap < 2; ++kap) {
         const int tok0 = 4 * kap + tig;                 // tokens tok0 + 8e, e = 0..3
@@ -226,7 +221,7 @@ __device__ __forceinline__ void process_group(
             st.oz[3] = fmaf(pa, za.w, fmaf(pb, zb.w, st.oz[3]));
         }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) pe[e] *= keep4;     // 4*p on hi lanes, 0 on lo lanes
+        for (int e = 0; e < 4; ++e) pe[e] *= keep;      // p on hi lanes, 0 on lo lanes
         const uint8_t* vrow = vc + tok0 * 32 + gid;
 #pragma unroll
         for (int gd = 0; gd < 4; ++gd) {
@@ -239,11 +234,10 @@ __device__ __forceinline__ void process_group(
             const uint32_t x01 = (uint32_t)vrow[8 * gd] | ((uint32_t)vrow[8 * 32 + 8 * gd] << 16);
             const uint32_t x23 = (uint32_t)vrow[16 * 32 + 8 * gd] | ((uint32_t)vrow[24 * 32 + 8 * gd] << 16);
             uint32_t a[4];
-            a[0] = enc_v<0>(x01); a[1] = enc_v<1>(x01); a[2] = enc_v<0>(x23); a[3] = enc_v<1>(x23);
+            a[0] = code_pair<0>(x01); a[1] = code_pair<1>(x01); a[2] = code_pair<0>(x23); a[3] = code_pair<1>(x23);
             mma_f16(st.o[2 * gd], a, b0, b1);
-            a[0] = enc_v<2>(x01); a[1] = enc_v<3>(x01); a[2] = enc_v<2>(x23); a[3] = enc_v<3>(x23);
+            a[0] = code_pair<2>(x01); a[1] = code_pair<3>(x01); a[2] = code_pair<2>(x23); a[3] = code_pair<3>(x23);
             mma_f16(st.o[2 * gd + 1], a, b0, b1);
-            mma_f16(st.o1[gd], ones_f16, b0, b1);
         }
     }
 }
@@ -251,7 +245,7 @@ __device__ __forceinline__ void process_group(
 // grid = (nq_splits, units); block = kWarps warps.  Split `blockIdx.x` of unit
 // `blockIdx.y` covers token groups [split*gps, min((split+1)*gps, n_groups));
 // its partial goes to slot blockIdx.x of n_splits_total.
-__global__ void __launch_bounds__(kWarps * 32, 2)
+__global__ void __launch_bounds__(kWarps * 32, KIVI_MMA_MIN_CTAS)
 attn_mma_kernel(kivi_layer L, int64_t quant_len, const void* __restrict__ q, int q_dtype,
                 float scale_log2, int n_rep, int gps, int n_splits_total,
                 float* __restrict__ part_o, float* __restrict__ part_ml) {
@@ -304,18 +298,18 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, const void* __restrict__ q, int
     }
 
     // query registers: channel 64*qh + 16*tig + 4*m + i at index 16*qh + 4*m + i,
-    // head hB, pre-multiplied by 4 * sm_scale * log2(e)
+    // head hB, pre-multiplied by sm_scale * log2(e)
     float qreg[32];
     {
-        const float f = 4.0f * scale_log2;
+        const float f = scale_log2;
 #pragma unroll
         for (int r = 0; r < 32; ++r) {
             const int ch = 64 * (r >> 4) + 16 * tig + (r & 15);
             qreg[r] = hB < n_rep ? f * load_as_float(q, q_dtype, ((int64_t)u * n_rep + hB) * kD + ch) : 0.0f;
         }
     }
-    const uint32_t part_mask = part ? 0xffff0000u : 0u;
-    const float keep4 = part ? 0.0f : 4.0f;
+    const uint32_t part_mask = part ? 0xffffe000u : 0u;   // keep 11 significant bits
+    const float keep = part ? 0.0f : 1.0f;
 
     WarpState st;
     st.m = -INFINITY; st.l = 0.0f;
@@ -326,8 +320,6 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, const void* __restrict__ q, int
 #pragma unroll
     for (int gd = 0; gd < 4; ++gd) {
         st.oz[gd] = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) st.o1[gd][i] = 0.0f;
     }
 
     bool ok = true;
@@ -344,7 +336,7 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, const void* __restrict__ q, int
                           sb + kGPS * 2048 + gi * 1024,
                           reinterpret_cast<const float*>(sb + kGPS * 3072 + gi * 512),
                           reinterpret_cast<const float*>(sb + kGPS * 3584 + gi * 512),
-                          qreg, part_mask, keep4, part, gid, tig, lane, st);
+                          qreg, part_mask, keep, part, gid, tig, lane, st);
         }
         __syncwarp();
         if (lane == 0 && i + kStages < my_n) issue(i + kStages);
@@ -381,10 +373,11 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, const void* __restrict__ q, int
 #pragma unroll
             for (int mt = 0; mt < 8; ++mt) {
                 const int gd = mt >> 1;
-                const float one = st.o1[gd][0] + st.o1[gd][1];
                 const int ch = 32 * gd + 4 * gid + 2 * (mt & 1);
-                o_s[tig * kD + ch] += f * (st.o[mt][0] + st.o[mt][1] - one + ozt[gd]);
-                o_s[tig * kD + ch + 1] += f * (st.o[mt][2] + st.o[mt][3] - one + ozt[gd]);
+                // rows gid / gid+8 hold code index 2*(mt&1) / 2*(mt&1)+1 of their byte
+                const float r0 = (mt & 1) ? kRow2 : kRow0, r1 = (mt & 1) ? kRow3 : kRow1;
+                o_s[tig * kD + ch] += f * fmaf(st.o[mt][0] + st.o[mt][1], r0, ozt[gd]);
+                o_s[tig * kD + ch + 1] += f * fmaf(st.o[mt][2] + st.o[mt][3], r1, ozt[gd]);
             }
         }
         __syncthreads();
