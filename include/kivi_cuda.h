@@ -98,9 +98,10 @@ int kivi_quant_dequant_roundtrip_values(const void* input, int in_dtype, float* 
  *
  * Quantized store of one unit, token group g (tokens g*G .. g*G+G-1):
  *   k_codes  + (u*max_groups + g) * (D*G/4): one key block.  With Q = G/4 and
- *            W = min(D,64), the byte at  (d/W)*Q*W + j*W + d%W  (0<=j<Q) holds
+ *            W = min(D,64), the byte at  (d/W)*Q*W + j*W + p(d%W)  (0<=j<Q) holds
  *            the codes of channel d for tokens j, j+Q, j+2Q, j+3Q of the group
- *            in bits 0-1, 2-3, 4-5, 6-7.
+ *            in bits 0-1, 2-3, 4-5, 6-7; p is the identity for W < 64 and for
+ *            W = 64 swaps bits 2-3 with bits 4-5 of its argument.
  *   k_scales, k_zeros + (u*max_groups + g) * D : fp32 per channel of the group
  *            (one per-channel group of the reference, quantize_kernels.hpp:36-42).
  *   v_codes  + (u*max_tokens + t) * (D/4): the reference's value layout, byte b

@@ -288,22 +288,6 @@ static int launch_fp32(const kivi_layer* L, int64_t quant_len, int res_start, in
     return KIVI_OK;
 }
 
-// only the residual-ring split (slot nq_splits), for callers whose quantized
-// splits run in another kernel
-int run_attn_fp32_residual(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
-                           const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits,
-                           int n_splits, float* part_o, float* part_ml, cudaStream_t st) {
-    switch (n_rep) {
-        case 1: return launch_fp32<1>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, 0, n_splits, part_o, part_ml, st, nq_splits, 1);
-        case 2: return launch_fp32<2>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, 0, n_splits, part_o, part_ml, st, nq_splits, 1);
-        case 3: return launch_fp32<3>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, 0, n_splits, part_o, part_ml, st, nq_splits, 1);
-        case 4: return launch_fp32<4>(L, quant_len, res_start, res_len, q, q_dtype, scale_log2, nq_splits, 0, n_splits, part_o, part_ml, st, nq_splits, 1);
-        default: break;
-    }
-    set_error("n_rep (%d) outside 1..4", n_rep);
-    return KIVI_ERR_UNSUPPORTED;
-}
-
 int run_attn_fp32(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
                   const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
                   int n_splits, float* part_o, float* part_ml, cudaStream_t st) {

@@ -147,7 +147,7 @@ __device__ __forceinline__ void process_group(
     float qz = 0.0f;
 #pragma unroll
     for (int kt = 0; kt < 8; ++kt) {
-        const int ch = 64 * (kt >> 2) + 16 * tig + 4 * (kt & 3);
+        const int ch = 64 * (kt >> 2) + 16 * (kt & 3) + 4 * tig;
         const float4 s4 = *reinterpret_cast<const float4*>(ks + ch);
         const float4 z4 = *reinterpret_cast<const float4*>(kz + ch);
         const float x0 = qreg[4 * kt + 0] * s4.x, x1 = qreg[4 * kt + 1] * s4.y;
@@ -242,12 +242,143 @@ __device__ __forceinline__ void process_group(
     }
 }
 
-// grid = (nq_splits, units); block = kWarps warps.  Split `blockIdx.x` of unit
-// `blockIdx.y` covers token groups [split*gps, min((split+1)*gps, n_groups));
-// its partial goes to slot blockIdx.x of n_splits_total.
+// ---- residual ring: full-precision tokens ---------------------------------------
+// CTA `rs` of the residual part handles window tokens [rs*chunk, (rs+1)*chunk).
+// A warp takes 32 tokens at a time: lane = (4 tokens, quarter of the channels)
+// for q.k (vector loads of 32 channels, 2 shuffles to finish the dot products),
+// then lane = 4 channels for p.v.  Result: per warp (m, l, o) for 4 heads, merged
+// through shared memory like the quantized splits.
+template <typename T> struct RowVec;
+template <> struct RowVec<float> {
+    __device__ static void load8(const float* p, float (&v)[8]) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    __device__ static void load4(const float* p, float (&v)[4]) {
+        const float4 a = *reinterpret_cast<const float4*>(p);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    }
+};
+template <> struct RowVec<__nv_bfloat16> {
+    __device__ static void load8(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+    }
+    __device__ static void load4(const __nv_bfloat16* p, float (&v)[4]) {
+        const uint2 t = *reinterpret_cast<const uint2*>(p);
+        v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+        v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+    }
+};
+
+template <typename T>
+__device__ __forceinline__ void residual_part(
+    const T* __restrict__ k_res, const T* __restrict__ v_res, int R, int res_start, int res_len,
+    int t_begin, int t_end, const float* __restrict__ q_s /* [4][128], pre-scaled */,
+    int lane, int warp, float (&m)[4], float (&l)[4], float (&o)[4][4]) {
+    const int tl = lane >> 2, cq = lane & 3;
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+        m[h] = -INFINITY; l[h] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[h][i] = 0.0f;
+    }
+    // a warp pass covers 32 tokens: lane (tl, cq) holds tokens t0 + tl + 8j, j = 0..3,
+    // and channels 32*cq .. 32*cq+31 of each; every q vector read feeds 4 tokens
+    for (int t0 = t_begin + 32 * warp; t0 < t_end; t0 += 32 * kWarps) {
+        float acc[4][4];
+        const T* row[4];
+        bool valid[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int t = t0 + tl + 8 * j;
+            valid[j] = t < t_end;
+            const int slot = (res_start + (valid[j] ? t : t0)) % R;
+            row[j] = k_res + (int64_t)slot * kD + 32 * cq;
+#pragma unroll
+            for (int h = 0; h < 4; ++h) acc[j][h] = 0.0f;
+        }
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            float kv[4][8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) RowVec<T>::load8(row[j] + 8 * c, kv[j]);
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                const float4 qa = *reinterpret_cast<const float4*>(q_s + h * kD + 32 * cq + 8 * c);
+                const float4 qb = *reinterpret_cast<const float4*>(q_s + h * kD + 32 * cq + 8 * c + 4);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float a = acc[j][h];
+                    a = fmaf(kv[j][0], qa.x, a); a = fmaf(kv[j][1], qa.y, a);
+                    a = fmaf(kv[j][2], qa.z, a); a = fmaf(kv[j][3], qa.w, a);
+                    a = fmaf(kv[j][4], qb.x, a); a = fmaf(kv[j][5], qb.y, a);
+                    a = fmaf(kv[j][6], qb.z, a); a = fmaf(kv[j][7], qb.w, a);
+                    acc[j][h] = a;
+                }
+            }
+        }
+        float p[4][4];     // [j][h]
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float sc = acc[j][h];
+                sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+                sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+                acc[j][h] = valid[j] ? sc : -INFINITY;
+                mx = fmaxf(mx, acc[j][h]);
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m[h], mx);          // finite: token t0 is always valid
+            const float alpha = ex2(m[h] - m_new);
+            m[h] = m_new;
+            float ps = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { p[j][h] = valid[j] ? ex2(acc[j][h] - m_new) : 0.0f; ps += p[j][h]; }
+            // the four lanes of a token quad hold the same p: count it once
+            l[h] = l[h] * alpha + (cq == 0 ? ps : 0.0f);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[h][i] *= alpha;
+        }
+        const int ntok = t_end - t0 < 32 ? t_end - t0 : 32;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            for (int tk = 0; tk < 8; ++tk) {
+                if (8 * j + tk >= ntok) break;
+                const int slot = (res_start + t0 + 8 * j + tk) % R;
+                float vv[4];
+                RowVec<T>::load4(v_res + (int64_t)slot * kD + 4 * lane, vv);
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    const float ph = __shfl_sync(0xffffffffu, p[j][h], 4 * tk);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o[h][i] = fmaf(ph, vv[i], o[h][i]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) l[h] += __shfl_xor_sync(0xffffffffu, l[h], off);
+    }
+}
+
+// grid = (n_res_splits + nq_splits, units); block = kWarps warps.  The first
+// n_res_splits CTAs of a unit take the residual ring (they are scheduled first
+// and overlap with the rest); CTA n_res_splits + i covers token groups
+// [i*gps, min((i+1)*gps, n_groups)).  Partial slots: quantized split i -> i,
+// residual part r -> nq_splits + r.
 __global__ void __launch_bounds__(kWarps * 32, KIVI_MMA_MIN_CTAS)
-attn_mma_kernel(kivi_layer L, int64_t quant_len, const void* __restrict__ q, int q_dtype,
-                float scale_log2, int n_rep, int gps, int n_splits_total,
+attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
+                const void* __restrict__ q, int q_dtype,
+                float scale_log2, int n_rep, int gps, int nq_splits, int n_res_splits, int res_chunk,
                 float* __restrict__ part_o, float* __restrict__ part_ml) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* stage_mem = smem_raw;                                               // [kWarps][kStages][kStageBytes]
@@ -255,9 +386,70 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, const void* __restrict__ q, int
     float* ml_s = reinterpret_cast<float*>(bars + kWarps * kStages);             // [kWarps][4][2]
     float* o_s = ml_s + kWarps * 4 * 2;                                          // [4][128]
 
-    const int u = blockIdx.y, split = blockIdx.x;
+    const int u = blockIdx.y;
+    const int n_splits_total = nq_splits + n_res_splits;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int gid = lane >> 2, tig = lane & 3;
+
+    if ((int)blockIdx.x < n_res_splits) {
+        // ---------------- residual ring ----------------
+        const int rs = blockIdx.x;
+        float* q_s = reinterpret_cast<float*>(stage_mem);            // [4][128]
+        for (int i = threadIdx.x; i < 4 * kD; i += blockDim.x) {
+            const int h = i / kD;
+            q_s[i] = h < n_rep ? scale_log2 * load_as_float(q, q_dtype, (int64_t)u * n_rep * kD + i) : 0.0f;
+        }
+        for (int i = threadIdx.x; i < 4 * kD; i += blockDim.x) o_s[i] = 0.0f;
+        __syncthreads();
+        const int t_begin = rs * res_chunk;
+        const int t_end = t_begin + res_chunk < res_len ? t_begin + res_chunk : res_len;
+        float m[4], l[4], o[4][4];
+        if (L.res_dtype == KIVI_BF16)
+            residual_part<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(L.k_res) + (int64_t)u * L.residual_cap * kD,
+                                         reinterpret_cast<const __nv_bfloat16*>(L.v_res) + (int64_t)u * L.residual_cap * kD,
+                                         L.residual_cap, res_start, res_len, t_begin, t_end, q_s, lane, warp, m, l, o);
+        else
+            residual_part<float>(reinterpret_cast<const float*>(L.k_res) + (int64_t)u * L.residual_cap * kD,
+                                 reinterpret_cast<const float*>(L.v_res) + (int64_t)u * L.residual_cap * kD,
+                                 L.residual_cap, res_start, res_len, t_begin, t_end, q_s, lane, warp, m, l, o);
+        if (lane < 4) {
+            // lane h publishes head h (m and l are warp-uniform after the reductions)
+            float mh = m[0], lh = l[0];
+            if (lane == 1) { mh = m[1]; lh = l[1]; }
+            if (lane == 2) { mh = m[2]; lh = l[2]; }
+            if (lane == 3) { mh = m[3]; lh = l[3]; }
+            ml_s[(warp * 4 + lane) * 2] = mh; ml_s[(warp * 4 + lane) * 2 + 1] = lh;
+        }
+        __syncthreads();
+        for (int w2 = 0; w2 < kWarps; ++w2) {
+            if (warp == w2) {
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    float M = -INFINITY;
+                    for (int w3 = 0; w3 < kWarps; ++w3) M = fmaxf(M, ml_s[(w3 * 4 + h) * 2]);
+                    const float f = (m[h] == -INFINITY) ? 0.0f : ex2(m[h] - M);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o_s[h * kD + 4 * lane + i] += f * o[h][i];
+                }
+            }
+            __syncthreads();
+        }
+        const int64_t pbase = ((int64_t)u * n_splits_total + nq_splits + rs) * n_rep;
+        for (int i = threadIdx.x; i < n_rep * kD; i += blockDim.x) part_o[pbase * kD + i] = o_s[i];
+        if (threadIdx.x < n_rep) {
+            const int h = threadIdx.x;
+            float Mh = -INFINITY, ls = 0.0f;
+            for (int w2 = 0; w2 < kWarps; ++w2) Mh = fmaxf(Mh, ml_s[(w2 * 4 + h) * 2]);
+            for (int w2 = 0; w2 < kWarps; ++w2) {
+                const float mw = ml_s[(w2 * 4 + h) * 2];
+                if (mw != -INFINITY) ls += ml_s[(w2 * 4 + h) * 2 + 1] * ex2(mw - Mh);
+            }
+            part_ml[(pbase + h) * 2] = Mh;
+            part_ml[(pbase + h) * 2 + 1] = ls;
+        }
+        return;
+    }
+    const int split = (int)blockIdx.x - n_res_splits;
     const int part = gid & 1, hB = gid >> 1;
     const int64_t max_groups = L.max_tokens / kG;
     const int64_t n_groups = quant_len / kG;
@@ -297,14 +489,14 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, const void* __restrict__ q, int
         for (int i = 0; i < kStages && i < my_n; ++i) issue(i);
     }
 
-    // query registers: channel 64*qh + 16*tig + 4*m + i at index 16*qh + 4*m + i,
+    // query registers: channel 64*qh + 16*m + 4*tig + i at index 16*qh + 4*m + i,
     // head hB, pre-multiplied by sm_scale * log2(e)
     float qreg[32];
     {
         const float f = scale_log2;
 #pragma unroll
         for (int r = 0; r < 32; ++r) {
-            const int ch = 64 * (r >> 4) + 16 * tig + (r & 15);
+            const int ch = 64 * (r >> 4) + 16 * ((r >> 2) & 3) + 4 * tig + (r & 3);
             qreg[r] = hB < n_rep ? f * load_as_float(q, q_dtype, ((int64_t)u * n_rep + hB) * kD + ch) : 0.0f;
         }
     }
@@ -403,35 +595,35 @@ constexpr size_t kSmemBytes = (size_t)kWarps * kStages * kStageBytes + kWarps * 
 
 }  // namespace
 
-int run_attn_fp32_residual(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
-                           const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits,
-                           int n_splits, float* part_o, float* part_ml, cudaStream_t st);
-
 bool attn_mma_supported(const kivi_layer* L, int n_rep, int q_dtype) {
     (void)q_dtype;
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     return L->head_dim == kD && L->group_size == kG && n_rep >= 1 && n_rep <= 4 &&
-           al(L->k_codes) && al(L->k_scales) && al(L->k_zeros) && al(L->v_codes) && al(L->v_scales) && al(L->v_zeros);
+           al(L->k_res) && al(L->v_res) && al(L->k_codes) && al(L->k_scales) && al(L->k_zeros) && al(L->v_codes) && al(L->v_scales) && al(L->v_zeros);
+}
+
+// number of residual CTAs per unit and tokens per CTA (multiple of 32)
+void attn_mma_residual_plan(int res_len, int* n_res_splits, int* res_chunk) {
+    int rs = (res_len + 32 * kWarps - 1) / (32 * kWarps);
+    if (rs > 8) rs = 8;
+    int chunk = rs ? (res_len + rs - 1) / rs : 0;
+    chunk = (chunk + 31) / 32 * 32;
+    *n_res_splits = chunk ? (res_len + chunk - 1) / chunk : 0;
+    *res_chunk = chunk;
 }
 
 int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
                  const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
-                 int n_splits, float* part_o, float* part_ml, cudaStream_t st) {
+                 int n_res_splits, int res_chunk, float* part_o, float* part_ml, cudaStream_t st) {
     static thread_local bool attr_set = false;
     if (!attr_set) {
         KIVI_CUDA_OK(cudaFuncSetAttribute(attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         attr_set = true;
     }
-    if (res_len > 0) {
-        if (int rc = run_attn_fp32_residual(L, quant_len, res_start, res_len, q, q_dtype, n_rep, scale_log2,
-                                            nq_splits, n_splits, part_o, part_ml, st)) return rc;
-    }
-    if (nq_splits > 0) {
-        dim3 grid((unsigned)nq_splits, (unsigned)L->num_units);
-        attn_mma_kernel<<<grid, kWarps * 32, kSmemBytes, st>>>(*L, quant_len, q, q_dtype, scale_log2, n_rep, gps,
-                                                             n_splits, part_o, part_ml);
-        KIVI_LAUNCH_OK();
-    }
+    dim3 grid((unsigned)(nq_splits + n_res_splits), (unsigned)L->num_units);
+    attn_mma_kernel<<<grid, kWarps * 32, kSmemBytes, st>>>(*L, quant_len, res_start, res_len, q, q_dtype, scale_log2,
+                                                         n_rep, gps, nq_splits, n_res_splits, res_chunk, part_o, part_ml);
+    KIVI_LAUNCH_OK();
     return KIVI_OK;
 }
 

@@ -45,9 +45,10 @@ int run_attn_fp32(const kivi_layer* L, int64_t quant_len, int res_start, int res
                   const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
                   int n_splits, float* part_o, float* part_ml, cudaStream_t st);
 bool attn_mma_supported(const kivi_layer* L, int n_rep, int q_dtype);
+void attn_mma_residual_plan(int res_len, int* n_res_splits, int* res_chunk);
 int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
                  const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
-                 int n_splits, float* part_o, float* part_ml, cudaStream_t st);
+                 int n_res_splits, int res_chunk, float* part_o, float* part_ml, cudaStream_t st);
 int attn_mma_fault_word(int* out);
 __global__ void merge_splits_kernel(const float* part_o, const float* part_ml, void* out,
                                     int out_dtype, int n_splits, int D);
@@ -117,12 +118,13 @@ extern "C" int kivi_quant_dequant_roundtrip_values(const void* input, int in_dty
 
 extern "C" int kivi_decode_attention_max_splits(void) { return kMaxSplitsC; }
 
-// partial outputs [units][splits+1][n_rep][D] + (max, sum) [units][splits+1][n_rep][2];
-// the +1 is the residual-ring split.
+// partial outputs [units][splits+8][n_rep][D] + (max, sum) [units][splits+8][n_rep][2];
+// the +8 covers the residual-ring parts (1 for the fp32 kernel, up to 8 for the
+// tensor-core kernel).
 extern "C" size_t kivi_decode_attention_workspace(int num_units, int n_rep, int head_dim, int num_splits) {
     if (num_units <= 0 || n_rep <= 0 || head_dim <= 0) return 0;
     if (num_splits <= 0 || num_splits > kMaxSplitsC) num_splits = kMaxSplitsC;
-    return (size_t)num_units * (num_splits + 1) * n_rep * (head_dim + 2) * sizeof(float);
+    return (size_t)num_units * (num_splits + 8) * n_rep * (head_dim + 2) * sizeof(float);
 }
 
 static int plan_splits(int num_units, int64_t n_groups, int requested) {
@@ -159,16 +161,6 @@ extern "C" int kivi_decode_attention(const kivi_layer* L, int64_t quant_len, int
     const int64_t n_groups = quant_len / G;
     const int nq_splits = plan_splits(L->num_units, n_groups, num_splits);
     const int gps = nq_splits > 0 ? (int)((n_groups + nq_splits - 1) / nq_splits) : 0;
-    const int n_splits = nq_splits + (res_len > 0 ? 1 : 0);
-    const size_t need = (size_t)L->num_units * n_splits * n_rep * (D + 2) * sizeof(float);
-    KIVI_REQUIRE(workspace != nullptr && workspace_bytes >= need,
-                 "workspace too small: %zu bytes given, %zu needed", workspace_bytes, need);
-    float* part_o = reinterpret_cast<float*>(workspace);
-    float* part_ml = part_o + (size_t)L->num_units * n_splits * n_rep * D;
-    if (sm_scale <= 0.0f) sm_scale = 1.0f / sqrtf((float)D);
-    const float scale_log2 = sm_scale * 1.4426950408889634f;
-    cudaStream_t st = (cudaStream_t)stream;
-
     bool use_mma = false;
     if (path == KIVI_ATTN_MMA) {
         if (!attn_mma_supported(L, n_rep, q_dtype)) {
@@ -181,13 +173,25 @@ extern "C" int kivi_decode_attention(const kivi_layer* L, int64_t quant_len, int
         // the tensor-core kernel when the shape allows it
         use_mma = q_dtype == KIVI_BF16 && attn_mma_supported(L, n_rep, q_dtype);
     }
+    int n_res_splits = res_len > 0 ? 1 : 0, res_chunk = res_len;
+    if (use_mma) attn_mma_residual_plan(res_len, &n_res_splits, &res_chunk);
+    const int n_splits = nq_splits + n_res_splits;
+    const size_t need = (size_t)L->num_units * n_splits * n_rep * (D + 2) * sizeof(float);
+    KIVI_REQUIRE(workspace != nullptr && workspace_bytes >= need,
+                 "workspace too small: %zu bytes given, %zu needed", workspace_bytes, need);
+    float* part_o = reinterpret_cast<float*>(workspace);
+    float* part_ml = part_o + (size_t)L->num_units * n_splits * n_rep * D;
+    if (sm_scale <= 0.0f) sm_scale = 1.0f / sqrtf((float)D);
+    const float scale_log2 = sm_scale * 1.4426950408889634f;
+    cudaStream_t st = (cudaStream_t)stream;
+
     int rc = use_mma
-        ? run_attn_mma(L, quant_len, res_start, res_len, q, q_dtype, n_rep, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st)
+        ? run_attn_mma(L, quant_len, res_start, res_len, q, q_dtype, n_rep, scale_log2, nq_splits, gps, n_res_splits, res_chunk, part_o, part_ml, st)
         : run_attn_fp32(L, quant_len, res_start, res_len, q, q_dtype, n_rep, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st);
     if (rc) return rc;
     dim3 grid((unsigned)L->num_units, (unsigned)n_rep);
     merge_splits_kernel<<<grid, D >= 256 ? 256 : 128, n_splits * sizeof(float), st>>>(part_o, part_ml, out, out_dtype, n_splits, D);
     KIVI_LAUNCH_OK();
-    note_launches(1 + (use_mma ? (nq_splits > 0) + (res_len > 0) : 1));
+    note_launches(2);
     return KIVI_OK;
 }

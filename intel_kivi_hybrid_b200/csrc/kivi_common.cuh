@@ -80,8 +80,14 @@ __device__ __forceinline__ void store_from_float(void* p, int dtype, int64_t i, 
 // ---- key block layout --------------------------------------------------------
 // Byte offset inside one key block of the codes of channel d, token lane j
 // (tokens j, j+Q, j+2Q, j+3Q of the group; Q = G/4); W = min(D, 64).
+// Within a 64-channel half-row the two 2-bit fields (d>>2)&3 and (d>>4)&3 of
+// the channel index are swapped, so that a 16-byte piece of a row holds four
+// 4-channel words that are 16 channels apart: the tensor-core kernel gives each
+// lane one such piece and then reads the matching scales without bank conflicts.
 __host__ __device__ __forceinline__ int kblock_offset(int d, int j, int Q, int W) {
-    return (d / W) * Q * W + j * W + (d % W);
+    int dl = d % W;
+    if (W == 64) dl = (dl & 3) | (((dl >> 4) & 3) << 2) | (((dl >> 2) & 3) << 4);
+    return (d / W) * Q * W + j * W + dl;
 }
 
 __host__ __device__ __forceinline__ int elem_size(int dtype) { return dtype == KIVI_BF16 ? 2 : 4; }

@@ -87,7 +87,9 @@ def test_packed_store_matches_oracle_flush_by_flush(cabi):
     assert torch.equal(st.v_codes[:, :ng * G].cpu(), vp)
     # key blocks hold the same codes as the reference layout, re-laid out
     kc = ko.unpack_codes(torch.stack(oc.k_packed, dim=2).reshape(B * H, ng, D, G // 4))   # [u,g,D,G]
-    blk = st.k_codes[:, :ng].cpu().reshape(B * H, ng, G // 4, D)                            # D <= 64: [j][d]
+    blk = st.k_codes[:, :ng].cpu().reshape(B * H, ng, G // 4, D)                            # one 64-wide half: [j][p(d)]
+    perm = torch.tensor([(d & 3) | (((d >> 4) & 3) << 2) | (((d >> 2) & 3) << 4) for d in range(D)])
+    blk = blk[..., perm]                                                                    # -> [j][d]
     Q = G // 4
     for e in range(4):
         got = (blk >> (2 * e)) & 3                       # tokens j + e*Q
