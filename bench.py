@@ -32,6 +32,8 @@ WORKLOADS = {
     "cfg3": (4, 8, 4, 128, 32, 128, 131072, 128),    # configs[3]: B=4, 128k context
     "small": (2, 8, 4, 128, 32, 128, 992, 128),
     "long": (2, 8, 4, 128, 32, 128, 65536, 128),     # few units, long history: profiling case
+    "mid": (16, 8, 4, 128, 32, 128, 16384, 128),
+    "prof": (14, 8, 4, 128, 32, 128, 16384, 128),    # ~one wave of CTAs with long streams: ncu case (235 MB)
 }
 LAYERS = 32          # Llama-3-8B depth, for the tokens/s figure
 
@@ -49,7 +51,9 @@ def peaks():
 
 
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi polled every 100 ms in the background; samples are kept with
+    their wall-clock time so that only those taken under load are used."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
@@ -62,7 +66,8 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def stop(self, windows):
+        """windows: list of (t0, t1) wall-clock intervals (time.time()) under load."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -71,6 +76,7 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
             out = ""
+        import datetime
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.strip().splitlines():
@@ -78,9 +84,13 @@ class ClockSampler:
             if len(p) < 7:
                 continue
             try:
-                sm.append(float(p[0])); mx.append(float(p[1]))
+                ts = datetime.datetime.strptime(p[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                f_sm, f_mx = float(p[1]), float(p[2])
             except ValueError:
                 continue
+            if not any(a - 0.05 <= ts <= b + 0.05 for a, b in windows):
+                continue
+            sm.append(f_sm); mx.append(f_mx)
             for n, v in zip(names, p[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
@@ -176,6 +186,7 @@ def run_ours(args, wl):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    sampler = ClockSampler(local) if rank == 0 else None     # started early: nvidia-smi needs a moment to come up
     dtype = torch.bfloat16
     path = {"auto": cabi.ATTN_AUTO, "fp32": cabi.ATTN_FP32, "mma": cabi.ATTN_MMA}[args.path]
     U = B * Hkv
@@ -213,20 +224,21 @@ def run_ours(args, wl):
         step(i)
     launches_per_step = cabi.lib.kivi_last_launch_count()
     barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
+    windows = []
+    w0 = time.time()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     ev[0].record()
     for i in range(args.steps):
         step(i)
         ev[i + 1].record()
     barrier()
+    windows.append((w0, time.time()))
     total_ms = ev[0].elapsed_time(ev[-1])
     per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
     if world > 1:
         t = torch.tensor([total_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t.item())
-    clocks = sampler.stop() if sampler else None
     ms_step = total_ms / args.steps
     by = alg_bytes(B, Hkv, n_rep, D, G, n_quant, n_res)
     value = world * by / (ms_step * 1e-3) / 1e9
@@ -271,6 +283,20 @@ def run_ours(args, wl):
         e2e_ms = float(t.item())
     e2e_val = world * by / (e2e_ms * 1e-3) / 1e9
 
+    clocks = None
+    if sampler is not None:
+        # the timed region can be shorter than one polling period: keep the same
+        # kernel loop running (untimed) until at least ~1.2 s of load was sampled
+        w0 = time.time()
+        i = 0
+        while time.time() - w0 < 1.2:
+            step(i); i += 1
+            if i % 50 == 0:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        windows.append((w0, time.time()))
+        clocks = sampler.stop(windows)
+        clocks["sampled"] = "timed region plus 1.2 s of the same step loop right after it"
     if rank == 0:
         peak, which = peaks()
         achieved = by / (statistics.median(per) * 1e-3) / 1e9

@@ -45,6 +45,12 @@ constexpr int kD = 128, kG = 32;
 #ifndef KIVI_MMA_STAGES
 #define KIVI_MMA_STAGES 2
 #endif
+#ifndef KIVI_MMA_UNROLL_HALVES
+#define KIVI_MMA_UNROLL_HALVES 2     /* 2 = fully unrolled (fastest), 1 = keep the two halves as loops */
+#endif
+#ifndef KIVI_MMA_Q_SMEM
+#define KIVI_MMA_Q_SMEM 0
+#endif
 #ifndef KIVI_MMA_MIN_CTAS
 #define KIVI_MMA_MIN_CTAS 3
 #endif
@@ -54,6 +60,9 @@ constexpr int kStages = KIVI_MMA_STAGES;
 constexpr int kGroupBytes = 4096;      // kc 1024 | ks 512 | kz 512 | vc 1024 | vs 512 | vz 512
 constexpr int kStageBytes = kGPS * kGroupBytes;
 constexpr uint32_t kSpinLimit = 1u << 22;
+// distance in floats between the query vectors of consecutive k-steps of a lane
+constexpr int kQStride = KIVI_MMA_Q_SMEM ? 16 : 4;
+constexpr int kUnrollHalves = KIVI_MMA_UNROLL_HALVES;
 
 __device__ int g_fault_word = 0;
 
@@ -134,40 +143,41 @@ struct WarpState {
 __device__ __forceinline__ void process_group(
     const uint8_t* __restrict__ kc, const float* __restrict__ ks, const float* __restrict__ kz,
     const uint8_t* __restrict__ vc, const float* __restrict__ vs, const float* __restrict__ vz,
-    const float (&qreg)[32], uint32_t part_mask, float keep, int part, int gid, int tig, int lane,
+    const float* __restrict__ qreg /* 32 values of this lane: registers or shared memory */,
+    uint32_t part_mask, float keep, int part, int gid, int tig, int lane,
     WarpState& st) {
     // ---------------- q.k ----------------
-    uint32_t w[8];
-    {
-        const uint4 a = *reinterpret_cast<const uint4*>(kc + gid * 64 + tig * 16);
-        const uint4 b = *reinterpret_cast<const uint4*>(kc + 512 + gid * 64 + tig * 16);
-        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
-    }
     float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
     float qz = 0.0f;
+#pragma unroll kUnrollHalves
+    for (int qh = 0; qh < 2; ++qh) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(kc + qh * 512 + gid * 64 + tig * 16);
+        const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-    for (int kt = 0; kt < 8; ++kt) {
-        const int ch = 64 * (kt >> 2) + 16 * (kt & 3) + 4 * tig;
-        const float4 s4 = *reinterpret_cast<const float4*>(ks + ch);
-        const float4 z4 = *reinterpret_cast<const float4*>(kz + ch);
-        const float x0 = qreg[4 * kt + 0] * s4.x, x1 = qreg[4 * kt + 1] * s4.y;
-        const float x2 = qreg[4 * kt + 2] * s4.z, x3 = qreg[4 * kt + 3] * s4.w;
-        qz = fmaf(qreg[4 * kt + 0], z4.x, qz); qz = fmaf(qreg[4 * kt + 1], z4.y, qz);
-        qz = fmaf(qreg[4 * kt + 2], z4.z, qz); qz = fmaf(qreg[4 * kt + 3], z4.w, qz);
-        // fp16 hi/lo split of q*s: hi lanes keep x truncated to 11 significant
-        // bits, lo lanes keep the remainder (part_mask = 0 on hi lanes)
-        const float r0 = x0 - __uint_as_float(__float_as_uint(x0) & part_mask);
-        const float r1 = x1 - __uint_as_float(__float_as_uint(x1) & part_mask);
-        const float r2 = x2 - __uint_as_float(__float_as_uint(x2) & part_mask);
-        const float r3 = x3 - __uint_as_float(__float_as_uint(x3) & part_mask);
-        const uint32_t b0 = pack_f16_rz(r0, r2);
-        const uint32_t b1 = pack_f16_rz(r1, r3);
-        const uint32_t we = w[kt], wo = w[kt] >> 8;
-        uint32_t a[4];
-        a[0] = code_pair<0>(we); a[1] = code_pair<1>(we); a[2] = code_pair<0>(wo); a[3] = code_pair<1>(wo);
-        mma_f16(c0, a, b0, b1);
-        a[0] = code_pair<2>(we); a[1] = code_pair<3>(we); a[2] = code_pair<2>(wo); a[3] = code_pair<3>(wo);
-        mma_f16(c1, a, b0, b1);
+        for (int m = 0; m < 4; ++m) {
+            const int kt = 4 * qh + m;
+            const int ch = 64 * qh + 16 * m + 4 * tig;
+            const float4 s4 = *reinterpret_cast<const float4*>(ks + ch);
+            const float4 z4 = *reinterpret_cast<const float4*>(kz + ch);
+            const float4 q4 = *reinterpret_cast<const float4*>(qreg + kQStride * kt);
+            const float x0 = q4.x * s4.x, x1 = q4.y * s4.y, x2 = q4.z * s4.z, x3 = q4.w * s4.w;
+            qz = fmaf(q4.x, z4.x, qz); qz = fmaf(q4.y, z4.y, qz);
+            qz = fmaf(q4.z, z4.z, qz); qz = fmaf(q4.w, z4.w, qz);
+            // fp16 hi/lo split of q*s: hi lanes keep x truncated to 11 significant
+            // bits, lo lanes keep the remainder (part_mask = 0 on hi lanes)
+            const float r0 = x0 - __uint_as_float(__float_as_uint(x0) & part_mask);
+            const float r1 = x1 - __uint_as_float(__float_as_uint(x1) & part_mask);
+            const float r2 = x2 - __uint_as_float(__float_as_uint(x2) & part_mask);
+            const float r3 = x3 - __uint_as_float(__float_as_uint(x3) & part_mask);
+            const uint32_t b0 = pack_f16_rz(r0, r2);
+            const uint32_t b1 = pack_f16_rz(r1, r3);
+            const uint32_t we = w[m], wo = w[m] >> 8;
+            uint32_t a[4];
+            a[0] = code_pair<0>(we); a[1] = code_pair<1>(we); a[2] = code_pair<0>(wo); a[3] = code_pair<1>(wo);
+            mma_f16(c0, a, b0, b1);
+            a[0] = code_pair<2>(we); a[1] = code_pair<3>(we); a[2] = code_pair<2>(wo); a[3] = code_pair<3>(wo);
+            mma_f16(c1, a, b0, b1);
+        }
     }
     // zero term of head gid>>1 (both lanes of a gid pair hold the same partial)
     qz += __shfl_xor_sync(0xffffffffu, qz, 1);
@@ -200,7 +210,7 @@ __device__ __forceinline__ void process_group(
     for (int e = 0; e < 4; ++e) { p[e] = ex2(s[e] - st.m); st.l += p[e]; }
 
     // ---------------- p.v ----------------
-#pragma unroll
+#pragma unroll kUnrollHalves
     for (int kap = 0; kap < 2; ++kap) {
         const int tok0 = 4 * kap + tig;                 // tokens tok0 + 8e, e = 0..3
         const int src = 4 * tok0 + (gid >> 1);          // lane holding their p for head gid>>1
@@ -385,6 +395,8 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + kWarps * kStages * kStageBytes);  // [kWarps][kStages]
     float* ml_s = reinterpret_cast<float*>(bars + kWarps * kStages);             // [kWarps][4][2]
     float* o_s = ml_s + kWarps * 4 * 2;                                          // [4][128]
+    float* q_sh = o_s + 4 * kD;                                                  // [4][128] (KIVI_MMA_Q_SMEM)
+    (void)q_sh;
 
     const int u = blockIdx.y;
     const int n_splits_total = nq_splits + n_res_splits;
@@ -491,7 +503,17 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
 
     // query registers: channel 64*qh + 16*m + 4*tig + i at index 16*qh + 4*m + i,
     // head hB, pre-multiplied by sm_scale * log2(e)
-    float qreg[32];
+#if KIVI_MMA_Q_SMEM
+    // shared [4 heads][8 k-steps][4 tig][4]: the lane's 4 channels of a k-step are one vector
+    for (int i = threadIdx.x; i < 4 * kD; i += blockDim.x) {
+        const int h = i >> 7, kt = (i >> 4) & 7, tg = (i >> 2) & 3, e = i & 3;
+        const int ch = 64 * (kt >> 2) + 16 * (kt & 3) + 4 * tg + e;
+        q_sh[i] = h < n_rep ? scale_log2 * load_as_float(q, q_dtype, ((int64_t)u * n_rep + h) * kD + ch) : 0.0f;
+    }
+    __syncthreads();
+    const float* qreg = q_sh + hB * 128 + tig * 4;
+#else
+    __align__(16) float qreg[32];
     {
         const float f = scale_log2;
 #pragma unroll
@@ -500,6 +522,7 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
             qreg[r] = hB < n_rep ? f * load_as_float(q, q_dtype, ((int64_t)u * n_rep + hB) * kD + ch) : 0.0f;
         }
     }
+#endif
     const uint32_t part_mask = part ? 0xffffe000u : 0u;   // keep 11 significant bits
     const float keep = part ? 0.0f : 1.0f;
 
@@ -591,7 +614,7 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
 }
 
 constexpr size_t kSmemBytes = (size_t)kWarps * kStages * kStageBytes + kWarps * kStages * 8 +
-                              kWarps * 4 * 2 * 4 + 4 * kD * 4;
+                              kWarps * 4 * 2 * 4 + 4 * kD * 4 + (KIVI_MMA_Q_SMEM ? 4 * kD * 4 : 0);
 
 }  // namespace
 

@@ -127,20 +127,43 @@ extern "C" size_t kivi_decode_attention_workspace(int num_units, int n_rep, int 
     return (size_t)num_units * (num_splits + 8) * n_rep * (head_dim + 2) * sizeof(float);
 }
 
-static int plan_splits(int num_units, int64_t n_groups, int requested) {
-    if (n_groups <= 0) return 0;
-    int s = requested;
-    if (s <= 0) {
-        // aim at ~8 CTAs of 128 threads per SM, never below 4 token groups per CTA
-        const int64_t target = (int64_t)num_sms() * 8;
-        s = (int)((target + num_units - 1) / num_units);
-        const int64_t cap = (n_groups + 3) / 4;
-        if (s > cap) s = (int)cap;
-    }
+static int clamp_splits(int64_t s, int64_t n_groups) {
     if (s > kMaxSplitsC) s = kMaxSplitsC;
-    if (s > n_groups) s = (int)n_groups;
+    if (s > n_groups) s = n_groups;
     if (s < 1) s = 1;
-    return s;
+    return (int)s;
+}
+
+// CUDA-core kernel: aim at ~8 CTAs of 128 threads per SM, never below 4 token
+// groups per CTA.
+static int plan_splits_fp32(int num_units, int64_t n_groups, int requested) {
+    if (n_groups <= 0) return 0;
+    if (requested > 0) return clamp_splits(requested, n_groups);
+    const int64_t target = (int64_t)num_sms() * 8;
+    int64_t s = (target + num_units - 1) / num_units;
+    const int64_t cap = (n_groups + 3) / 4;
+    if (s > cap) s = cap;
+    return clamp_splits(s, n_groups);
+}
+
+// Tensor-core kernel: 3 CTAs per SM are resident.  Measured on B200, a CTA
+// costs about c0 = 10 us of fixed time (cold instruction fetch, first bulk
+// copy, the merge of its warps) plus c1 = 0.47 us per token group, so with
+// `slots` resident CTAs the time of s splits per unit is about
+//   units*s*c0/slots + units*n_groups*c1/slots + (c0 + n_groups*c1/s)/2,
+// minimal at s = sqrt(n_groups*c1*slots / (2*units*c0)).  When that lands
+// between one and two waves of CTAs, one full wave is faster.
+static int plan_splits_mma(int num_units, int64_t n_groups, int requested, int n_res_splits) {
+    if (n_groups <= 0) return 0;
+    if (requested > 0) return clamp_splits(requested, n_groups);
+    const double slots = 3.0 * num_sms();
+    const double c1_over_c0 = 0.047;
+    int64_t s = (int64_t)llround(sqrt(0.5 * (double)n_groups * c1_over_c0 * slots / num_units));
+    if (s < 1) s = 1;
+    const int64_t s_fill = (int64_t)(slots / num_units) - n_res_splits;     // most splits that still fit one wave
+    const double waves = (double)num_units * (double)(s + n_res_splits) / slots;
+    if (waves < 2.0 && s_fill >= 1) s = s_fill;
+    return clamp_splits(s, n_groups);
 }
 
 extern "C" int kivi_decode_attention(const kivi_layer* L, int64_t quant_len, int res_start,
@@ -159,8 +182,6 @@ extern "C" int kivi_decode_attention(const kivi_layer* L, int64_t quant_len, int
     KIVI_REQUIRE(L->num_units <= 65535, "num_units (%d) above 65535", L->num_units);
     const int D = L->head_dim, G = L->group_size;
     const int64_t n_groups = quant_len / G;
-    const int nq_splits = plan_splits(L->num_units, n_groups, num_splits);
-    const int gps = nq_splits > 0 ? (int)((n_groups + nq_splits - 1) / nq_splits) : 0;
     bool use_mma = false;
     if (path == KIVI_ATTN_MMA) {
         if (!attn_mma_supported(L, n_rep, q_dtype)) {
@@ -175,6 +196,9 @@ extern "C" int kivi_decode_attention(const kivi_layer* L, int64_t quant_len, int
     }
     int n_res_splits = res_len > 0 ? 1 : 0, res_chunk = res_len;
     if (use_mma) attn_mma_residual_plan(res_len, &n_res_splits, &res_chunk);
+    const int nq_splits = use_mma ? plan_splits_mma(L->num_units, n_groups, num_splits, n_res_splits)
+                                  : plan_splits_fp32(L->num_units, n_groups, num_splits);
+    const int gps = nq_splits > 0 ? (int)((n_groups + nq_splits - 1) / nq_splits) : 0;
     const int n_splits = nq_splits + n_res_splits;
     const size_t need = (size_t)L->num_units * n_splits * n_rep * (D + 2) * sizeof(float);
     KIVI_REQUIRE(workspace != nullptr && workspace_bytes >= need,
