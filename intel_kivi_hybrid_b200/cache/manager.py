@@ -1,0 +1,264 @@
+"""KiviCache: KIVI 2-bit asymmetric KV cache, resident on the GPU.
+
+Drop-in for the reference's ``KiviCache`` (src/kivi_sycl/cache/manager.py:52-423):
+same constructor arguments and asserts, ``from_model``, ``add_tokens``,
+``get_full_cache``, ``reset``, ``get_stats``, ``total_flushes`` and the
+attributes its tests read (``_quant_token_count``, ``res_keys``, ``G``, ``R``,
+``num_layers``, ``batch_size``, ``num_kv_heads``).
+
+What is different underneath: the reference keeps the residual window and a
+dequantized fp32 history on the CPU and throws the packed data away
+(manager.py:100-117); here every layer owns a packed store and a residual ring
+in device memory (``cabi.LayerStore``), flushes run as kernels on the current
+stream with no host round trip, and ``decode_attention`` attends over the
+packed store directly.  ``get_full_cache`` survives as the compatibility path
+for third-party model code that wants dense past_key_values.
+
+With ``shard=(rank, world)`` a process keeps only its contiguous slice of the
+(batch, kv_head) units; ``decode_attention`` then all-gathers the outputs.
+"""
+from typing import List, Optional, Tuple
+
+import torch
+
+from .. import cabi
+from ..config.model_config import detect_model_config
+from ..parallel import all_gather_units, unit_partition
+
+__all__ = ["KiviCache"]
+
+
+def _iter_kv_layers(past_key_values):
+    """(key, value) per layer from a legacy tuple of pairs, a Cache with
+    ``.layers[i].keys/.values``, or one with ``key_cache``/``value_cache`` lists
+    (same three shapes the reference accepts, manager.py:14-33)."""
+    if hasattr(past_key_values, "layers"):
+        for layer in past_key_values.layers:
+            yield layer.keys, layer.values
+    elif hasattr(past_key_values, "key_cache") and hasattr(past_key_values, "value_cache"):
+        yield from zip(past_key_values.key_cache, past_key_values.value_cache)
+    else:
+        for item in past_key_values:
+            yield item[0], item[1]
+
+
+def _build_cache(layers):
+    """List of (key, value) -> transformers DynamicCache through ``update``, the
+    construction path that is stable across transformers versions
+    (manager.py:36-49)."""
+    from transformers.cache_utils import DynamicCache
+    cache = DynamicCache()
+    for i, (k, v) in enumerate(layers):
+        cache.update(k, v, i)
+    return cache
+
+
+class KiviCache:
+    def __init__(self, num_layers: int, head_dim: int, num_kv_heads: Optional[int] = None,
+                 device: str = "cuda", group_size: int = 32, residual_length: int = 128,
+                 max_tokens: int = 4096, rounding: str = "half_away",
+                 shard: Optional[Tuple[int, int]] = None):
+        assert head_dim % group_size == 0, \
+            f"head_dim ({head_dim}) must be divisible by group_size ({group_size})"
+        assert group_size >= 4 and group_size % 4 == 0, \
+            f"group_size ({group_size}) must be >= 4 and divisible by 4"
+        assert group_size <= residual_length, (
+            f"group_size ({group_size}) must not exceed residual_length ({residual_length}) "
+            f"- flushing requires a full group of tokens to be available in the residual buffer, "
+            f"or tokens are silently dropped.")
+        assert rounding in ("half_away", "half_even")
+        self.device = device
+        self.G = group_size
+        self.R = residual_length
+        self.head_dim = head_dim
+        self.num_layers = num_layers
+        self.num_kv_heads = num_kv_heads
+        self.batch_size: Optional[int] = None
+        self.rounding = cabi.ROUND_HALF_AWAY if rounding == "half_away" else cabi.ROUND_HALF_EVEN
+        self.shard = shard
+        self._capacity = max(max_tokens, group_size)
+        self._stores: List[Optional[cabi.LayerStore]] = [None] * num_layers
+        self._flush_count: List[int] = [0] * num_layers
+        self._cache_view = None
+        self._cache_view_valid = False
+        self._serve_device = None
+        self._serve_dtype = None
+        self._units: Optional[Tuple[int, int]] = None      # [u0, u1) held by this process
+
+    @classmethod
+    def from_model(cls, model, device: str = "cuda", group_size: int = 32,
+                   residual_length: int = 128, **kwargs) -> "KiviCache":
+        cfg = detect_model_config(model)
+        return cls(num_layers=cfg["num_layers"], head_dim=cfg["head_dim"], num_kv_heads=cfg["num_kv_heads"],
+                   device=device, group_size=group_size, residual_length=residual_length, **kwargs)
+
+    # ------------------------------------------------------------------ state views
+    @property
+    def _quant_token_count(self) -> List[int]:
+        return [0 if s is None else s.quant_len for s in self._stores]
+
+    def _window(self, i: int, which: str) -> Optional[torch.Tensor]:
+        st = self._stores[i]
+        if st is None:
+            return None
+        ring = st.k_res if which == "k" else st.v_res
+        idx = (torch.arange(st.res_len, device=ring.device) + st.res_start) % st.R
+        n_local = st.num_units
+        H = self.num_kv_heads
+        win = ring.index_select(1, idx)
+        return win.reshape(n_local // H, H, st.res_len, self.head_dim) if n_local % H == 0 else win
+
+    @property
+    def res_keys(self) -> List[Optional[torch.Tensor]]:
+        """Residual window of every layer, oldest token first, [B, H, res_len, D]."""
+        return [self._window(i, "k") for i in range(self.num_layers)]
+
+    @property
+    def res_values(self) -> List[Optional[torch.Tensor]]:
+        return [self._window(i, "v") for i in range(self.num_layers)]
+
+    # ------------------------------------------------------------------ core API
+    def _new_store(self, n_units: int, capacity: int, dtype) -> cabi.LayerStore:
+        return cabi.LayerStore(n_units, self.head_dim, self.G, self.R, capacity, dtype, self.device)
+
+    def _ensure_capacity(self, i: int, n_new: int, dtype, n_units: int) -> cabi.LayerStore:
+        st = self._stores[i]
+        if st is None:
+            st = self._stores[i] = self._new_store(n_units, self._capacity, dtype)
+        _, need, _ = cabi.cache_plan(st.quant_len, st.res_len, n_new, self.G, self.R)
+        if need > st.max_tokens:
+            cap = st.max_tokens
+            while cap < need:
+                cap *= 2
+            big = self._new_store(n_units, cap, dtype)
+            ng, nt = st.quant_len // self.G, st.quant_len
+            for name, n in (("k_codes", ng), ("k_scales", ng), ("k_zeros", ng),
+                            ("v_codes", nt), ("v_scales", nt), ("v_zeros", nt)):
+                getattr(big, name)[:, :n].copy_(getattr(st, name)[:, :n])
+            big.k_res.copy_(st.k_res); big.v_res.copy_(st.v_res)
+            big.quant_len, big.res_start, big.res_len = st.quant_len, st.res_start, st.res_len
+            st = self._stores[i] = big
+        return st
+
+    def add_tokens(self, past_key_values):
+        """Ingest the KV pairs of one forward pass (each tensor [B, H, Seq, D],
+        the full cache the model returns).  Only the tokens beyond those already
+        tracked are taken; they go to the residual ring and whole groups of G are
+        flushed to the packed store while the window holds >= R tokens
+        (manager.py:162-249)."""
+        if past_key_values is not self._cache_view:
+            self._cache_view_valid = False
+        for i, (k, v) in enumerate(_iter_kv_layers(past_key_values)):
+            if self.batch_size is None:
+                self.batch_size = k.shape[0]
+                self.num_kv_heads = k.shape[1]
+                self._serve_device, self._serve_dtype = k.device, k.dtype
+                n_units = self.batch_size * self.num_kv_heads
+                self._units = unit_partition(n_units, *self.shard) if self.shard else (0, n_units)
+            else:
+                assert k.shape[0] == self.batch_size, (
+                    f"KiviCache batch size changed mid-session ({self.batch_size} -> {k.shape[0]}) at layer {i}. "
+                    f"Call reset() before starting a new request/batch.")
+            st = self._stores[i]
+            new_start = 0
+            if st is not None and st.quant_len + st.res_len > 0:
+                new_start = st.quant_len + st.res_len
+                assert k.shape[2] >= new_start, (
+                    f"KiviCache desync at layer {i}: expected past length {new_start} but got {k.shape[2]}. "
+                    f"add_tokens() must be called exactly once per forward pass, seeded by get_full_cache().")
+            n_new = k.shape[2] - new_start
+            assert n_new > 0, (
+                f"KiviCache desync at layer {i}: the forward pass produced no tokens beyond the {new_start} "
+                f"already tracked. add_tokens() was called twice on the same forward output, or the model was "
+                f"fed a past_key_values not obtained from get_full_cache(). Silently skipping here would drop "
+                f"this step's KV and corrupt all subsequent attention.")
+            dtype = torch.bfloat16 if k.dtype == torch.bfloat16 else torch.float32
+            u0, u1 = self._units
+            nk = k[:, :, new_start:, :].flatten(0, 1)[u0:u1].to(device=self.device, dtype=dtype)
+            nv = v[:, :, new_start:, :].flatten(0, 1)[u0:u1].to(device=self.device, dtype=dtype)
+            st = self._ensure_capacity(i, n_new, dtype, u1 - u0)
+            before = st.quant_len
+            st.update(nk, nv, self.rounding)
+            flushed = (st.quant_len - before) // self.G
+            if flushed:
+                self._flush_count[i] += flushed
+                # flushed tokens are now served at 2-bit fidelity: the persistent
+                # view no longer matches (manager.py:244-249)
+                self._cache_view_valid = False
+
+    def decode_attention(self, layer: int, q: torch.Tensor, out_dtype=None) -> torch.Tensor:
+        """Fused attention of one decode step over the packed cache of ``layer``:
+        softmax(q K^T / sqrt(D)) V over [quantized history || residual window].
+        q: [B, Hq, D] on the cache device; returns [B, Hq, D].  No dequantized
+        cache is materialised (this replaces get_full_cache + the model's own
+        attention, generate.py:75-77, for callers that can hand over q)."""
+        st = self._stores[layer]
+        assert st is not None, "decode_attention() before any add_tokens()"
+        B, Hq, D = q.shape
+        n_rep = Hq // self.num_kv_heads
+        u0, u1 = self._units
+        q_units = q.reshape(B * self.num_kv_heads, n_rep, D)[u0:u1].contiguous()
+        out = st.attention(q_units, n_rep=n_rep, out_dtype=out_dtype)
+        if self.shard and self.shard[1] > 1:
+            out = all_gather_units(out, B * self.num_kv_heads, self.shard[0], self.shard[1])
+        return out.reshape(B, Hq, D)
+
+    def get_full_cache(self):
+        """Dense past_key_values for unmodified model code (manager.py:251-290):
+        dequantized history followed by the residual window, as a DynamicCache on
+        the device and in the dtype the model handed its KV in."""
+        if self._cache_view is not None and self._cache_view_valid:
+            return self._cache_view
+        assert not (self.shard and self.shard[1] > 1), "get_full_cache() is not available on a sharded cache"
+        layers = []
+        for i in range(self.num_layers):
+            st = self._stores[i]
+            if st is None or st.quant_len + st.res_len == 0:
+                layers.append((torch.empty(0), torch.empty(0)))
+                continue
+            k, v = st.materialize()
+            shape = (self.batch_size, self.num_kv_heads, k.shape[1], self.head_dim)
+            layers.append((k.reshape(shape).to(self._serve_device, self._serve_dtype),
+                           v.reshape(shape).to(self._serve_device, self._serve_dtype)))
+        self._cache_view = _build_cache(layers)
+        self._cache_view_valid = True
+        return self._cache_view
+
+    def reset(self):
+        """Clear all cached data so the same object can serve a new sequence
+        (manager.py:292-303); device buffers are released and re-created lazily."""
+        self._flush_count = [0] * self.num_layers
+        self._stores = [None] * self.num_layers
+        self.batch_size = None
+        self._cache_view = None
+        self._cache_view_valid = False
+
+    # ------------------------------------------------------------------ stats
+    @property
+    def total_flushes(self) -> int:
+        return sum(self._flush_count)
+
+    def get_stats(self, layer: int = 0) -> dict:
+        """Token and byte counts of one layer, same keys and formulas as the
+        reference (manager.py:384-419).  ``kivi_bytes`` = packed store in use
+        (codes + fp32 scales and zeros, the reference's analytic figure
+        :350-356) + the residual window."""
+        B = self.batch_size or 1
+        H = self.num_kv_heads or 1
+        st = self._stores[layer]
+        D, G = self.head_dim, self.G
+        quant_tokens = 0 if st is None else st.quant_len
+        res_tokens = 0 if st is None else st.res_len
+        total = quant_tokens + res_tokens
+        per_flush = B * H * (D * (G // 4) + D * 8 + G * (D // 4) + G * (D // G) * 8)
+        quant_bytes = per_flush * (quant_tokens // G)
+        elem = 4 if st is None else st.k_res.element_size()
+        res_bytes = 2 * B * H * res_tokens * D * elem
+        fp32_bytes = 2 * B * H * total * D * 4
+        kivi = quant_bytes + res_bytes
+        return {"total_tokens": total, "quantized_tokens": quant_tokens, "residual_tokens": res_tokens,
+                "kivi_bytes": kivi, "fp32_bytes": fp32_bytes, "compression": fp32_bytes / kivi if kivi > 0 else 0}
+
+    def __repr__(self):
+        return (f"KiviCache(layers={self.num_layers}, head_dim={self.head_dim}, "
+                f"G={self.G}, R={self.R}, device='{self.device}')")

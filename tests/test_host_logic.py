@@ -1,0 +1,148 @@
+"""CPU-only checks of the host side: the C-ABI library loads and exports every
+symbol the header declares, the flush arithmetic equals the reference policy,
+unit sharding and its gather (gloo, world size 2), config sniffing, sampling,
+and the Python surface of the drop-in API.  No kernel is launched here."""
+import ctypes
+import os
+import re
+import subprocess
+import sys
+import types
+
+import pytest
+import torch
+
+from oracle import kivi_oracle as ko
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from intel_kivi_hybrid_b200 import _build, cabi
+    hdr = open(os.path.join(ROOT, "include", "kivi_cuda.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    declared = set(re.findall(r"\b(kivi_[a-z0-9_]+)\s*\(", hdr))
+    assert {"kivi_quantize_keys_per_channel", "kivi_cache_update", "kivi_decode_attention"} <= declared
+    lib = ctypes.CDLL(_build.LIB)
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} declared in include/kivi_cuda.h but not exported"
+    assert declared == set(cabi.SIGNATURES), "ctypes binding and header list different entry points"
+    assert cabi.lib.kivi_version() >= 100
+
+
+def test_cache_plan_equals_reference_flush_policy():
+    from intel_kivi_hybrid_b200 import cabi
+    for G, R in ((4, 8), (32, 128), (16, 16), (32, 100), (64, 64)):
+        for ql in (0, G, 5 * G):
+            for rl in (0, 1, R - G, R - 1):
+                for n in (1, 2, G - 1, G, R, 3 * R + 5, 8192):
+                    f, q2, r2 = ko.flush_schedule(ql, rl, n, G, R)
+                    assert cabi.cache_plan(ql, rl, n, G, R) == (f, q2, r2)
+    assert cabi.cache_plan(0, 0, 512, 32, 128) == (13, 416, 96)     # 512-token prefill of config 0
+    with pytest.raises(RuntimeError, match="group_size"):
+        cabi.cache_plan(0, 0, 1, 64, 32)
+
+
+def test_host_side_validation_needs_no_gpu():
+    from intel_kivi_hybrid_b200 import cabi
+    # null pointers / bad sizes are rejected on the host before any CUDA call
+    rc = cabi.lib.kivi_quantize_keys_per_channel(None, 0, None, None, None, 4, 32, 0, None)
+    assert rc == 1 and b"null" in cabi.lib.kivi_last_error()
+    rc = cabi.lib.kivi_dequantize_keys_per_channel(None, None, None, None, 4, 6, None)
+    assert rc == 1
+    assert cabi.lib.kivi_decode_attention_workspace(512, 4, 128, 0) == 512 * (128 + 8) * 4 * 130 * 4
+    assert cabi.lib.kivi_decode_attention_max_splits() == 128
+
+
+def test_unit_partition_covers_every_unit_once():
+    from intel_kivi_hybrid_b200.parallel import unit_partition
+    for n in (1, 7, 32, 512, 513):
+        for world in (1, 2, 4, 8):
+            parts = [unit_partition(n, r, world) for r in range(world)]
+            assert parts[0][0] == 0 and parts[-1][1] == n
+            assert all(parts[i][1] == parts[i + 1][0] for i in range(world - 1))
+            sizes = [b - a for a, b in parts]
+            assert max(sizes) - min(sizes) <= 1
+
+
+_GLOO_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from intel_kivi_hybrid_b200.parallel import all_gather_units, unit_partition
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo")
+for n_units in (8, 7):                       # equal and ragged shards
+    full = torch.arange(n_units * 3 * 4, dtype=torch.float32).reshape(n_units, 3, 4)
+    u0, u1 = unit_partition(n_units, rank, world)
+    got = all_gather_units(full[u0:u1].clone(), n_units, rank, world)
+    assert torch.equal(got, full), (rank, n_units)
+dist.barrier()
+dist.destroy_process_group()
+print("ok", rank)
+'''
+
+
+def test_all_gather_units_gloo_world2(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(_GLOO_WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29641", WORLD_SIZE="2")
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT], env=dict(env, RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=120)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    assert all("ok" in o for o in outs)
+
+
+def test_detect_model_config_families():
+    from intel_kivi_hybrid_b200.config.model_config import detect_model_config
+    mk = lambda **kw: types.SimpleNamespace(config=types.SimpleNamespace(**kw))
+    assert detect_model_config(mk(n_layer=12, n_head=12, n_embd=768)) == \
+        {"num_layers": 12, "num_kv_heads": 12, "head_dim": 64}                      # GPT-2
+    assert detect_model_config(mk(num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+                                  hidden_size=4096)) == {"num_layers": 32, "num_kv_heads": 8, "head_dim": 128}  # Llama-3-8B
+    assert detect_model_config(mk(num_hidden_layers=2, num_attention_heads=4, hidden_size=64, head_dim=32))["head_dim"] == 32
+    with pytest.raises(ValueError, match="num_layers"):
+        detect_model_config(mk(n_head=2, n_embd=8))
+    with pytest.raises(ValueError, match="head_dim"):
+        detect_model_config(mk(n_layer=2, n_head=2))
+
+
+def test_sample_token():
+    from intel_kivi_hybrid_b200.generation.sampling import sample_token
+    logits = torch.tensor([[0.1, 3.0, -1.0, 2.0], [5.0, 0.0, 0.0, 0.0]])
+    assert sample_token(logits, 1.0, None, False).tolist() == [[1], [0]]
+    torch.manual_seed(0)
+    for _ in range(20):
+        t = sample_token(logits.clone(), 0.7, 2, True)
+        assert t.shape == (2, 1) and t[0, 0].item() in (1, 3) and t[1, 0].item() in (0, 1, 2, 3)
+
+
+def test_drop_in_surface():
+    import kivi_cuda
+    import kivi_sycl
+    from kivi_sycl import KiviCache, generate, __version__
+    assert __version__ == "0.1.0" and kivi_cuda.KiviCache is KiviCache and callable(generate)
+    with pytest.raises(AssertionError, match="divisible by group_size"):
+        KiviCache(2, 48, group_size=32)
+    with pytest.raises(AssertionError, match="must not exceed residual_length"):
+        KiviCache(2, 64, group_size=64, residual_length=32)
+    with pytest.raises(AssertionError, match=">= 4 and divisible by 4"):
+        KiviCache(2, 64, group_size=2)
+    c = KiviCache(num_layers=3, head_dim=64, num_kv_heads=2, device="cuda", group_size=32, residual_length=128)
+    assert (c.G, c.R, c.num_layers, c.batch_size, c.total_flushes) == (32, 128, 3, None, 0)
+    assert c._quant_token_count == [0, 0, 0] and c.res_keys == [None, None, None]
+    assert repr(c) == "KiviCache(layers=3, head_dim=64, G=32, R=128, device='cuda')"
+    assert c.get_stats()["compression"] == 0
+    # the twelve operators + KiviEvent, with the reference's keyword names (pybind_module.cpp:18-81)
+    from kivi_sycl import _C
+    ops = ["quantize_keys", "quantize_values", "dequantize_keys", "dequantize_values",
+           "quant_dequant_roundtrip_keys", "quant_dequant_roundtrip_values"]
+    for op in ops:
+        assert callable(getattr(_C, op)) and callable(getattr(_C, op + "_async"))
+    assert hasattr(_C.KiviEvent, "wait")
+    doc = _C.quantize_values.__doc__
+    for kw in ("input", "output", "scales", "zeros", "head_dim", "group_size"):
+        assert kw + ":" in doc
+    x = torch.zeros(64)
+    with pytest.raises(RuntimeError, match="must be on cuda"):
+        _C.quant_dequant_roundtrip_keys(input=x, output=torch.zeros(64), group_size=32)
