@@ -185,7 +185,8 @@ def run_ours(args, wl):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
     sampler = ClockSampler(local) if rank == 0 else None     # started early: nvidia-smi needs a moment to come up
     dtype = torch.bfloat16
     path = {"auto": cabi.ATTN_AUTO, "fp32": cabi.ATTN_FP32, "mma": cabi.ATTN_MMA}[args.path]
@@ -283,20 +284,21 @@ def run_ours(args, wl):
         e2e_ms = float(t.item())
     e2e_val = world * by / (e2e_ms * 1e-3) / 1e9
 
+    # the timed region can be shorter than one polling period of nvidia-smi: every
+    # rank keeps the same step loop running (untimed) for about 1.2 s more -- the
+    # same number of steps everywhere, because a step holds a collective
     clocks = None
+    n_extra = int(min(20000, max(args.steps, 1.2e3 / max(ms_step, 1e-3))))
+    w0 = time.time()
+    for i in range(n_extra):
+        step(i)
+        if i % 200 == 199:
+            torch.cuda.synchronize()
+    barrier()
+    windows.append((w0, time.time()))
     if sampler is not None:
-        # the timed region can be shorter than one polling period: keep the same
-        # kernel loop running (untimed) until at least ~1.2 s of load was sampled
-        w0 = time.time()
-        i = 0
-        while time.time() - w0 < 1.2:
-            step(i); i += 1
-            if i % 50 == 0:
-                torch.cuda.synchronize()
-        torch.cuda.synchronize()
-        windows.append((w0, time.time()))
         clocks = sampler.stop(windows)
-        clocks["sampled"] = "timed region plus 1.2 s of the same step loop right after it"
+        clocks["sampled"] = "timed region plus ~1.2 s of the same step loop right after it"
     if rank == 0:
         peak, which = peaks()
         achieved = by / (statistics.median(per) * 1e-3) / 1e9
