@@ -197,6 +197,34 @@ int kivi_decode_attention(const kivi_layer* layer, int64_t quant_len, int res_st
                           int n_rep, float sm_scale, void* workspace, size_t workspace_bytes,
                           int num_splits, int path, void* stream);
 
+/* Decode attention for callers that cannot allocate device memory.
+ *
+ * No counterpart in the reference.  Some hosts of this library may not call
+ * cudaMalloc at all: an inference server that hands every byte of HBM to its own
+ * pool at start-up, a plug-in that runs inside another framework's memory plan,
+ * a latency-critical loop where an allocation (which may synchronise the
+ * device) is forbidden.  kivi_decode_attention needs a workspace from its
+ * caller; this variant needs none.  Its split partials live in a fixed array
+ * inside the library image (KIVI_NOALLOC_SCRATCH_BYTES, present on every GPU
+ * that loads the library, for as long as the process lives), and the call
+ * itself performs no cudaMalloc, cudaFree or any other allocating call.
+ *
+ * Same arguments and result as kivi_decode_attention minus the workspace.
+ * Limit: num_units * (splits + residual parts) * n_rep * (head_dim + 2) * 4
+ * bytes must fit in the array; a larger problem is refused with
+ * KIVI_ERR_INVALID_ARGUMENT and a message naming the limit (pass a smaller
+ * num_splits, or use kivi_decode_attention with your own workspace).
+ * The first call on each device looks up the array's device address (no
+ * allocation, but make that first call before starting a stream capture).
+ * All calls on a device share the one array and nothing in it needs to start
+ * at zero -- every slot that is read has been written by the same call -- but
+ * two calls whose kernels overlap on the GPU (different streams, different
+ * threads) would overwrite each other's partials: serialise them. */
+#define KIVI_NOALLOC_SCRATCH_BYTES (8u << 20)
+int kivi_decode_attention_noalloc(const kivi_layer* layer, int64_t quant_len, int res_start,
+                                  int res_len, const void* q, int q_dtype, void* out, int out_dtype,
+                                  int n_rep, float sm_scale, int num_splits, int path, void* stream);
+
 /* Reads (and synchronises with) the device fault word: non-zero once any wait
  * inside a kernel of this library ran out (a bulk copy that never completed).
  * Such a kernel returns normally and reports the affected split as empty. */

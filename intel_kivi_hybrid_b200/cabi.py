@@ -47,6 +47,8 @@ SIGNATURES = {
     "kivi_cache_import_keys": (_int, [_c.POINTER(Layer), _vp, _vp, _vp, _i64, _vp]),
     "kivi_decode_attention_workspace": (_c.c_size_t, [_int, _int, _int, _int]),
     "kivi_decode_attention_max_splits": (_int, []),
+    "kivi_decode_attention_noalloc": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _int, _vp, _int, _int, _f,
+                                             _int, _int, _vp]),
     "kivi_decode_attention": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _int, _vp, _int, _int, _f,
                                      _vp, _c.c_size_t, _int, _int, _vp]),
 }
@@ -220,6 +222,17 @@ class LayerStore:
         _check(lib.kivi_decode_attention(_c.byref(self.c), self.quant_len, self.res_start, self.res_len,
                                          q.data_ptr(), _dt(q), out.data_ptr(), _dt(out), n_rep, float(sm_scale),
                                          ws.data_ptr(), ws.numel(), num_splits, path, _stream()))
+        return out
+
+    def attention_noalloc(self, q, out, n_rep, sm_scale=0.0, num_splits=0, path=ATTN_AUTO):
+        """kivi_decode_attention_noalloc: same result as attention(), with the
+        split partials in the library's built-in scratch array instead of a
+        workspace tensor.  `out` must be preallocated by the caller: nothing is
+        allocated on this path."""
+        _dev(q, out)
+        _check(lib.kivi_decode_attention_noalloc(_c.byref(self.c), self.quant_len, self.res_start, self.res_len,
+                                                 q.data_ptr(), _dt(q), out.data_ptr(), _dt(out), n_rep,
+                                                 float(sm_scale), num_splits, path, _stream()))
         return out
 
 

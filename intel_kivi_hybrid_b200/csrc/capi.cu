@@ -4,6 +4,8 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "kivi_common.cuh"
 
 namespace kivi {
@@ -218,4 +220,47 @@ extern "C" int kivi_decode_attention(const kivi_layer* L, int64_t quant_len, int
     KIVI_LAUNCH_OK();
     note_launches(2);
     return KIVI_OK;
+}
+
+// ---- decode attention without a caller workspace --------------------------------
+// The split partials of this entry point live in a fixed array in the library
+// image instead of caller memory, for hosts that may not allocate (see the
+// header).  `g_noalloc_scratch` is a device symbol: in host code the name is not
+// a device address, so the address is looked up once per device with
+// cudaGetSymbolAddress and cached.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[KIVI_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+}  // namespace
+
+extern "C" int kivi_decode_attention_noalloc(const kivi_layer* L, int64_t quant_len, int res_start,
+                                             int res_len, const void* q, int q_dtype, void* out,
+                                             int out_dtype, int n_rep, float sm_scale, int num_splits,
+                                             int path, void* stream) {
+    int dev = 0;
+    KIVI_CUDA_OK(cudaGetDevice(&dev));
+    KIVI_REQUIRE(dev >= 0 && dev < kMaxDevices, "device index %d outside 0..%d", dev, kMaxDevices - 1);
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (g_noalloc_ptr[dev] == nullptr) {
+            void* p = nullptr;
+            KIVI_CUDA_OK(cudaGetSymbolAddress(&p, g_noalloc_scratch));   // this device's copy of the array
+            g_noalloc_ptr[dev] = p;
+        }
+        scratch = g_noalloc_ptr[dev];
+    }
+    const int rc = kivi_decode_attention(L, quant_len, res_start, res_len, q, q_dtype, out, out_dtype, n_rep,
+                                         sm_scale, scratch, (size_t)KIVI_NOALLOC_SCRATCH_BYTES, num_splits, path, stream);
+    if (rc == KIVI_ERR_INVALID_ARGUMENT && strstr(g_err, "workspace too small") != nullptr) {
+        char detail[256];
+        snprintf(detail, sizeof(detail), "%s", g_err);
+        set_error("problem too large for the built-in scratch of kivi_decode_attention_noalloc (%u bytes): %s; "
+                  "pass a smaller num_splits or call kivi_decode_attention with your own workspace",
+                  (unsigned)KIVI_NOALLOC_SCRATCH_BYTES, detail);
+    }
+    return rc;
 }
