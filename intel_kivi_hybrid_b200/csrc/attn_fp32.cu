@@ -243,6 +243,10 @@ merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ 
                     void* __restrict__ out, int out_dtype, int n_splits, int D) {
     extern __shared__ float w_s[];                   // [n_splits] weights
     __shared__ float denom_s;
+    // launched with programmatic stream serialization: everything above may
+    // overlap the tail of the attention kernel, the partials may not be read
+    // before that kernel has completed
+    cudaGridDependencySynchronize();
     const int u = blockIdx.x, h = blockIdx.y, nrep = gridDim.y;
     const int64_t row0 = (int64_t)u * n_splits * nrep + h;   // + s*nrep
     float M = -INFINITY;

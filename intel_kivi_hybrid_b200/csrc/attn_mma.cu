@@ -45,11 +45,11 @@ constexpr int kD = 128, kG = 32;
 #ifndef KIVI_MMA_STAGES
 #define KIVI_MMA_STAGES 2
 #endif
-#ifndef KIVI_MMA_UNROLL_HALVES
-#define KIVI_MMA_UNROLL_HALVES 2     /* 2 = fully unrolled (fastest), 1 = keep the two halves as loops */
+#ifndef KIVI_MMA_JOINT
+#define KIVI_MMA_JOINT 1            /* 1: both groups of a stage share one softmax update */
 #endif
-#ifndef KIVI_MMA_Q_SMEM
-#define KIVI_MMA_Q_SMEM 0
+#ifndef KIVI_MMA_CHAINS
+#define KIVI_MMA_CHAINS 2           /* independent accumulator chains per q.k tile */
 #endif
 #ifndef KIVI_MMA_MIN_CTAS
 #define KIVI_MMA_MIN_CTAS 3
@@ -60,9 +60,6 @@ constexpr int kStages = KIVI_MMA_STAGES;
 constexpr int kGroupBytes = 4096;      // kc 1024 | ks 512 | kz 512 | vc 1024 | vs 512 | vz 512
 constexpr int kStageBytes = kGPS * kGroupBytes;
 constexpr uint32_t kSpinLimit = 1u << 22;
-// distance in floats between the query vectors of consecutive k-steps of a lane
-constexpr int kQStride = KIVI_MMA_Q_SMEM ? 16 : 4;
-constexpr int kUnrollHalves = KIVI_MMA_UNROLL_HALVES;
 
 __device__ int g_fault_word = 0;
 
@@ -139,17 +136,18 @@ struct WarpState {
     float oz[4];           // zero-point term, head gid>>1, partial over lanes
 };
 
-// One token group (32 tokens) from shared memory.
-__device__ __forceinline__ void process_group(
+// ---- one token group (32 tokens) in three phases ----------------------------------
+// q.k: scores of the lane's four tokens (gid + 8e) for head `tig`, log2 domain.
+__device__ __forceinline__ void qk_phase(
     const uint8_t* __restrict__ kc, const float* __restrict__ ks, const float* __restrict__ kz,
-    const uint8_t* __restrict__ vc, const float* __restrict__ vs, const float* __restrict__ vz,
-    const float* __restrict__ qreg /* 32 values of this lane: registers or shared memory */,
-    uint32_t part_mask, float keep, int part, int gid, int tig, int lane,
-    WarpState& st) {
-    // ---------------- q.k ----------------
-    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* __restrict__ qreg, uint32_t part_mask, int gid, int tig, float (&s)[4]) {
+    float c0[KIVI_MMA_CHAINS][4], c1[KIVI_MMA_CHAINS][4];
+#pragma unroll
+    for (int ch_ = 0; ch_ < KIVI_MMA_CHAINS; ++ch_)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { c0[ch_][i] = 0.f; c1[ch_][i] = 0.f; }
     float qz = 0.0f;
-#pragma unroll kUnrollHalves
+#pragma unroll
     for (int qh = 0; qh < 2; ++qh) {
         const uint4 wv = *reinterpret_cast<const uint4*>(kc + qh * 512 + gid * 64 + tig * 16);
         const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
@@ -159,7 +157,7 @@ __device__ __forceinline__ void process_group(
             const int ch = 64 * qh + 16 * m + 4 * tig;
             const float4 s4 = *reinterpret_cast<const float4*>(ks + ch);
             const float4 z4 = *reinterpret_cast<const float4*>(kz + ch);
-            const float4 q4 = *reinterpret_cast<const float4*>(qreg + kQStride * kt);
+            const float4 q4 = *reinterpret_cast<const float4*>(qreg + 4 * kt);
             const float x0 = q4.x * s4.x, x1 = q4.y * s4.y, x2 = q4.z * s4.z, x3 = q4.w * s4.w;
             qz = fmaf(q4.x, z4.x, qz); qz = fmaf(q4.y, z4.y, qz);
             qz = fmaf(q4.z, z4.z, qz); qz = fmaf(q4.w, z4.w, qz);
@@ -174,21 +172,33 @@ __device__ __forceinline__ void process_group(
             const uint32_t we = w[m], wo = w[m] >> 8;
             uint32_t a[4];
             a[0] = code_pair<0>(we); a[1] = code_pair<1>(we); a[2] = code_pair<0>(wo); a[3] = code_pair<1>(wo);
-            mma_f16(c0, a, b0, b1);
+            mma_f16(c0[kt % KIVI_MMA_CHAINS], a, b0, b1);
             a[0] = code_pair<2>(we); a[1] = code_pair<3>(we); a[2] = code_pair<2>(wo); a[3] = code_pair<3>(wo);
-            mma_f16(c1, a, b0, b1);
+            mma_f16(c1[kt % KIVI_MMA_CHAINS], a, b0, b1);
         }
     }
+#if KIVI_MMA_CHAINS == 2
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { c0[0][i] += c0[1][i]; c1[0][i] += c1[1][i]; }
+#endif
     // zero term of head gid>>1 (both lanes of a gid pair hold the same partial)
     qz += __shfl_xor_sync(0xffffffffu, qz, 1);
     qz += __shfl_xor_sync(0xffffffffu, qz, 2);
     const float qz_t = __shfl_sync(0xffffffffu, qz, 8 * tig);
-    float s[4];
-    s[0] = fmaf(c0[0] + c0[1], kRow0, qz_t);   // token gid
-    s[1] = fmaf(c0[2] + c0[3], kRow1, qz_t);   // token gid + 8
-    s[2] = fmaf(c1[0] + c1[1], kRow2, qz_t);   // token gid + 16
-    s[3] = fmaf(c1[2] + c1[3], kRow3, qz_t);   // token gid + 24
-    float gmax = fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3]));
+    s[0] = fmaf(c0[0][0] + c0[0][1], kRow0, qz_t);   // token gid
+    s[1] = fmaf(c0[0][2] + c0[0][3], kRow1, qz_t);   // token gid + 8
+    s[2] = fmaf(c1[0][0] + c1[0][1], kRow2, qz_t);   // token gid + 16
+    s[3] = fmaf(c1[0][2] + c1[0][3], kRow3, qz_t);   // token gid + 24
+}
+
+// running max / sum update for NG groups at once; turns scores into weights
+template <int NG>
+__device__ __forceinline__ void softmax_phase(float (&s)[NG][4], int gid, int lane, WarpState& st) {
+    float gmax = -INFINITY;
+#pragma unroll
+    for (int g = 0; g < NG; ++g)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) gmax = fmaxf(gmax, s[g][e]);
     gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, 4));
     gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, 8));
     gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, 16));
@@ -205,12 +215,17 @@ __device__ __forceinline__ void process_group(
 #pragma unroll
         for (int gd = 0; gd < 4; ++gd) st.oz[gd] *= alpha_b;
     }
-    float p[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) { p[e] = ex2(s[e] - st.m); st.l += p[e]; }
+    for (int g = 0; g < NG; ++g)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { s[g][e] = ex2(s[g][e] - st.m); st.l += s[g][e]; }
+}
 
-    // ---------------- p.v ----------------
-#pragma unroll kUnrollHalves
+// p.v of one group; p[e] = weight of token gid + 8e for head tig
+__device__ __forceinline__ void pv_phase(
+    const uint8_t* __restrict__ vc, const float* __restrict__ vs, const float* __restrict__ vz,
+    const float (&p)[4], int part, int gid, int tig, WarpState& st) {
+#pragma unroll
     for (int kap = 0; kap < 2; ++kap) {
         const int tok0 = 4 * kap + tig;                 // tokens tok0 + 8e, e = 0..3
         const int src = 4 * tok0 + (gid >> 1);          // lane holding their p for head gid>>1
@@ -230,8 +245,8 @@ __device__ __forceinline__ void process_group(
             st.oz[2] = fmaf(pa, za.z, fmaf(pb, zb.z, st.oz[2]));
             st.oz[3] = fmaf(pa, za.w, fmaf(pb, zb.w, st.oz[3]));
         }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) pe[e] *= keep;      // p on hi lanes, 0 on lo lanes
+        // lo lanes feed the odd B columns with the same p*s: those columns of the
+        // accumulators are never read
         const uint8_t* vrow = vc + tok0 * 32 + gid;
 #pragma unroll
         for (int gd = 0; gd < 4; ++gd) {
@@ -250,6 +265,25 @@ __device__ __forceinline__ void process_group(
             mma_f16(st.o[2 * gd + 1], a, b0, b1);
         }
     }
+}
+
+// NG consecutive token groups of one pipeline stage, processed together: the
+// q.k and p.v phases of the groups are independent instruction streams, the
+// softmax update is done once for all NG*32 tokens.
+template <int NG>
+__device__ __forceinline__ void process_groups(
+    const uint8_t* __restrict__ sb, int g0, const float* __restrict__ qreg, uint32_t part_mask,
+    int part, int gid, int tig, int lane, WarpState& st) {
+    float s[NG][4];
+#pragma unroll
+    for (int g = 0; g < NG; ++g)
+        qk_phase(sb + (g0 + g) * 1024, reinterpret_cast<const float*>(sb + kGPS * 1024 + (g0 + g) * 512),
+                 reinterpret_cast<const float*>(sb + kGPS * 1536 + (g0 + g) * 512), qreg, part_mask, gid, tig, s[g]);
+    softmax_phase<NG>(s, gid, lane, st);
+#pragma unroll
+    for (int g = 0; g < NG; ++g)
+        pv_phase(sb + kGPS * 2048 + (g0 + g) * 1024, reinterpret_cast<const float*>(sb + kGPS * 3072 + (g0 + g) * 512),
+                 reinterpret_cast<const float*>(sb + kGPS * 3584 + (g0 + g) * 512), s[g], part, gid, tig, st);
 }
 
 // ---- residual ring: full-precision tokens ---------------------------------------
@@ -395,8 +429,6 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + kWarps * kStages * kStageBytes);  // [kWarps][kStages]
     float* ml_s = reinterpret_cast<float*>(bars + kWarps * kStages);             // [kWarps][4][2]
     float* o_s = ml_s + kWarps * 4 * 2;                                          // [4][128]
-    float* q_sh = o_s + 4 * kD;                                                  // [4][128] (KIVI_MMA_Q_SMEM)
-    (void)q_sh;
 
     const int u = blockIdx.y;
     const int n_splits_total = nq_splits + n_res_splits;
@@ -503,16 +535,6 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
 
     // query registers: channel 64*qh + 16*m + 4*tig + i at index 16*qh + 4*m + i,
     // head hB, pre-multiplied by sm_scale * log2(e)
-#if KIVI_MMA_Q_SMEM
-    // shared [4 heads][8 k-steps][4 tig][4]: the lane's 4 channels of a k-step are one vector
-    for (int i = threadIdx.x; i < 4 * kD; i += blockDim.x) {
-        const int h = i >> 7, kt = (i >> 4) & 7, tg = (i >> 2) & 3, e = i & 3;
-        const int ch = 64 * (kt >> 2) + 16 * (kt & 3) + 4 * tg + e;
-        q_sh[i] = h < n_rep ? scale_log2 * load_as_float(q, q_dtype, ((int64_t)u * n_rep + h) * kD + ch) : 0.0f;
-    }
-    __syncthreads();
-    const float* qreg = q_sh + hB * 128 + tig * 4;
-#else
     __align__(16) float qreg[32];
     {
         const float f = scale_log2;
@@ -522,9 +544,7 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
             qreg[r] = hB < n_rep ? f * load_as_float(q, q_dtype, ((int64_t)u * n_rep + hB) * kD + ch) : 0.0f;
         }
     }
-#endif
     const uint32_t part_mask = part ? 0xffffe000u : 0u;   // keep 11 significant bits
-    const float keep = part ? 0.0f : 1.0f;
 
     WarpState st;
     st.m = -INFINITY; st.l = 0.0f;
@@ -544,15 +564,17 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
         const int64_t g0 = g_begin + (int64_t)(warp + kWarps * i) * kGPS;
         const int ng = (int)((g_end - g0) < kGPS ? (g_end - g0) : kGPS);
         const uint8_t* sb = wstage + s * kStageBytes;
-        for (int gi = 0; gi < ng; ++gi) {
-            process_group(sb + gi * 1024,
-                          reinterpret_cast<const float*>(sb + kGPS * 1024 + gi * 512),
-                          reinterpret_cast<const float*>(sb + kGPS * 1536 + gi * 512),
-                          sb + kGPS * 2048 + gi * 1024,
-                          reinterpret_cast<const float*>(sb + kGPS * 3072 + gi * 512),
-                          reinterpret_cast<const float*>(sb + kGPS * 3584 + gi * 512),
-                          qreg, part_mask, keep, part, gid, tig, lane, st);
+#if KIVI_MMA_JOINT
+        static_assert(kGPS == 2, "joint processing is written for two groups per stage");
+        if (ng == 2) {
+            process_groups<2>(sb, 0, qreg, part_mask, part, gid, tig, lane, st);
+        } else {
+            process_groups<1>(sb, 0, qreg, part_mask, part, gid, tig, lane, st);
         }
+#else
+        for (int gi = 0; gi < ng; ++gi)
+            process_groups<1>(sb, gi, qreg, part_mask, part, gid, tig, lane, st);
+#endif
         __syncwarp();
         if (lane == 0 && i + kStages < my_n) issue(i + kStages);
     }
@@ -591,8 +613,8 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
                 const int ch = 32 * gd + 4 * gid + 2 * (mt & 1);
                 // rows gid / gid+8 hold code index 2*(mt&1) / 2*(mt&1)+1 of their byte
                 const float r0 = (mt & 1) ? kRow2 : kRow0, r1 = (mt & 1) ? kRow3 : kRow1;
-                o_s[tig * kD + ch] += f * fmaf(st.o[mt][0] + st.o[mt][1], r0, ozt[gd]);
-                o_s[tig * kD + ch + 1] += f * fmaf(st.o[mt][2] + st.o[mt][3], r1, ozt[gd]);
+                o_s[tig * kD + ch] += f * fmaf(st.o[mt][0], r0, ozt[gd]);       // odd columns unused
+                o_s[tig * kD + ch + 1] += f * fmaf(st.o[mt][2], r1, ozt[gd]);
             }
         }
         __syncthreads();
@@ -614,7 +636,7 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
 }
 
 constexpr size_t kSmemBytes = (size_t)kWarps * kStages * kStageBytes + kWarps * kStages * 8 +
-                              kWarps * 4 * 2 * 4 + 4 * kD * 4 + (KIVI_MMA_Q_SMEM ? 4 * kD * 4 : 0);
+                              kWarps * 4 * 2 * 4 + 4 * kD * 4;
 
 }  // namespace
 

@@ -215,9 +215,23 @@ extern "C" int kivi_decode_attention(const kivi_layer* L, int64_t quant_len, int
         ? run_attn_mma(L, quant_len, res_start, res_len, q, q_dtype, n_rep, scale_log2, nq_splits, gps, n_res_splits, res_chunk, part_o, part_ml, st)
         : run_attn_fp32(L, quant_len, res_start, res_len, q, q_dtype, n_rep, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st);
     if (rc) return rc;
-    dim3 grid((unsigned)L->num_units, (unsigned)n_rep);
-    merge_splits_kernel<<<grid, D >= 256 ? 256 : 128, n_splits * sizeof(float), st>>>(part_o, part_ml, out, out_dtype, n_splits, D);
-    KIVI_LAUNCH_OK();
+    {
+        // the merge is queued behind the attention kernel with programmatic stream
+        // serialization, so its launch latency overlaps that kernel's tail
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)L->num_units, (unsigned)n_rep);
+        cfg.blockDim = dim3(D >= 256 ? 256 : 128);
+        cfg.dynamicSmemBytes = n_splits * sizeof(float);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const float* po = part_o;
+        const float* pm = part_ml;
+        KIVI_CUDA_OK(cudaLaunchKernelEx(&cfg, merge_splits_kernel, po, pm, out, out_dtype, n_splits, D));
+    }
     note_launches(2);
     return KIVI_OK;
 }
