@@ -332,17 +332,61 @@ def run_ours(args, wl):
         dist.destroy_process_group()
 
 
+def run_quantize(args):
+    """--workload cfg4: bulk prefill flush (BASELINE configs[4]): B=8, 32 KV heads,
+    D=128, 8192 tokens quantized in one kivi_cache_update call per layer (keys per
+    channel over 32-token groups, values per token over 32-channel groups)."""
+    from intel_kivi_hybrid_b200 import cabi
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    U, S, D, G, R = 8 * 32, 8192, 128, 32, 128
+    res = {}
+    for name, dtype, eb in (("f32", torch.float32, 4), ("bf16", torch.bfloat16, 2)):
+        k, v = make_unit_tensors(8, 32, S, D, 77, dev, dtype)
+        st = cabi.LayerStore(U, D, G, R, S, dtype, dev)
+        n_flush, ql, rl = cabi.cache_plan(0, 0, S, G, R)
+        by = 2 * U * (ql * D * eb + ql * D // 4 + (ql * D // G) * 8) + 2 * U * rl * D * eb * 2
+        for _ in range(max(3, args.warmup)):
+            st.reset(); st.update(k, v)
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+        ev[0].record()
+        for i in range(args.steps):
+            st.reset(); st.update(k, v)
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
+        res[name] = {"ms": statistics.median(per), "gbs": by / (statistics.median(per) * 1e-3) / 1e9, "bytes": by,
+                     "launches": cabi.lib.kivi_last_launch_count()}
+        del k, v, st
+        torch.cuda.empty_cache()
+    peak, which = peaks()
+    line = {"metric": "kivi_quantize_pack_gbs", "value": res["bf16"]["gbs"], "unit": "GB/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["bf16"]["ms"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "cfg4", "units": U, "tokens": S, "D": D, "G": G, "R": R,
+                       "l2": "inputs larger than L2 (1.07 GB per tensor)"},
+            "f32": res["f32"], "bf16": res["bf16"],
+            "roofline": {"bound": "hbm", "achieved": res["bf16"]["gbs"], "peak": peak, "unit": "GB/s",
+                         "frac": res["bf16"]["gbs"] / peak, "frac_f32": res["f32"]["gbs"] / peak, "peak_source": which,
+                         "traffic": None},
+            "gpu_launches": args.steps * res["bf16"]["launches"]}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["cfg4"])
     ap.add_argument("--path", default="auto", choices=["auto", "fp32", "mma"])
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
+    if args.workload == "cfg4":
+        return run_quantize(args)
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, wl)

@@ -34,6 +34,22 @@ __device__ __forceinline__ float src_load(const TokenSource& s, int u, int64_t t
     return load_as_float(s.fresh, s.fresh_dtype, (int64_t)u * s.unit_stride + (tau - s.res_len) * s.tok_stride + d);
 }
 
+template <typename T> struct Load8;
+template <> struct Load8<float> {
+    __device__ static void run(const float* p, float (&v)[8]) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+};
+template <> struct Load8<__nv_bfloat16> {
+    __device__ static void run(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 t = __ldg(reinterpret_cast<const uint4*>(p));
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+    }
+};
+
 // Keys of one token group of one unit: thread d owns channel d, reads the G
 // tokens of its channel (a warp reads 32 consecutive channels of one token per
 // instruction), quantizes them over the token axis, and the CTA writes one key
@@ -63,15 +79,16 @@ flush_keys_kernel(TokenSource src, uint8_t* __restrict__ k_codes, float* __restr
             }
         }
         const float scale = group_scale(mn, mx);
+        const float rcp = group_rcp(scale);
         k_scales[((int64_t)u * max_groups + g) * D + d] = scale;
         k_zeros[((int64_t)u * max_groups + g) * D + d] = mn;
         if (GT > 0) {
 #pragma unroll
             for (int j = 0; j < GT / 4; ++j) {
-                float q0 = code_of<HALF_EVEN>(x[j], mn, scale);
-                float q1 = code_of<HALF_EVEN>(x[j + GT / 4], mn, scale);
-                float q2 = code_of<HALF_EVEN>(x[j + 2 * (GT / 4)], mn, scale);
-                float q3 = code_of<HALF_EVEN>(x[j + 3 * (GT / 4)], mn, scale);
+                float q0 = code_of<HALF_EVEN>(x[j], mn, scale, rcp);
+                float q1 = code_of<HALF_EVEN>(x[j + GT / 4], mn, scale, rcp);
+                float q2 = code_of<HALF_EVEN>(x[j + 2 * (GT / 4)], mn, scale, rcp);
+                float q3 = code_of<HALF_EVEN>(x[j + 3 * (GT / 4)], mn, scale, rcp);
                 s_block[kblock_offset(d, j, Q, W)] =
                     (uint8_t)__float2int_rn(fmaf(q3, 64.0f, fmaf(q2, 16.0f, fmaf(q1, 4.0f, q0))));
             }
@@ -79,7 +96,7 @@ flush_keys_kernel(TokenSource src, uint8_t* __restrict__ k_codes, float* __restr
             for (int j = 0; j < Q; ++j) {
                 uint32_t byte = 0;
                 for (int e = 0; e < 4; ++e) {
-                    float q = code_of<HALF_EVEN>(src_load(src, u, tau0 + j + e * Q, d), mn, scale);
+                    float q = code_of<HALF_EVEN>(src_load(src, u, tau0 + j + e * Q, d), mn, scale, rcp);
                     byte |= (uint32_t)__float2int_rn(q) << (2 * e);
                 }
                 s_block[kblock_offset(d, j, Q, W)] = (uint8_t)byte;
@@ -95,6 +112,60 @@ flush_keys_kernel(TokenSource src, uint8_t* __restrict__ k_codes, float* __restr
     } else {
         for (int i = threadIdx.x; i < block_bytes; i += blockDim.x) dst[i] = s_block[i];
     }
+}
+
+// Keys, fast path for D = 128, G = 32: the CTA stages the 32-token x 128-channel
+// tile of its group in shared memory with 128-bit loads (a token row is
+// contiguous in both sources), then thread d walks column d (conflict-free:
+// a warp reads 32 consecutive elements of one row), quantizes it over the 32
+// tokens and the CTA writes one key block with 128-bit stores.
+template <typename TR, typename TF, bool HALF_EVEN>
+__global__ void __launch_bounds__(128)
+flush_keys_fast_kernel(TokenSource src, uint8_t* __restrict__ k_codes, float* __restrict__ k_scales,
+                       float* __restrict__ k_zeros, int64_t max_groups, int64_t group0) {
+    constexpr int D = 128, G = 32, Q = 8;
+    __shared__ __align__(16) float s_tile[G][D + 4];     // +4: rows start 16 bytes apart in bank space
+    __shared__ __align__(16) uint8_t s_block[D * Q];
+    const int u = blockIdx.y;
+    const int64_t g = group0 + blockIdx.x;
+    const int64_t tau0 = (int64_t)blockIdx.x * G;
+    // 32 rows x 16 pieces of 8 elements = 512 pieces, 4 per thread
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        const int piece = it * 128 + threadIdx.x;
+        const int t = piece >> 4, c = (piece & 15) * 8;
+        const int64_t tau = tau0 + t;
+        float v[8];
+        if (tau < src.res_len) {
+            const int slot = (int)((src.res_start + tau) % src.R);
+            Load8<TR>::run(reinterpret_cast<const TR*>(src.ring) + ((int64_t)u * src.R + slot) * D + c, v);
+        } else {
+            Load8<TF>::run(reinterpret_cast<const TF*>(src.fresh) + (int64_t)u * src.unit_stride +
+                               (tau - src.res_len) * src.tok_stride + c, v);
+        }
+        *reinterpret_cast<float4*>(&s_tile[t][c]) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(&s_tile[t][c + 4]) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    __syncthreads();
+    const int d = threadIdx.x;
+    float x[G];
+    float mn = 1e30f, mx = -1e30f;
+#pragma unroll
+    for (int t = 0; t < G; ++t) { x[t] = s_tile[t][d]; mn = fminf(mn, x[t]); mx = fmaxf(mx, x[t]); }
+    const float scale = group_scale(mn, mx);
+    const float rcp = group_rcp(scale);
+    k_scales[((int64_t)u * max_groups + g) * D + d] = scale;
+    k_zeros[((int64_t)u * max_groups + g) * D + d] = mn;
+#pragma unroll
+    for (int j = 0; j < Q; ++j) {
+        const float q0 = code_of<HALF_EVEN>(x[j], mn, scale, rcp), q1 = code_of<HALF_EVEN>(x[j + Q], mn, scale, rcp);
+        const float q2 = code_of<HALF_EVEN>(x[j + 2 * Q], mn, scale, rcp), q3 = code_of<HALF_EVEN>(x[j + 3 * Q], mn, scale, rcp);
+        s_block[kblock_offset(d, j, Q, 64)] = (uint8_t)__float2int_rn(fmaf(q3, 64.0f, fmaf(q2, 16.0f, fmaf(q1, 4.0f, q0))));
+    }
+    __syncthreads();
+    uint8_t* dst = k_codes + ((int64_t)u * max_groups + g) * (D * Q);
+    if (threadIdx.x < 64)
+        *reinterpret_cast<uint4*>(dst + threadIdx.x * 16) = *reinterpret_cast<const uint4*>(s_block + threadIdx.x * 16);
 }
 
 // Values: one thread per (token, channel group); groups of G consecutive
@@ -117,6 +188,7 @@ flush_values_kernel(TokenSource src, uint8_t* __restrict__ v_codes, float* __res
         mn = fminf(mn, v); mx = fmaxf(mx, v);
     }
     const float scale = group_scale(mn, mx);
+        const float rcp = group_rcp(scale);
     const int64_t t = tok0 + tau;
     v_scales[((int64_t)u * max_tokens + t) * ng + gd] = scale;
     v_zeros[((int64_t)u * max_tokens + t) * ng + gd] = mn;
@@ -125,10 +197,65 @@ flush_values_kernel(TokenSource src, uint8_t* __restrict__ v_codes, float* __res
         uint32_t byte = 0;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            float q = code_of<HALF_EVEN>(src_load(src, u, tau, gd * G + i + e), mn, scale);
+            float q = code_of<HALF_EVEN>(src_load(src, u, tau, gd * G + i + e), mn, scale, rcp);
             byte |= (uint32_t)__float2int_rn(q) << (2 * e);
         }
         dst[i / 4] = (uint8_t)byte;
+    }
+}
+
+// Values, fast path for D = 128, G = 32: four consecutive lanes share one
+// (token, channel group); each lane owns 8 consecutive channels (one or two
+// 128-bit loads), min/max finish with two xor-shuffles, a lane writes its two
+// packed bytes, lane 0 of the four the scale and zero.  A warp covers two
+// tokens, a CTA of 256 threads 16 tokens per iteration.
+template <typename TR, typename TF, bool HALF_EVEN>
+__global__ void __launch_bounds__(256)
+flush_values_fast_kernel(TokenSource src, uint8_t* __restrict__ v_codes, float* __restrict__ v_scales,
+                         float* __restrict__ v_zeros, int64_t max_tokens, int64_t tok0, int64_t n_tok) {
+    constexpr int D = 128, G = 32, ITER = 4;
+    const int u = blockIdx.y;
+    const int lane16 = threadIdx.x & 15;                 // 16 lanes per token
+    const int sub = lane16 & 3, gd = lane16 >> 2;
+    float v[ITER][8];
+    int64_t tau[ITER];
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+        tau[it] = ((int64_t)blockIdx.x * ITER + it) * 16 + (threadIdx.x >> 4);
+        if (tau[it] < n_tok) {
+            if (tau[it] < src.res_len) {
+                const int slot = (int)((src.res_start + tau[it]) % src.R);
+                Load8<TR>::run(reinterpret_cast<const TR*>(src.ring) + ((int64_t)u * src.R + slot) * D + lane16 * 8, v[it]);
+            } else {
+                Load8<TF>::run(reinterpret_cast<const TF*>(src.fresh) + (int64_t)u * src.unit_stride +
+                                   (tau[it] - src.res_len) * src.tok_stride + lane16 * 8, v[it]);
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[it][e] = 0.0f;
+        }
+    }
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+        float mn = 1e30f, mx = -1e30f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { mn = fminf(mn, v[it][e]); mx = fmaxf(mx, v[it][e]); }
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, 1)); mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, 2)); mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float scale = group_scale(mn, mx);
+        const float rcp = group_rcp(scale);
+        if (tau[it] < n_tok) {
+            uint32_t bytes = 0;
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                const float q0 = code_of<HALF_EVEN>(v[it][4 * b + 0], mn, scale, rcp), q1 = code_of<HALF_EVEN>(v[it][4 * b + 1], mn, scale, rcp);
+                const float q2 = code_of<HALF_EVEN>(v[it][4 * b + 2], mn, scale, rcp), q3 = code_of<HALF_EVEN>(v[it][4 * b + 3], mn, scale, rcp);
+                bytes |= (uint32_t)__float2int_rn(fmaf(q3, 64.0f, fmaf(q2, 16.0f, fmaf(q1, 4.0f, q0)))) << (8 * b);
+            }
+            const int64_t t = (int64_t)u * max_tokens + tok0 + tau[it];
+            *reinterpret_cast<uint16_t*>(v_codes + t * (D / 4) + lane16 * 2) = (uint16_t)bytes;
+            if (sub == 0) { v_scales[t * (D / G) + gd] = scale; v_zeros[t * (D / G) + gd] = mn; }
+        }
     }
 }
 
@@ -299,7 +426,22 @@ extern "C" int kivi_cache_update(const kivi_layer* L, int64_t quant_len, int res
         const int threads = D >= 256 ? 256 : (D >= 128 ? 128 : (D >= 64 ? 64 : 32));
         const size_t smem = (size_t)D * G / 4;
         const bool he = rounding == KIVI_ROUND_HALF_EVEN;
-        if (G == 32) {
+        auto al16k = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+        const int eszk = elem_size(new_dtype);
+        const bool fast_k = D == 128 && G == 32 && al16k(new_k) && al16k(L->k_res) && al16k(L->k_codes) &&
+                            (unit_stride_k * eszk) % 16 == 0 && (tok_stride_k * eszk) % 16 == 0;
+        if (fast_k) {
+#define KIVI_FK(TR, TF)                                                                                              \
+            do {                                                                                                     \
+                if (he) flush_keys_fast_kernel<TR, TF, true><<<grid, 128, 0, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0); \
+                else flush_keys_fast_kernel<TR, TF, false><<<grid, 128, 0, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0);   \
+            } while (0)
+            if (L->res_dtype == KIVI_F32 && new_dtype == KIVI_F32) KIVI_FK(float, float);
+            else if (L->res_dtype == KIVI_F32) KIVI_FK(float, __nv_bfloat16);
+            else if (new_dtype == KIVI_F32) KIVI_FK(__nv_bfloat16, float);
+            else KIVI_FK(__nv_bfloat16, __nv_bfloat16);
+#undef KIVI_FK
+        } else if (G == 32) {
             if (he) flush_keys_kernel<32, true><<<grid, threads, smem, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0, G);
             else flush_keys_kernel<32, false><<<grid, threads, smem, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0, G);
         } else {
@@ -308,10 +450,28 @@ extern "C" int kivi_cache_update(const kivi_layer* L, int64_t quant_len, int res
         }
         KIVI_LAUNCH_OK();
         const int64_t n_tok = (int64_t)f * G;
-        const int64_t items = n_tok * (D / G);
-        dim3 gridv((unsigned)((items + 255) / 256), (unsigned)L->num_units);
-        if (he) flush_values_kernel<true><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, n_tok, G);
-        else flush_values_kernel<false><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, n_tok, G);
+        auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+        const int esz = elem_size(new_dtype);
+        const bool fast_v = D == 128 && G == 32 && al16(new_v) && al16(L->v_res) &&
+                            (unit_stride_v * esz) % 16 == 0 && (tok_stride_v * esz) % 16 == 0;
+        if (fast_v) {
+            dim3 gridv((unsigned)((n_tok + 63) / 64), (unsigned)L->num_units);
+#define KIVI_FV(TR, TF)                                                                                              \
+            do {                                                                                                     \
+                if (he) flush_values_fast_kernel<TR, TF, true><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, n_tok); \
+                else flush_values_fast_kernel<TR, TF, false><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, n_tok);   \
+            } while (0)
+            if (L->res_dtype == KIVI_F32 && new_dtype == KIVI_F32) KIVI_FV(float, float);
+            else if (L->res_dtype == KIVI_F32) KIVI_FV(float, __nv_bfloat16);
+            else if (new_dtype == KIVI_F32) KIVI_FV(__nv_bfloat16, float);
+            else KIVI_FV(__nv_bfloat16, __nv_bfloat16);
+#undef KIVI_FV
+        } else {
+            const int64_t items = n_tok * (D / G);
+            dim3 gridv((unsigned)((items + 255) / 256), (unsigned)L->num_units);
+            if (he) flush_values_kernel<true><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, n_tok, G);
+            else flush_values_kernel<false><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, n_tok, G);
+        }
         KIVI_LAUNCH_OK();
         launches += 2;
     }

@@ -102,15 +102,16 @@ group_quant_kernel(const T* __restrict__ in, uint8_t* __restrict__ packed,
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         }
         const float scale = group_scale(mn, mx);
+        const float rcp = group_rcp(scale);
         const int64_t g = tile_g0 + lg[it];
         if (MODE == 0) {
             uint32_t bytes[(BPL + 3) / 4] = {};
 #pragma unroll
             for (int b = 0; b < BPL; ++b) {
-                float q0 = code_of<HALF_EVEN>(v[it][4 * b + 0], mn, scale);
-                float q1 = code_of<HALF_EVEN>(v[it][4 * b + 1], mn, scale);
-                float q2 = code_of<HALF_EVEN>(v[it][4 * b + 2], mn, scale);
-                float q3 = code_of<HALF_EVEN>(v[it][4 * b + 3], mn, scale);
+                float q0 = code_of<HALF_EVEN>(v[it][4 * b + 0], mn, scale, rcp);
+                float q1 = code_of<HALF_EVEN>(v[it][4 * b + 1], mn, scale, rcp);
+                float q2 = code_of<HALF_EVEN>(v[it][4 * b + 2], mn, scale, rcp);
+                float q3 = code_of<HALF_EVEN>(v[it][4 * b + 3], mn, scale, rcp);
                 // exact small integers: assemble the byte in fp32, convert once
                 uint32_t byte = (uint32_t)__float2int_rn(fmaf(q3, 64.0f, fmaf(q2, 16.0f, fmaf(q1, 4.0f, q0))));
                 bytes[b / 4] |= byte << (8 * (b % 4));
@@ -128,10 +129,10 @@ group_quant_kernel(const T* __restrict__ in, uint8_t* __restrict__ packed,
 #pragma unroll
             for (int k = 0; k < EPL / 4; ++k) {
                 float4 r;
-                r.x = dequant(code_of<HALF_EVEN>(v[it][4 * k + 0], mn, scale), scale, mn);
-                r.y = dequant(code_of<HALF_EVEN>(v[it][4 * k + 1], mn, scale), scale, mn);
-                r.z = dequant(code_of<HALF_EVEN>(v[it][4 * k + 2], mn, scale), scale, mn);
-                r.w = dequant(code_of<HALF_EVEN>(v[it][4 * k + 3], mn, scale), scale, mn);
+                r.x = dequant(code_of<HALF_EVEN>(v[it][4 * k + 0], mn, scale, rcp), scale, mn);
+                r.y = dequant(code_of<HALF_EVEN>(v[it][4 * k + 1], mn, scale, rcp), scale, mn);
+                r.z = dequant(code_of<HALF_EVEN>(v[it][4 * k + 2], mn, scale, rcp), scale, mn);
+                r.w = dequant(code_of<HALF_EVEN>(v[it][4 * k + 3], mn, scale, rcp), scale, mn);
                 reinterpret_cast<float4*>(o)[k] = r;
             }
         }
@@ -178,6 +179,7 @@ group_quant_generic_kernel(const void* __restrict__ in, int in_dtype, uint8_t* _
         mx = fmaxf(mx, x);
     }
     const float scale = group_scale(mn, mx);
+        const float rcp = group_rcp(scale);
     if (MODE == 0) {
         scales[g] = scale;
         zeros[g] = mn;
@@ -185,14 +187,14 @@ group_quant_generic_kernel(const void* __restrict__ in, int in_dtype, uint8_t* _
             uint32_t byte = 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                float q = code_of<HALF_EVEN>(load_as_float(in, in_dtype, base + i + j), mn, scale);
+                float q = code_of<HALF_EVEN>(load_as_float(in, in_dtype, base + i + j), mn, scale, rcp);
                 byte |= (uint32_t)__float2int_rn(q) << (2 * j);
             }
             packed[g * (G / 4) + i / 4] = (uint8_t)byte;
         }
     } else {
         for (int i = 0; i < G; ++i) {
-            float q = code_of<HALF_EVEN>(load_as_float(in, in_dtype, base + i), mn, scale);
+            float q = code_of<HALF_EVEN>(load_as_float(in, in_dtype, base + i), mn, scale, rcp);
             rt_out[base + i] = dequant(q, scale, mn);
         }
     }
