@@ -186,19 +186,22 @@ class KiviCache:
                 # view no longer matches (manager.py:244-249)
                 self._cache_view_valid = False
 
-    def decode_attention(self, layer: int, q: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    def decode_attention(self, layer: int, q: torch.Tensor, out_dtype=None, num_splits: int = 0) -> torch.Tensor:
         """Fused attention of one decode step over the packed cache of ``layer``:
         softmax(q K^T / sqrt(D)) V over [quantized history || residual window].
         q: [B, Hq, D] on the cache device; returns [B, Hq, D].  No dequantized
         cache is materialised (this replaces get_full_cache + the model's own
-        attention, generate.py:75-77, for callers that can hand over q)."""
+        attention, generate.py:75-77, for callers that can hand over q).
+        ``num_splits`` fixes how many pieces each unit's history is cut into
+        (0 = chosen from the problem size); with the same value a sharded and an
+        unsharded cache give bit-identical outputs."""
         st = self._stores[layer]
         assert st is not None, "decode_attention() before any add_tokens()"
         B, Hq, D = q.shape
         n_rep = Hq // self.num_kv_heads
         u0, u1 = self._units
         q_units = q.reshape(B * self.num_kv_heads, n_rep, D)[u0:u1].contiguous()
-        out = st.attention(q_units, n_rep=n_rep, out_dtype=out_dtype)
+        out = st.attention(q_units, n_rep=n_rep, out_dtype=out_dtype, num_splits=num_splits)
         if self.shard and self.shard[1] > 1:
             out = all_gather_units(out, B * self.num_kv_heads, self.shard[0], self.shard[1])
         return out.reshape(B, Hq, D)

@@ -1,0 +1,65 @@
+"""Sharded KiviCache on two GPUs (skipped when fewer are visible): every rank
+keeps half of the (batch, kv_head) units, the all-gathered decode-attention
+output must equal the single-GPU output bit for bit (same kernel, same number
+of splits per unit) and the oracle within tolerance.  Ranks are child processes over
+NCCL; each leaves only after its last collective has completed."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+_WORKER = r'''
+import os, sys, datetime, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from kivi_cuda import KiviCache
+from oracle import kivi_oracle as ko
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = f"cuda:{rank}"
+dist.init_process_group("nccl", device_id=torch.device(dev), timeout=datetime.timedelta(seconds=60))
+B, Hkv, n_rep, D, T = 2, 4, 4, 128, 650
+K = ko.make_keys(B, Hkv, T, D, 5).to(torch.bfloat16)
+V = ko.make_values(B, Hkv, T, D, 5).to(torch.bfloat16)
+q = ko.make_queries(B, Hkv * n_rep, D, 5).to(torch.bfloat16)
+sharded = KiviCache(num_layers=1, head_dim=D, device=dev, shard=(rank, world))
+single = KiviCache(num_layers=1, head_dim=D, device=dev)
+for c in (sharded, single):
+    c.add_tokens(((K[:, :, :T - 3].to(dev), V[:, :, :T - 3].to(dev)),))
+    c.add_tokens(((K.to(dev), V.to(dev)),))
+assert sharded._stores[0].num_units == B * Hkv // world
+out_s = sharded.decode_attention(0, q.to(dev), out_dtype=torch.float32, num_splits=3)
+out_1 = single.decode_attention(0, q.to(dev), out_dtype=torch.float32, num_splits=3)
+torch.cuda.synchronize()
+assert torch.equal(out_s, out_1), "sharded output differs from the single-GPU output"
+ref = ko.kivi_decode_attention(q, K, V, single._quant_token_count[0], 32, "half_away", dtype=torch.float64).float()
+err = ((out_s.cpu() - ref).abs().amax(-1) / ref.abs().amax(-1)).max().item()
+assert err < 2e-3, err
+dist.barrier()
+torch.cuda.synchronize()
+dist.destroy_process_group()
+print("ok", rank, err)
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_cache_equals_single_gpu(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29655", WORLD_SIZE="2",
+               NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT], env=dict(env, RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = []
+    for p in procs:
+        try:
+            outs.append(p.communicate(timeout=240)[0])
+        except subprocess.TimeoutExpired:
+            p.kill()
+            outs.append("timeout")
+    assert all(p.returncode == 0 for p in procs), outs
+    assert all("ok" in o for o in outs), outs
