@@ -99,14 +99,19 @@ int kivi_quant_dequant_roundtrip_values(const void* input, int in_dtype, float* 
  * Quantized store of one unit, token group g (tokens g*G .. g*G+G-1):
  *   k_codes  + (u*max_groups + g) * (D*G/4): one key block.  With Q = G/4 and
  *            W = min(D,64), the byte at  (d/W)*Q*W + j*W + p(d%W)  (0<=j<Q) holds
- *            the codes of channel d for tokens j, j+Q, j+2Q, j+3Q of the group
- *            in bits 0-1, 2-3, 4-5, 6-7; p is the identity for W < 64 and for
- *            W = 64 swaps bits 2-3 with bits 4-5 of its argument.
+ *            the codes of channel d for tokens 4j .. 4j+3 of the group in bits
+ *            0-1, 2-3, 4-5, 6-7 (the byte the reference's key operator writes);
+ *            p is the identity for W < 64 and for W = 64 swaps bits 2-3 with
+ *            bits 4-5 of its argument.
  *   k_scales, k_zeros + (u*max_groups + g) * D : fp32 per channel of the group
  *            (one per-channel group of the reference, quantize_kernels.hpp:36-42).
  *   v_codes  + (u*max_tokens + t) * (D/4): the reference's value layout, byte b
  *            = channels 4b..4b+3 of token t (quantize_kernels.hpp:55-60).
  *   v_scales, v_zeros + (u*max_tokens + t) * (D/G): fp32 per channel group.
+ *            For D = 128, G = 32 the 32 token rows of a group are permuted
+ *            inside the group's own 1 KB / 512 B: code byte b of token
+ *            t = 16k + 4c + n is byte n of 32-bit word (b/8)*64 + k*32 + (b%8)*4 + c,
+ *            and the token's scale/zero row is 16k + 4n + c.
  * Residual ring of one unit: k_res, v_res + u*R*D elements of res_dtype; the
  * live window is slots (res_start + i) % R for 0 <= i < res_len, oldest first.
  * The three counters (quant_len, res_start, res_len) are kept by the caller;

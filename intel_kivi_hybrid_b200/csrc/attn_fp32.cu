@@ -101,7 +101,7 @@ attn_fp32_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
 #pragma unroll
                 for (int h = 0; h < NREP; ++h) acc[h] = 0.0f;
                 if (valid) {
-                    const int j = tt % Q, e = tt / Q;
+                    const int j = tt / 4, e = tt % 4;
                     for (int d0 = 0; d0 < D; d0 += 4) {
                         const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(kb + kblock_offset(d0, j, Q, W)));
 #pragma unroll
@@ -116,7 +116,9 @@ attn_fp32_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
                 absorb_scores(acc, valid);
                 const int ntok = G - c0 < 32 ? G - c0 : 32;
                 const int64_t t0 = g * G + c0;
-                const int64_t tb = (int64_t)u * L.max_tokens + t0;
+                const uint8_t* vcu = L.v_codes + (int64_t)u * L.max_tokens * (D / 4);
+                const float* vsu = L.v_scales + (int64_t)u * L.max_tokens * ng;
+                const float* vzu = L.v_zeros + (int64_t)u * L.max_tokens * ng;
                 for (int tk = 0; tk < ntok; ++tk) {
                     float p[NREP];
 #pragma unroll
@@ -125,10 +127,11 @@ attn_fp32_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
                     for (int b = 0; b < DB; ++b) {
                         const int byte = lane + 32 * b;
                         if (byte < D / 4) {
-                            const uint32_t vb = __ldg(L.v_codes + (tb + tk) * (D / 4) + byte);
+                            const uint32_t vb = __ldg(vcu + vcode_offset(t0 + tk, byte, D, G));
                             const int gd = (4 * byte) / G;
-                            const float s = __ldg(L.v_scales + (tb + tk) * ng + gd);
-                            const float z = __ldg(L.v_zeros + (tb + tk) * ng + gd);
+                            const int64_t mi = vmeta_index(t0 + tk, gd, D, G);
+                            const float s = __ldg(vsu + mi);
+                            const float z = __ldg(vzu + mi);
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
                                 const float v = fmaf((float)((vb >> (2 * i)) & 3u), s, z);

@@ -137,7 +137,7 @@ struct WarpState {
 };
 
 // ---- one token group (32 tokens) in three phases ----------------------------------
-// q.k: scores of the lane's four tokens (gid + 8e) for head `tig`, log2 domain.
+// q.k: scores of the lane's four tokens (4*gid + e) for head `tig`, log2 domain.
 __device__ __forceinline__ void qk_phase(
     const uint8_t* __restrict__ kc, const float* __restrict__ ks, const float* __restrict__ kz,
     const float* __restrict__ qreg, uint32_t part_mask, int gid, int tig, float (&s)[4]) {
@@ -185,10 +185,10 @@ __device__ __forceinline__ void qk_phase(
     qz += __shfl_xor_sync(0xffffffffu, qz, 1);
     qz += __shfl_xor_sync(0xffffffffu, qz, 2);
     const float qz_t = __shfl_sync(0xffffffffu, qz, 8 * tig);
-    s[0] = fmaf(c0[0][0] + c0[0][1], kRow0, qz_t);   // token gid
-    s[1] = fmaf(c0[0][2] + c0[0][3], kRow1, qz_t);   // token gid + 8
-    s[2] = fmaf(c1[0][0] + c1[0][1], kRow2, qz_t);   // token gid + 16
-    s[3] = fmaf(c1[0][2] + c1[0][3], kRow3, qz_t);   // token gid + 24
+    s[0] = fmaf(c0[0][0] + c0[0][1], kRow0, qz_t);   // token 4*gid
+    s[1] = fmaf(c0[0][2] + c0[0][3], kRow1, qz_t);   // token 4*gid + 1
+    s[2] = fmaf(c1[0][0] + c1[0][1], kRow2, qz_t);   // token 4*gid + 2
+    s[3] = fmaf(c1[0][2] + c1[0][3], kRow3, qz_t);   // token 4*gid + 3
 }
 
 // running max / sum update for NG groups at once; turns scores into weights
@@ -221,25 +221,30 @@ __device__ __forceinline__ void softmax_phase(float (&s)[NG][4], int gid, int la
         for (int e = 0; e < 4; ++e) { s[g][e] = ex2(s[g][e] - st.m); st.l += s[g][e]; }
 }
 
-// p.v of one group; p[e] = weight of token gid + 8e for head tig
+// p.v of one group; p[n] = weight of token 4*gid + n for head tig.
+// Value block words (kivi_common.cuh): word (gd, kappa, r, c) holds natural byte
+// 8*gd + r (channels 32*gd + 4*r + i) of tokens 16*kappa + 4*c + n in bytes n.
+// A lane (gid, tig) reads word (gd, kappa, gid, tig): bytes 0/2 are its k-slots
+// 2tig / 2tig+1, bytes 1/3 (after >> 8) its k-slots 2tig+8 / 2tig+9.
 __device__ __forceinline__ void pv_phase(
     const uint8_t* __restrict__ vc, const float* __restrict__ vs, const float* __restrict__ vz,
     const float (&p)[4], int part, int gid, int tig, WarpState& st) {
+    const uint32_t* vw = reinterpret_cast<const uint32_t*>(vc) + gid * 4 + tig;
 #pragma unroll
     for (int kap = 0; kap < 2; ++kap) {
-        const int tok0 = 4 * kap + tig;                 // tokens tok0 + 8e, e = 0..3
-        const int src = 4 * tok0 + (gid >> 1);          // lane holding their p for head gid>>1
+        const int src = 4 * (4 * kap + tig) + (gid >> 1);   // lane holding tokens 16*kap + 4*tig + n, head gid>>1
         float pe[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) pe[e] = __shfl_sync(0xffffffffu, p[e], src);
+        for (int n = 0; n < 4; ++n) pe[n] = __shfl_sync(0xffffffffu, p[n], src);
+        // scales / zeros of token 16*kap + 4*tig + n sit at row 16*kap + 4*n + tig
         float4 sv[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) sv[e] = *reinterpret_cast<const float4*>(vs + (tok0 + 8 * e) * 4);
-        {   // zero term: hi lanes take e = 0,1, lo lanes e = 2,3
+        for (int n = 0; n < 4; ++n) sv[n] = *reinterpret_cast<const float4*>(vs + (16 * kap + 4 * n + tig) * 4);
+        {   // zero term: hi lanes take n = 0,1, lo lanes n = 2,3
             const float pa = part ? pe[2] : pe[0], pb = part ? pe[3] : pe[1];
-            const int ta = tok0 + 16 * part;
-            const float4 za = *reinterpret_cast<const float4*>(vz + ta * 4);
-            const float4 zb = *reinterpret_cast<const float4*>(vz + (ta + 8) * 4);
+            const int ra = 16 * kap + 8 * part + tig;
+            const float4 za = *reinterpret_cast<const float4*>(vz + ra * 4);
+            const float4 zb = *reinterpret_cast<const float4*>(vz + (ra + 4) * 4);
             st.oz[0] = fmaf(pa, za.x, fmaf(pb, zb.x, st.oz[0]));
             st.oz[1] = fmaf(pa, za.y, fmaf(pb, zb.y, st.oz[1]));
             st.oz[2] = fmaf(pa, za.z, fmaf(pb, zb.z, st.oz[2]));
@@ -247,21 +252,19 @@ __device__ __forceinline__ void pv_phase(
         }
         // lo lanes feed the odd B columns with the same p*s: those columns of the
         // accumulators are never read
-        const uint8_t* vrow = vc + tok0 * 32 + gid;
 #pragma unroll
         for (int gd = 0; gd < 4; ++gd) {
             const float s0 = gd == 0 ? sv[0].x : gd == 1 ? sv[0].y : gd == 2 ? sv[0].z : sv[0].w;
             const float s1 = gd == 0 ? sv[1].x : gd == 1 ? sv[1].y : gd == 2 ? sv[1].z : sv[1].w;
             const float s2 = gd == 0 ? sv[2].x : gd == 1 ? sv[2].y : gd == 2 ? sv[2].z : sv[2].w;
             const float s3 = gd == 0 ? sv[3].x : gd == 1 ? sv[3].y : gd == 2 ? sv[3].z : sv[3].w;
-            const uint32_t b0 = pack_f16_rn(pe[0] * s0, pe[1] * s1);
-            const uint32_t b1 = pack_f16_rn(pe[2] * s2, pe[3] * s3);
-            const uint32_t x01 = (uint32_t)vrow[8 * gd] | ((uint32_t)vrow[8 * 32 + 8 * gd] << 16);
-            const uint32_t x23 = (uint32_t)vrow[16 * 32 + 8 * gd] | ((uint32_t)vrow[24 * 32 + 8 * gd] << 16);
+            const uint32_t b0 = pack_f16_rn(pe[0] * s0, pe[2] * s2);     // k-slots 2tig, 2tig+1: tokens n = 0, 2
+            const uint32_t b1 = pack_f16_rn(pe[1] * s1, pe[3] * s3);     // k-slots 2tig+8, +9:   tokens n = 1, 3
+            const uint32_t we = vw[gd * 64 + kap * 32], wo = we >> 8;
             uint32_t a[4];
-            a[0] = code_pair<0>(x01); a[1] = code_pair<1>(x01); a[2] = code_pair<0>(x23); a[3] = code_pair<1>(x23);
+            a[0] = code_pair<0>(we); a[1] = code_pair<1>(we); a[2] = code_pair<0>(wo); a[3] = code_pair<1>(wo);
             mma_f16(st.o[2 * gd], a, b0, b1);
-            a[0] = code_pair<2>(x01); a[1] = code_pair<3>(x01); a[2] = code_pair<2>(x23); a[3] = code_pair<3>(x23);
+            a[0] = code_pair<2>(we); a[1] = code_pair<3>(we); a[2] = code_pair<2>(wo); a[3] = code_pair<3>(wo);
             mma_f16(st.o[2 * gd + 1], a, b0, b1);
         }
     }

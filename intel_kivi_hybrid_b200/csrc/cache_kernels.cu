@@ -85,10 +85,10 @@ flush_keys_kernel(TokenSource src, uint8_t* __restrict__ k_codes, float* __restr
         if (GT > 0) {
 #pragma unroll
             for (int j = 0; j < GT / 4; ++j) {
-                float q0 = code_of<HALF_EVEN>(x[j], mn, scale, rcp);
-                float q1 = code_of<HALF_EVEN>(x[j + GT / 4], mn, scale, rcp);
-                float q2 = code_of<HALF_EVEN>(x[j + 2 * (GT / 4)], mn, scale, rcp);
-                float q3 = code_of<HALF_EVEN>(x[j + 3 * (GT / 4)], mn, scale, rcp);
+                float q0 = code_of<HALF_EVEN>(x[4 * j], mn, scale, rcp);
+                float q1 = code_of<HALF_EVEN>(x[4 * j + 1], mn, scale, rcp);
+                float q2 = code_of<HALF_EVEN>(x[4 * j + 2], mn, scale, rcp);
+                float q3 = code_of<HALF_EVEN>(x[4 * j + 3], mn, scale, rcp);
                 s_block[kblock_offset(d, j, Q, W)] =
                     (uint8_t)__float2int_rn(fmaf(q3, 64.0f, fmaf(q2, 16.0f, fmaf(q1, 4.0f, q0))));
             }
@@ -96,7 +96,7 @@ flush_keys_kernel(TokenSource src, uint8_t* __restrict__ k_codes, float* __restr
             for (int j = 0; j < Q; ++j) {
                 uint32_t byte = 0;
                 for (int e = 0; e < 4; ++e) {
-                    float q = code_of<HALF_EVEN>(src_load(src, u, tau0 + j + e * Q, d), mn, scale, rcp);
+                    float q = code_of<HALF_EVEN>(src_load(src, u, tau0 + 4 * j + e, d), mn, scale, rcp);
                     byte |= (uint32_t)__float2int_rn(q) << (2 * e);
                 }
                 s_block[kblock_offset(d, j, Q, W)] = (uint8_t)byte;
@@ -158,8 +158,8 @@ flush_keys_fast_kernel(TokenSource src, uint8_t* __restrict__ k_codes, float* __
     k_zeros[((int64_t)u * max_groups + g) * D + d] = mn;
 #pragma unroll
     for (int j = 0; j < Q; ++j) {
-        const float q0 = code_of<HALF_EVEN>(x[j], mn, scale, rcp), q1 = code_of<HALF_EVEN>(x[j + Q], mn, scale, rcp);
-        const float q2 = code_of<HALF_EVEN>(x[j + 2 * Q], mn, scale, rcp), q3 = code_of<HALF_EVEN>(x[j + 3 * Q], mn, scale, rcp);
+        const float q0 = code_of<HALF_EVEN>(x[4 * j], mn, scale, rcp), q1 = code_of<HALF_EVEN>(x[4 * j + 1], mn, scale, rcp);
+        const float q2 = code_of<HALF_EVEN>(x[4 * j + 2], mn, scale, rcp), q3 = code_of<HALF_EVEN>(x[4 * j + 3], mn, scale, rcp);
         s_block[kblock_offset(d, j, Q, 64)] = (uint8_t)__float2int_rn(fmaf(q3, 64.0f, fmaf(q2, 16.0f, fmaf(q1, 4.0f, q0))));
     }
     __syncthreads();
@@ -190,9 +190,9 @@ flush_values_kernel(TokenSource src, uint8_t* __restrict__ v_codes, float* __res
     const float scale = group_scale(mn, mx);
         const float rcp = group_rcp(scale);
     const int64_t t = tok0 + tau;
-    v_scales[((int64_t)u * max_tokens + t) * ng + gd] = scale;
-    v_zeros[((int64_t)u * max_tokens + t) * ng + gd] = mn;
-    uint8_t* dst = v_codes + ((int64_t)u * max_tokens + t) * (D / 4) + gd * (G / 4);
+    v_scales[(int64_t)u * max_tokens * ng + vmeta_index(t, gd, D, G)] = scale;
+    v_zeros[(int64_t)u * max_tokens * ng + vmeta_index(t, gd, D, G)] = mn;
+    uint8_t* dst = v_codes + (int64_t)u * max_tokens * (D / 4);
     for (int i = 0; i < G; i += 4) {
         uint32_t byte = 0;
 #pragma unroll
@@ -200,7 +200,7 @@ flush_values_kernel(TokenSource src, uint8_t* __restrict__ v_codes, float* __res
             float q = code_of<HALF_EVEN>(src_load(src, u, tau, gd * G + i + e), mn, scale, rcp);
             byte |= (uint32_t)__float2int_rn(q) << (2 * e);
         }
-        dst[i / 4] = (uint8_t)byte;
+        dst[vcode_offset(t, gd * (G / 4) + i / 4, D, G)] = (uint8_t)byte;
     }
 }
 
@@ -252,9 +252,14 @@ flush_values_fast_kernel(TokenSource src, uint8_t* __restrict__ v_codes, float* 
                 const float q2 = code_of<HALF_EVEN>(v[it][4 * b + 2], mn, scale, rcp), q3 = code_of<HALF_EVEN>(v[it][4 * b + 3], mn, scale, rcp);
                 bytes |= (uint32_t)__float2int_rn(fmaf(q3, 64.0f, fmaf(q2, 16.0f, fmaf(q1, 4.0f, q0)))) << (8 * b);
             }
-            const int64_t t = (int64_t)u * max_tokens + tok0 + tau[it];
-            *reinterpret_cast<uint16_t*>(v_codes + t * (D / 4) + lane16 * 2) = (uint16_t)bytes;
-            if (sub == 0) { v_scales[t * (D / G) + gd] = scale; v_zeros[t * (D / G) + gd] = mn; }
+            const int64_t t = tok0 + tau[it];
+            uint8_t* vc = v_codes + (int64_t)u * max_tokens * (D / 4);
+            vc[vcode_offset(t, lane16 * 2, D, G)] = (uint8_t)bytes;
+            vc[vcode_offset(t, lane16 * 2 + 1, D, G)] = (uint8_t)(bytes >> 8);
+            if (sub == 0) {
+                const int64_t mi = (int64_t)u * max_tokens * (D / G) + vmeta_index(t, gd, D, G);
+                v_scales[mi] = scale; v_zeros[mi] = mn;
+            }
         }
     }
 }
@@ -299,13 +304,13 @@ materialize_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
         if (t < quant_len) {
             const int64_t g = t / G;
             const int tt = (int)(t % G);
-            const int j = tt % Q, e = tt / Q;
+            const int j = tt / 4, e = tt % 4;
             const int64_t gb = (int64_t)u * max_groups + g;
             uint32_t kb = L.k_codes[gb * (D * Q) + kblock_offset(d, j, Q, W)];
             kv = dequant((float)((kb >> (2 * e)) & 3u), L.k_scales[gb * D + d], L.k_zeros[gb * D + d]);
-            const int64_t tb = (int64_t)u * L.max_tokens + t;
-            uint32_t vb = L.v_codes[tb * (D / 4) + d / 4];
-            vv = dequant((float)((vb >> (2 * (d % 4))) & 3u), L.v_scales[tb * ng + d / G], L.v_zeros[tb * ng + d / G]);
+            uint32_t vb = L.v_codes[(int64_t)u * L.max_tokens * (D / 4) + vcode_offset(t, d / 4, D, G)];
+            const int64_t mi = (int64_t)u * L.max_tokens * ng + vmeta_index(t, d / G, D, G);
+            vv = dequant((float)((vb >> (2 * (d % 4))) & 3u), L.v_scales[mi], L.v_zeros[mi]);
         } else {
             const int slot = (int)((res_start + (t - quant_len)) % L.residual_cap);
             const int64_t o = ((int64_t)u * L.residual_cap + slot) * D + d;
@@ -335,11 +340,7 @@ import_keys_kernel(kivi_layer L, const uint8_t* __restrict__ packed, const float
         // operator bytes of this (channel, group): byte b = tokens 4b..4b+3
         const uint8_t* row = packed + ((int64_t)u * D + d) * (S / 4) + g * Q;
         for (int j = 0; j < Q; ++j) {
-            uint32_t byte = 0;
-            for (int e = 0; e < 4; ++e) {
-                const int tt = j + e * Q;
-                byte |= ((row[tt / 4] >> (2 * (tt % 4))) & 3u) << (2 * e);
-            }
+            const uint32_t byte = row[j];
             L.k_codes[gb * (D * Q) + kblock_offset(d, j, Q, W)] = (uint8_t)byte;
         }
     }

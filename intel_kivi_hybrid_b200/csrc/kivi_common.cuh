@@ -96,16 +96,45 @@ __device__ __forceinline__ void store_from_float(void* p, int dtype, int64_t i, 
 }
 
 // ---- key block layout --------------------------------------------------------
-// Byte offset inside one key block of the codes of channel d, token lane j
-// (tokens j, j+Q, j+2Q, j+3Q of the group; Q = G/4); W = min(D, 64).
-// Within a 64-channel half-row the two 2-bit fields (d>>2)&3 and (d>>4)&3 of
-// the channel index are swapped, so that a 16-byte piece of a row holds four
-// 4-channel words that are 16 channels apart: the tensor-core kernel gives each
-// lane one such piece and then reads the matching scales without bank conflicts.
+// Byte offset inside one key block of the codes of channel d, token quad j
+// (tokens 4j .. 4j+3 of the group in bits 0-1, 2-3, 4-5, 6-7; 0 <= j < Q = G/4);
+// W = min(D, 64).  Within a 64-channel half-row the two 2-bit fields (d>>2)&3
+// and (d>>4)&3 of the channel index are swapped, so that a 16-byte piece of a
+// row holds four 4-channel words that are 16 channels apart: the tensor-core
+// kernel gives each lane one such piece and then reads the matching scales
+// without bank conflicts.
 __host__ __device__ __forceinline__ int kblock_offset(int d, int j, int Q, int W) {
     int dl = d % W;
     if (W == 64) dl = (dl & 3) | (((dl >> 4) & 3) << 2) | (((dl >> 2) & 3) << 4);
     return (d / W) * Q * W + j * W + dl;
+}
+
+// ---- value layout ---------------------------------------------------------------
+// Values keep the reference's per-token rows (byte b of token t = channels
+// 4b..4b+3, quantize_kernels.hpp:55-60) except for D = 128, G = 32, where the
+// 32 rows of a token group are re-laid inside their own 1 KB (codes) and 512 B
+// (scales, zeros) so that the tensor-core kernel reads them with full-width,
+// conflict-free loads:
+//   codes: 32-bit word (gd, kappa, r, c) = gd*64 + kappa*32 + r*4 + c holds, in
+//          bytes n = 0..3, the natural byte 8*gd + r of tokens 16*kappa + 4*c + n;
+//   scales / zeros: token 16*kappa + 4*c + n sits at row 16*kappa + 4*n + c.
+__host__ __device__ __forceinline__ bool value_blocks(int D, int G) { return D == 128 && G == 32; }
+
+// byte offset of natural byte `b` of token `t` (token index inside the layer's
+// store) relative to the start of the store of its unit
+__host__ __device__ __forceinline__ int64_t vcode_offset(int64_t t, int b, int D, int G) {
+    if (!value_blocks(D, G)) return t * (D / 4) + b;
+    const int tt = (int)(t & 31);
+    const int word = (b >> 3) * 64 + (tt >> 4) * 32 + (b & 7) * 4 + ((tt >> 2) & 3);
+    return (t - tt) * 32 + word * 4 + (tt & 3);
+}
+
+// index of the (scale, zero) of channel group gd of token t
+__host__ __device__ __forceinline__ int64_t vmeta_index(int64_t t, int gd, int D, int G) {
+    if (!value_blocks(D, G)) return t * (D / G) + gd;
+    const int tt = (int)(t & 31);
+    const int row = (tt & 16) | ((tt & 3) << 2) | ((tt >> 2) & 3);
+    return ((t - tt) + row) * 4 + gd;
 }
 
 __host__ __device__ __forceinline__ int elem_size(int dtype) { return dtype == KIVI_BF16 ? 2 : 4; }

@@ -92,9 +92,33 @@ def test_packed_store_matches_oracle_flush_by_flush(cabi):
     blk = blk[..., perm]                                                                    # -> [j][d]
     Q = G // 4
     for e in range(4):
-        got = (blk >> (2 * e)) & 3                       # tokens j + e*Q
-        assert torch.equal(got.transpose(2, 3), kc[..., e * Q:(e + 1) * Q].to(torch.uint8))
+        got = (blk >> (2 * e)) & 3                       # bit pair e of byte j = token 4j + e
+        assert torch.equal(got.transpose(2, 3), kc[..., e::4].to(torch.uint8))
     # served tensors: history round trip + exact residual
+    k, v = st.materialize()
+    sk, sv = oc.served()
+    assert torch.equal(k.cpu(), units(sk)) and torch.equal(v.cpu(), units(sv))
+
+
+def test_value_blocks_of_llama_shaped_layers_hold_the_reference_bytes(cabi):
+    """D=128, G=32 layers store each 32-token value group as a re-laid block;
+    undoing the documented permutation must give the reference's packed rows, and
+    the served tensors must equal the oracle's bit for bit."""
+    B, H, D, G, R = 1, 2, 128, 32, 128
+    K = ko.make_keys(B, H, 200, D, seed=8)
+    V = ko.make_values(B, H, 200, D, seed=8)
+    oc = ko.OracleCache(D, G, R, rounding="half_away")
+    st = cabi.LayerStore(B * H, D, G, R, 256, torch.float32, "cuda")
+    oc.append(K, V); st.update(units(K).cuda(), units(V).cuda())
+    ng = st.quant_len // G
+    assert ng == oc.flushes == 3
+    vp = torch.cat(oc.v_packed, dim=2).reshape(B * H, ng, G, D // 4)               # natural rows [t][b]
+    blk = st.v_codes[:, :ng * G].cpu().reshape(B * H, ng, 4, 2, 8, 4, 4)            # [gd][kappa][r][c][n]
+    nat = blk.permute(0, 1, 3, 5, 6, 2, 4).reshape(B * H, ng, G, D // 4)            # t = 16k+4c+n, b = 8gd+r
+    assert torch.equal(nat, vp)
+    vs = torch.cat(oc.v_scales, dim=2).reshape(B * H, ng, G, D // G)
+    rows = st.v_scales[:, :ng * G].cpu().reshape(B * H, ng, 2, 4, 4, D // G)        # [kappa][n][c]
+    assert torch.equal(rows.permute(0, 1, 2, 4, 3, 5).reshape(B * H, ng, G, D // G), vs)
     k, v = st.materialize()
     sk, sv = oc.served()
     assert torch.equal(k.cpu(), units(sk)) and torch.equal(v.cpu(), units(sv))
