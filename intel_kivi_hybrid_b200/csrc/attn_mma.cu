@@ -516,21 +516,31 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
     }
     __syncwarp();
 
-    const int64_t ubase_g = (int64_t)u * max_groups;
-    const int64_t ubase_t = (int64_t)u * L.max_tokens;
+    // chunk i of this warp starts at group g_begin + (warp + kWarps*i)*kGPS: base
+    // pointers of chunk 0, advanced by a constant per chunk
+    const int64_t gw0 = (int64_t)u * max_groups + g_begin + (int64_t)warp * kGPS;
+    const int64_t tw0 = (int64_t)u * L.max_tokens + (g_begin + (int64_t)warp * kGPS) * kG;
+    const uint8_t* pk_c = L.k_codes + gw0 * 1024;
+    const float* pk_s = L.k_scales + gw0 * kD;
+    const float* pk_z = L.k_zeros + gw0 * kD;
+    const uint8_t* pv_c = L.v_codes + tw0 * 32;
+    const float* pv_s = L.v_scales + tw0 * 4;
+    const float* pv_z = L.v_zeros + tw0 * 4;
+    const int n_my_groups = (int)(g_end - g_begin);
     auto issue = [&](int i) {
-        const int64_t g0 = g_begin + (int64_t)(warp + kWarps * i) * kGPS;
-        const int ng = (int)((g_end - g0) < kGPS ? (g_end - g0) : kGPS);
+        const int goff = (warp + kWarps * i) * kGPS;             // groups from g_begin
+        const int ng = (n_my_groups - goff) < kGPS ? (n_my_groups - goff) : kGPS;
         const int s = i % kStages;
         const uint32_t bar = bar0 + 8 * s;
         const uint32_t dst = smem_u32(wstage + s * kStageBytes);
+        const int64_t adv = (int64_t)i * kWarps * kGPS;          // groups past chunk 0
         mbar_expect_tx(bar, (uint32_t)ng * kGroupBytes);
-        bulk_g2s(dst, L.k_codes + (ubase_g + g0) * 1024, ng * 1024, bar);
-        bulk_g2s(dst + kGPS * 1024, L.k_scales + (ubase_g + g0) * kD, ng * 512, bar);
-        bulk_g2s(dst + kGPS * 1536, L.k_zeros + (ubase_g + g0) * kD, ng * 512, bar);
-        bulk_g2s(dst + kGPS * 2048, L.v_codes + (ubase_t + g0 * kG) * 32, ng * 1024, bar);
-        bulk_g2s(dst + kGPS * 3072, L.v_scales + (ubase_t + g0 * kG) * 4, ng * 512, bar);
-        bulk_g2s(dst + kGPS * 3584, L.v_zeros + (ubase_t + g0 * kG) * 4, ng * 512, bar);
+        bulk_g2s(dst, pk_c + adv * 1024, ng * 1024, bar);
+        bulk_g2s(dst + kGPS * 1024, pk_s + adv * kD, ng * 512, bar);
+        bulk_g2s(dst + kGPS * 1536, pk_z + adv * kD, ng * 512, bar);
+        bulk_g2s(dst + kGPS * 2048, pv_c + adv * 1024, ng * 1024, bar);
+        bulk_g2s(dst + kGPS * 3072, pv_s + adv * 128, ng * 512, bar);
+        bulk_g2s(dst + kGPS * 3584, pv_z + adv * 128, ng * 512, bar);
     };
     if (lane == 0) {
         for (int i = 0; i < kStages && i < my_n; ++i) issue(i);

@@ -255,3 +255,47 @@ def test_attention_mma_rejects_other_shapes(cabi):
     cabi.load_state(st, torch.randn(2, 64, 64, device="cuda"), torch.randn(2, 64, 64, device="cuda"), 64)
     with pytest.raises(RuntimeError, match="tensor-core path"):
         st.attention(torch.randn(2, 1, 64, device="cuda"), path=cabi.ATTN_MMA)
+
+
+# ---- full-size properties (config 2 of the benchmark: 512 units x 32768 tokens) ----
+
+def test_full_size_config2_properties(cabi):
+    """At the benchmark's full size the oracle is too slow, so check properties that
+    do not depend on size: the result does not depend on the number of splits, the
+    tensor-core and the fp32 kernel agree, every output is a convex combination of
+    value rows (inside their per-channel range), and a slice of units reproduces
+    the CPU oracle."""
+    B, Hkv, n_rep, D, G, R, n_quant, n_res = 64, 8, 4, 128, 32, 128, 32640, 128
+    U, T = B * Hkv, n_quant + n_res
+    g = torch.Generator(device="cuda").manual_seed(123)
+    k = torch.empty(U, T, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.empty(U, T, D, device="cuda", dtype=torch.bfloat16)
+    for u0 in range(0, U, 64):
+        k[u0:u0 + 64] = torch.randn(64, T, D, device="cuda", generator=g).to(torch.bfloat16)
+        v[u0:u0 + 64] = torch.randn(64, T, D, device="cuda", generator=g).to(torch.bfloat16)
+    k[:, :, 5] *= 10.0                                     # an outlier channel
+    st = cabi.LayerStore(U, D, G, R, n_quant, torch.bfloat16, "cuda")
+    cabi.load_state(st, k, v, n_quant)
+    q = torch.randn(U, n_rep, D, device="cuda", generator=g).to(torch.bfloat16)
+    o_auto = st.attention(q, n_rep=n_rep, path=cabi.ATTN_MMA, out_dtype=torch.float32)
+    o_s1 = st.attention(q, n_rep=n_rep, path=cabi.ATTN_MMA, num_splits=1, out_dtype=torch.float32)
+    o_s9 = st.attention(q, n_rep=n_rep, path=cabi.ATTN_MMA, num_splits=9, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert cabi.device_fault() == 0 and torch.isfinite(o_auto).all()
+    assert rel_err(o_s1, o_auto) < 2e-5 and rel_err(o_s9, o_auto) < 2e-5
+    # fp32 kernel on the last units (a full run of it takes ~5 ms; slicing needs a second store)
+    sub = slice(U - 8, U)
+    st8 = cabi.LayerStore(8, D, G, R, n_quant, torch.bfloat16, "cuda")
+    cabi.load_state(st8, k[sub], v[sub], n_quant)
+    o_f32 = st8.attention(q[sub].contiguous(), n_rep=n_rep, path=cabi.ATTN_FP32, out_dtype=torch.float32)
+    assert rel_err(o_auto[sub], o_f32) < TOL_BF16
+    # convexity: the quantized values stay inside [min, max] of their group, so the output
+    # stays inside the per-channel range of the unit's values
+    vmin = v.float().amin(dim=1, keepdim=True)
+    vmax = v.float().amax(dim=1, keepdim=True)
+    eps = 1e-2
+    assert bool(((o_auto >= vmin - eps) & (o_auto <= vmax + eps)).all())
+    # oracle on the first KV head of the first batch row
+    kk, vv = k[:1].cpu().reshape(1, 1, T, D), v[:1].cpu().reshape(1, 1, T, D)
+    ref = ko.kivi_decode_attention(q[:1].cpu().reshape(1, n_rep, D), kk, vv, n_quant, G, "half_away", dtype=torch.float64)
+    assert rel_err(o_auto[:1], ref.float().reshape(1, n_rep, D)) < TOL_BF16
