@@ -228,7 +228,7 @@ __device__ __forceinline__ void softmax_phase(float (&s)[NG][4], int gid, int la
 // 2tig / 2tig+1, bytes 1/3 (after >> 8) its k-slots 2tig+8 / 2tig+9.
 __device__ __forceinline__ void pv_phase(
     const uint8_t* __restrict__ vc, const float* __restrict__ vs, const float* __restrict__ vz,
-    const float (&p)[4], int part, int gid, int tig, WarpState& st) {
+    const float (&p)[4], int part, int gid, int tig, float (&acc)[8][4], WarpState& st) {
     const uint32_t* vw = reinterpret_cast<const uint32_t*>(vc) + gid * 4 + tig;
 #pragma unroll
     for (int kap = 0; kap < 2; ++kap) {
@@ -263,9 +263,9 @@ __device__ __forceinline__ void pv_phase(
             const uint32_t we = vw[gd * 64 + kap * 32], wo = we >> 8;
             uint32_t a[4];
             a[0] = code_pair<0>(we); a[1] = code_pair<1>(we); a[2] = code_pair<0>(wo); a[3] = code_pair<1>(wo);
-            mma_f16(st.o[2 * gd], a, b0, b1);
+            mma_f16(acc[2 * gd], a, b0, b1);
             a[0] = code_pair<2>(we); a[1] = code_pair<3>(we); a[2] = code_pair<2>(wo); a[3] = code_pair<3>(wo);
-            mma_f16(st.o[2 * gd + 1], a, b0, b1);
+            mma_f16(acc[2 * gd + 1], a, b0, b1);
         }
     }
 }
@@ -283,10 +283,23 @@ __device__ __forceinline__ void process_groups(
         qk_phase(sb + (g0 + g) * 1024, reinterpret_cast<const float*>(sb + kGPS * 1024 + (g0 + g) * 512),
                  reinterpret_cast<const float*>(sb + kGPS * 1536 + (g0 + g) * 512), qreg, part_mask, gid, tig, s[g]);
     softmax_phase<NG>(s, gid, lane, st);
+    // The tensor core adds each product into its fp32 accumulator with
+    // truncation; against an accumulator that has grown over thousands of tokens
+    // that is a biased loss (all addends p*s*c are positive) which the later
+    // cancellation with the zero term amplifies.  So the MMAs of this stage go
+    // into fresh accumulators and join the running sums through ordinary adds
+    // (only the even columns are ever read).
+    float acc[8][4];
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[mt][i] = 0.0f;
 #pragma unroll
     for (int g = 0; g < NG; ++g)
         pv_phase(sb + kGPS * 2048 + (g0 + g) * 1024, reinterpret_cast<const float*>(sb + kGPS * 3072 + (g0 + g) * 512),
-                 reinterpret_cast<const float*>(sb + kGPS * 3584 + (g0 + g) * 512), s[g], part, gid, tig, st);
+                 reinterpret_cast<const float*>(sb + kGPS * 3584 + (g0 + g) * 512), s[g], part, gid, tig, acc, st);
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) { st.o[mt][0] += acc[mt][0]; st.o[mt][2] += acc[mt][2]; }
 }
 
 // ---- residual ring: full-precision tokens ---------------------------------------

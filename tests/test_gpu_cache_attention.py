@@ -282,12 +282,17 @@ def test_full_size_config2_properties(cabi):
     o_s9 = st.attention(q, n_rep=n_rep, path=cabi.ATTN_MMA, num_splits=9, out_dtype=torch.float32)
     torch.cuda.synchronize()
     assert cabi.device_fault() == 0 and torch.isfinite(o_auto).all()
-    assert rel_err(o_s1, o_auto) < 2e-5 and rel_err(o_s9, o_auto) < 2e-5
+    # different split counts change the running max that p = 2^(s-m) is taken against, hence the
+    # fp16 rounding of p*s: agreement is at the level of that rounding, not bitwise
+    e1, e9 = rel_err(o_s1, o_auto), rel_err(o_s9, o_auto)
+    print(f"[cfg2 full size] splits 1 vs auto {e1:.2e}, 9 vs auto {e9:.2e}")
+    assert e1 < TOL_BF16 and e9 < TOL_BF16
     # fp32 kernel on the last units (a full run of it takes ~5 ms; slicing needs a second store)
     sub = slice(U - 8, U)
     st8 = cabi.LayerStore(8, D, G, R, n_quant, torch.bfloat16, "cuda")
     cabi.load_state(st8, k[sub], v[sub], n_quant)
     o_f32 = st8.attention(q[sub].contiguous(), n_rep=n_rep, path=cabi.ATTN_FP32, out_dtype=torch.float32)
+    print(f"[cfg2 full size] tensor-core vs fp32 kernel {rel_err(o_auto[sub], o_f32):.2e}")
     assert rel_err(o_auto[sub], o_f32) < TOL_BF16
     # convexity: the quantized values stay inside [min, max] of their group, so the output
     # stays inside the per-channel range of the unit's values
