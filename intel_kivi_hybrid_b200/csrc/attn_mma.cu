@@ -177,10 +177,12 @@ __device__ __forceinline__ void qk_phase(
             mma_f16(c1[kt % KIVI_MMA_CHAINS], a, b0, b1);
         }
     }
-#if KIVI_MMA_CHAINS == 2
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { c0[0][i] += c0[1][i]; c1[0][i] += c1[1][i]; }
-#endif
+    for (int step = KIVI_MMA_CHAINS / 2; step >= 1; step /= 2)
+#pragma unroll
+        for (int ch_ = 0; ch_ < step; ++ch_)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { c0[ch_][i] += c0[ch_ + step][i]; c1[ch_][i] += c1[ch_ + step][i]; }
     // zero term of head gid>>1 (both lanes of a gid pair hold the same partial)
     qz += __shfl_xor_sync(0xffffffffu, qz, 1);
     qz += __shfl_xor_sync(0xffffffffu, qz, 2);
