@@ -168,8 +168,9 @@ def run_reference(args, wl):
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": t * 1e3 * (B / B_s), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "B": B, "Hkv": Hkv, "Hq": Hkv * n_rep, "D": D, "G": G,
-                       "n_quant": n_quant, "n_res": n_res},
+            "config": {"workload": args.workload, "B_per_gpu": B, "Hkv": Hkv, "Hq": Hkv * n_rep, "D": D, "G": G,
+                       "n_quant": n_quant, "n_res": n_res,
+                       "parallelism": "reference CPU path on rank 0's host cores, one batch row per step"},
             "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))

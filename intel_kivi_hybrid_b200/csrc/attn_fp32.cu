@@ -240,37 +240,59 @@ attn_fp32_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
 }  // namespace
 
 // out[u][h][:] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
-// grid = (units, n_rep); partials laid out [(u*n_splits + s)*n_rep + h].
-__global__ void __launch_bounds__(256)
+// grid = (units, n_rep), 128 threads; partials laid out [(u*n_splits + s)*n_rep + h].
+// Thread s loads (m_s, l_s); the maximum and the denominator are block
+// reductions, so no thread walks the splits alone; the channel loop keeps four
+// independent loads in flight.
+__global__ void __launch_bounds__(128)
 merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                     void* __restrict__ out, int out_dtype, int n_splits, int D) {
     extern __shared__ float w_s[];                   // [n_splits] weights
-    __shared__ float denom_s;
+    __shared__ float red_s[8];
+    const int u = blockIdx.x, h = blockIdx.y, nrep = gridDim.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int64_t row0 = (int64_t)u * n_splits * nrep + h;   // + s*nrep
     // launched with programmatic stream serialization: everything above may
     // overlap the tail of the attention kernel, the partials may not be read
     // before that kernel has completed
     cudaGridDependencySynchronize();
-    const int u = blockIdx.x, h = blockIdx.y, nrep = gridDim.y;
-    const int64_t row0 = (int64_t)u * n_splits * nrep + h;   // + s*nrep
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(row0 + (int64_t)s * nrep) * 2]);
-    if (threadIdx.x == 0) {
-        float den = 0.0f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = part_ml[(row0 + (int64_t)s * nrep) * 2];
-            const float wgt = (ms == -INFINITY) ? 0.0f : exp2f(ms - M);
-            w_s[s] = wgt;
-            den += wgt * part_ml[(row0 + (int64_t)s * nrep) * 2 + 1];
-        }
-        denom_s = den;
-    }
+    float m_loc = -INFINITY;
+    for (int s = threadIdx.x; s < n_splits; s += blockDim.x)
+        m_loc = fmaxf(m_loc, part_ml[(row0 + (int64_t)s * nrep) * 2]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m_loc = fmaxf(m_loc, __shfl_xor_sync(0xffffffffu, m_loc, o));
+    if (lane == 0) red_s[warp] = m_loc;
     __syncthreads();
-    const float inv = 1.0f / denom_s;
+    float M = red_s[0];
+    for (int w = 1; w < nwarps; ++w) M = fmaxf(M, red_s[w]);
+    float den = 0.0f;
+    for (int s = threadIdx.x; s < n_splits; s += blockDim.x) {
+        const float ms = part_ml[(row0 + (int64_t)s * nrep) * 2];
+        const float wgt = (ms == -INFINITY) ? 0.0f : exp2f(ms - M);
+        w_s[s] = wgt;
+        den += wgt * part_ml[(row0 + (int64_t)s * nrep) * 2 + 1];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+    __syncthreads();                                  // red_s reads above are done
+    if (lane == 0) red_s[4 + warp] = den;
+    __syncthreads();
+    den = 0.0f;
+    for (int w = 0; w < nwarps; ++w) den += red_s[4 + w];
+    const float inv = 1.0f / den;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float acc = 0.0f;
-        for (int s = 0; s < n_splits; ++s)
-            acc = fmaf(part_o[(row0 + (int64_t)s * nrep) * D + d], w_s[s], acc);
-        store_from_float(out, out_dtype, ((int64_t)u * nrep + h) * D + d, acc * inv);
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        int s = 0;
+        for (; s + 4 <= n_splits; s += 4) {
+            const float v0 = part_o[(row0 + (int64_t)(s + 0) * nrep) * D + d];
+            const float v1 = part_o[(row0 + (int64_t)(s + 1) * nrep) * D + d];
+            const float v2 = part_o[(row0 + (int64_t)(s + 2) * nrep) * D + d];
+            const float v3 = part_o[(row0 + (int64_t)(s + 3) * nrep) * D + d];
+            a0 = fmaf(v0, w_s[s], a0); a1 = fmaf(v1, w_s[s + 1], a1);
+            a2 = fmaf(v2, w_s[s + 2], a2); a3 = fmaf(v3, w_s[s + 3], a3);
+        }
+        for (; s < n_splits; ++s) a0 = fmaf(part_o[(row0 + (int64_t)s * nrep) * D + d], w_s[s], a0);
+        store_from_float(out, out_dtype, ((int64_t)u * nrep + h) * D + d, ((a0 + a1) + (a2 + a3)) * inv);
     }
 }
 

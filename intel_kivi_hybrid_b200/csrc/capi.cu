@@ -220,7 +220,7 @@ extern "C" int kivi_decode_attention(const kivi_layer* L, int64_t quant_len, int
         // serialization, so its launch latency overlaps that kernel's tail
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)L->num_units, (unsigned)n_rep);
-        cfg.blockDim = dim3(D >= 256 ? 256 : 128);
+        cfg.blockDim = dim3(128);
         cfg.dynamicSmemBytes = n_splits * sizeof(float);
         cfg.stream = st;
         cudaLaunchAttribute attr[1];
