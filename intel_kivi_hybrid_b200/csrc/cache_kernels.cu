@@ -213,22 +213,29 @@ template <typename TR, typename TF, bool HALF_EVEN>
 __global__ void __launch_bounds__(256)
 flush_values_fast_kernel(TokenSource src, uint8_t* __restrict__ v_codes, float* __restrict__ v_scales,
                          float* __restrict__ v_zeros, int64_t max_tokens, int64_t tok0, int64_t n_tok) {
-    constexpr int D = 128, G = 32, ITER = 4;
+    constexpr int D = 128, G = 32, ITER = 4;             // 64 tokens = two value blocks per CTA
+    // the blocks are assembled in shared memory (their bytes are permuted, see
+    // vcode_offset) and leave with 128-bit stores
+    __shared__ __align__(16) uint8_t s_codes[2 * 1024];
+    __shared__ __align__(16) float s_scale[2 * 128];
+    __shared__ __align__(16) float s_zero[2 * 128];
     const int u = blockIdx.y;
     const int lane16 = threadIdx.x & 15;                 // 16 lanes per token
     const int sub = lane16 & 3, gd = lane16 >> 2;
+    const int64_t cta_tau0 = (int64_t)blockIdx.x * (ITER * 16);
     float v[ITER][8];
-    int64_t tau[ITER];
+    int tl[ITER];                                        // token index inside the CTA's 64
 #pragma unroll
     for (int it = 0; it < ITER; ++it) {
-        tau[it] = ((int64_t)blockIdx.x * ITER + it) * 16 + (threadIdx.x >> 4);
-        if (tau[it] < n_tok) {
-            if (tau[it] < src.res_len) {
-                const int slot = (int)((src.res_start + tau[it]) % src.R);
+        tl[it] = it * 16 + (threadIdx.x >> 4);
+        const int64_t tau = cta_tau0 + tl[it];
+        if (tau < n_tok) {
+            if (tau < src.res_len) {
+                const int slot = (int)((src.res_start + tau) % src.R);
                 Load8<TR>::run(reinterpret_cast<const TR*>(src.ring) + ((int64_t)u * src.R + slot) * D + lane16 * 8, v[it]);
             } else {
                 Load8<TF>::run(reinterpret_cast<const TF*>(src.fresh) + (int64_t)u * src.unit_stride +
-                                   (tau[it] - src.res_len) * src.tok_stride + lane16 * 8, v[it]);
+                                   (tau - src.res_len) * src.tok_stride + lane16 * 8, v[it]);
             }
         } else {
 #pragma unroll
@@ -244,23 +251,33 @@ flush_values_fast_kernel(TokenSource src, uint8_t* __restrict__ v_codes, float* 
         mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, 2)); mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         const float scale = group_scale(mn, mx);
         const float rcp = group_rcp(scale);
-        if (tau[it] < n_tok) {
-            uint32_t bytes = 0;
+        uint32_t bytes = 0;
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                const float q0 = code_of<HALF_EVEN>(v[it][4 * b + 0], mn, scale, rcp), q1 = code_of<HALF_EVEN>(v[it][4 * b + 1], mn, scale, rcp);
-                const float q2 = code_of<HALF_EVEN>(v[it][4 * b + 2], mn, scale, rcp), q3 = code_of<HALF_EVEN>(v[it][4 * b + 3], mn, scale, rcp);
-                bytes |= (uint32_t)__float2int_rn(fmaf(q3, 64.0f, fmaf(q2, 16.0f, fmaf(q1, 4.0f, q0)))) << (8 * b);
-            }
-            const int64_t t = tok0 + tau[it];
-            uint8_t* vc = v_codes + (int64_t)u * max_tokens * (D / 4);
-            vc[vcode_offset(t, lane16 * 2, D, G)] = (uint8_t)bytes;
-            vc[vcode_offset(t, lane16 * 2 + 1, D, G)] = (uint8_t)(bytes >> 8);
-            if (sub == 0) {
-                const int64_t mi = (int64_t)u * max_tokens * (D / G) + vmeta_index(t, gd, D, G);
-                v_scales[mi] = scale; v_zeros[mi] = mn;
-            }
+        for (int b = 0; b < 2; ++b) {
+            const float q0 = code_of<HALF_EVEN>(v[it][4 * b + 0], mn, scale, rcp), q1 = code_of<HALF_EVEN>(v[it][4 * b + 1], mn, scale, rcp);
+            const float q2 = code_of<HALF_EVEN>(v[it][4 * b + 2], mn, scale, rcp), q3 = code_of<HALF_EVEN>(v[it][4 * b + 3], mn, scale, rcp);
+            bytes |= (uint32_t)__float2int_rn(fmaf(q3, 64.0f, fmaf(q2, 16.0f, fmaf(q1, 4.0f, q0)))) << (8 * b);
         }
+        // offsets relative to the CTA's first token (a multiple of 64, so block aligned)
+        s_codes[vcode_offset(tl[it], lane16 * 2, D, G)] = (uint8_t)bytes;
+        s_codes[vcode_offset(tl[it], lane16 * 2 + 1, D, G)] = (uint8_t)(bytes >> 8);
+        if (sub == 0) {
+            const int mi = (int)vmeta_index(tl[it], gd, D, G);
+            s_scale[mi] = scale; s_zero[mi] = mn;
+        }
+    }
+    __syncthreads();
+    // tok0 is a multiple of G and cta_tau0 of 64: whole blocks; a partial last CTA holds whole groups too
+    const int64_t left = n_tok - cta_tau0;
+    const int n_here = left < ITER * 16 ? (int)left : ITER * 16;        // multiple of 32
+    const int64_t t_first = (int64_t)u * max_tokens + tok0 + cta_tau0;
+    uint4* gc = reinterpret_cast<uint4*>(v_codes + t_first * (D / 4));
+    float4* gs = reinterpret_cast<float4*>(v_scales + t_first * (D / G));
+    float4* gz = reinterpret_cast<float4*>(v_zeros + t_first * (D / G));
+    for (int i = threadIdx.x; i < n_here * 2; i += 256) gc[i] = reinterpret_cast<const uint4*>(s_codes)[i];
+    for (int i = threadIdx.x; i < n_here; i += 256) {
+        gs[i] = reinterpret_cast<const float4*>(s_scale)[i];
+        gz[i] = reinterpret_cast<const float4*>(s_zero)[i];
     }
 }
 
@@ -453,7 +470,8 @@ extern "C" int kivi_cache_update(const kivi_layer* L, int64_t quant_len, int res
         const int64_t n_tok = (int64_t)f * G;
         auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
         const int esz = elem_size(new_dtype);
-        const bool fast_v = D == 128 && G == 32 && al16(new_v) && al16(L->v_res) &&
+        const bool fast_v = D == 128 && G == 32 && al16(new_v) && al16(L->v_res) && al16(L->v_codes) &&
+                            al16(L->v_scales) && al16(L->v_zeros) &&
                             (unit_stride_v * esz) % 16 == 0 && (tok_stride_v * esz) % 16 == 0;
         if (fast_v) {
             dim3 gridv((unsigned)((n_tok + 63) / 64), (unsigned)L->num_units);
