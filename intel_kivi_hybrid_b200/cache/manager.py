@@ -236,6 +236,56 @@ class KiviCache:
         self._cache_view = None
         self._cache_view_valid = False
 
+    # ------------------------------------------------------------------ checkpoint
+    def state_dict(self) -> dict:
+        """Everything needed to resume decoding elsewhere: per layer the packed
+        store in use (codes, scales, zeros), the residual ring and the three
+        counters, plus the shape bookkeeping.  Tensors are clones on the cache
+        device.  (The reference has no checkpointing; its reset() is the only
+        state operation, manager.py:292-303.)"""
+        layers = []
+        for st in self._stores:
+            if st is None:
+                layers.append(None)
+                continue
+            ng, nt = st.quant_len // self.G, st.quant_len
+            layers.append({
+                "quant_len": st.quant_len, "res_start": st.res_start, "res_len": st.res_len,
+                "num_units": st.num_units, "dtype": st.dtype,
+                "k_codes": st.k_codes[:, :ng].clone(), "k_scales": st.k_scales[:, :ng].clone(),
+                "k_zeros": st.k_zeros[:, :ng].clone(), "v_codes": st.v_codes[:, :nt].clone(),
+                "v_scales": st.v_scales[:, :nt].clone(), "v_zeros": st.v_zeros[:, :nt].clone(),
+                "k_res": st.k_res.clone(), "v_res": st.v_res.clone()})
+        return {"version": 1, "G": self.G, "R": self.R, "head_dim": self.head_dim, "num_layers": self.num_layers,
+                "num_kv_heads": self.num_kv_heads, "batch_size": self.batch_size, "units": self._units,
+                "flush_count": list(self._flush_count), "serve_device": self._serve_device,
+                "serve_dtype": self._serve_dtype, "layers": layers}
+
+    def load_state_dict(self, state: dict) -> None:
+        """Inverse of state_dict(); the cache must have been built with the same
+        group_size, residual_length, head_dim and num_layers."""
+        assert state["version"] == 1
+        for key, mine in (("G", self.G), ("R", self.R), ("head_dim", self.head_dim), ("num_layers", self.num_layers)):
+            assert state[key] == mine, f"state_dict {key}={state[key]} does not match this cache ({mine})"
+        self.num_kv_heads, self.batch_size = state["num_kv_heads"], state["batch_size"]
+        self._units = state["units"]
+        self._flush_count = list(state["flush_count"])
+        self._serve_device, self._serve_dtype = state["serve_device"], state["serve_dtype"]
+        self._cache_view, self._cache_view_valid = None, False
+        for i, lay in enumerate(state["layers"]):
+            if lay is None:
+                self._stores[i] = None
+                continue
+            cap = max(self._capacity, lay["quant_len"])
+            st = self._new_store(lay["num_units"], cap, lay["dtype"])
+            ng, nt = lay["quant_len"] // self.G, lay["quant_len"]
+            for name, n in (("k_codes", ng), ("k_scales", ng), ("k_zeros", ng),
+                            ("v_codes", nt), ("v_scales", nt), ("v_zeros", nt)):
+                getattr(st, name)[:, :n].copy_(lay[name])
+            st.k_res.copy_(lay["k_res"]); st.v_res.copy_(lay["v_res"])
+            st.quant_len, st.res_start, st.res_len = lay["quant_len"], lay["res_start"], lay["res_len"]
+            self._stores[i] = st
+
     # ------------------------------------------------------------------ stats
     @property
     def total_flushes(self) -> int:

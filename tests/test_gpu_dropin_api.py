@@ -245,3 +245,22 @@ def test_decode_attention_through_kivicache():
     ref = ko.kivi_decode_attention(q, K, V, n_quant, 32, "half_away", dtype=torch.float64).float()
     err = ((out.cpu() - ref).abs().amax(-1) / ref.abs().amax(-1)).max().item()
     assert out.shape == (B, Hkv * n_rep, D) and err < 2e-3
+
+
+def test_state_dict_round_trip_resumes_bit_identically():
+    from kivi_sycl import KiviCache
+    B, Hkv, n_rep, D, T = 1, 2, 4, 128, 420
+    K = ko.make_keys(B, Hkv, T, D, 9).to(torch.bfloat16).cuda()
+    V = ko.make_values(B, Hkv, T, D, 9).to(torch.bfloat16).cuda()
+    q = ko.make_queries(B, Hkv * n_rep, D, 9).to(torch.bfloat16).cuda()
+    a = KiviCache(num_layers=1, head_dim=D, device=DEV)
+    a.add_tokens(((K[:, :, :300], V[:, :, :300]),))
+    state = a.state_dict()
+    b = KiviCache(num_layers=1, head_dim=D, device=DEV)
+    b.load_state_dict(state)
+    for c in (a, b):                                      # both continue with the same tokens
+        for t in range(300, T):
+            c.add_tokens(((K[:, :, :t + 1], V[:, :, :t + 1]),))
+    assert a._quant_token_count == b._quant_token_count and a.total_flushes == b.total_flushes
+    assert torch.equal(a.decode_attention(0, q), b.decode_attention(0, q))
+    assert a.get_stats() == b.get_stats()
