@@ -149,16 +149,7 @@ class KiviCache:
         if past_key_values is not self._cache_view:
             self._cache_view_valid = False
         for i, (k, v) in enumerate(_iter_kv_layers(past_key_values)):
-            if self.batch_size is None:
-                self.batch_size = k.shape[0]
-                self.num_kv_heads = k.shape[1]
-                self._serve_device, self._serve_dtype = k.device, k.dtype
-                n_units = self.batch_size * self.num_kv_heads
-                self._units = unit_partition(n_units, *self.shard) if self.shard else (0, n_units)
-            else:
-                assert k.shape[0] == self.batch_size, (
-                    f"KiviCache batch size changed mid-session ({self.batch_size} -> {k.shape[0]}) at layer {i}. "
-                    f"Call reset() before starting a new request/batch.")
+            self._latch_shapes(k, i)
             st = self._stores[i]
             new_start = 0
             if st is not None and st.quant_len + st.res_len > 0:
@@ -172,21 +163,43 @@ class KiviCache:
                 f"already tracked. add_tokens() was called twice on the same forward output, or the model was "
                 f"fed a past_key_values not obtained from get_full_cache(). Silently skipping here would drop "
                 f"this step's KV and corrupt all subsequent attention.")
-            dtype = torch.bfloat16 if k.dtype == torch.bfloat16 else torch.float32
-            u0, u1 = self._units
-            nk = k[:, :, new_start:, :].flatten(0, 1)[u0:u1].to(device=self.device, dtype=dtype)
-            nv = v[:, :, new_start:, :].flatten(0, 1)[u0:u1].to(device=self.device, dtype=dtype)
-            st = self._ensure_capacity(i, n_new, dtype, u1 - u0)
-            before = st.quant_len
-            st.update(nk, nv, self.rounding)
-            flushed = (st.quant_len - before) // self.G
-            if flushed:
-                self._flush_count[i] += flushed
-                # flushed tokens are now served at 2-bit fidelity: the persistent
-                # view no longer matches (manager.py:244-249)
-                self._cache_view_valid = False
+            self.ingest_layer(i, k[:, :, new_start:, :], v[:, :, new_start:, :])
 
-    def decode_attention(self, layer: int, q: torch.Tensor, out_dtype=None, num_splits: int = 0) -> torch.Tensor:
+    def _latch_shapes(self, k: torch.Tensor, layer: int) -> None:
+        if self.batch_size is None:
+            self.batch_size = k.shape[0]
+            self.num_kv_heads = k.shape[1]
+            self._serve_device, self._serve_dtype = k.device, k.dtype
+            n_units = self.batch_size * self.num_kv_heads
+            self._units = unit_partition(n_units, *self.shard) if self.shard else (0, n_units)
+        else:
+            assert k.shape[0] == self.batch_size, (
+                f"KiviCache batch size changed mid-session ({self.batch_size} -> {k.shape[0]}) at layer {layer}. "
+                f"Call reset() before starting a new request/batch.")
+
+    def ingest_layer(self, layer: int, new_k: torch.Tensor, new_v: torch.Tensor) -> None:
+        """Append the NEW tokens of one layer ([B, H, n_new, D]) to the residual
+        ring and flush whole groups while the window holds >= R tokens.  This is
+        the per-layer body of add_tokens(); a past_key_values object that streams
+        the model's K/V into the cache calls it directly."""
+        self._latch_shapes(new_k, layer)
+        n_new = new_k.shape[2]
+        dtype = torch.bfloat16 if new_k.dtype == torch.bfloat16 else torch.float32
+        u0, u1 = self._units
+        nk = new_k.flatten(0, 1)[u0:u1].to(device=self.device, dtype=dtype)
+        nv = new_v.flatten(0, 1)[u0:u1].to(device=self.device, dtype=dtype)
+        st = self._ensure_capacity(layer, n_new, dtype, u1 - u0)
+        before = st.quant_len
+        st.update(nk, nv, self.rounding)
+        flushed = (st.quant_len - before) // self.G
+        if flushed:
+            self._flush_count[layer] += flushed
+            # flushed tokens are now served at 2-bit fidelity: the persistent
+            # view no longer matches (manager.py:244-249)
+            self._cache_view_valid = False
+
+    def decode_attention(self, layer: int, q: torch.Tensor, out_dtype=None, num_splits: int = 0,
+                         sm_scale: float = 0.0) -> torch.Tensor:
         """Fused attention of one decode step over the packed cache of ``layer``:
         softmax(q K^T / sqrt(D)) V over [quantized history || residual window].
         q: [B, Hq, D] on the cache device; returns [B, Hq, D].  No dequantized
@@ -194,14 +207,15 @@ class KiviCache:
         attention, generate.py:75-77, for callers that can hand over q).
         ``num_splits`` fixes how many pieces each unit's history is cut into
         (0 = chosen from the problem size); with the same value a sharded and an
-        unsharded cache give bit-identical outputs."""
+        unsharded cache give bit-identical outputs; ``sm_scale`` overrides the
+        default head_dim**-0.5."""
         st = self._stores[layer]
         assert st is not None, "decode_attention() before any add_tokens()"
         B, Hq, D = q.shape
         n_rep = Hq // self.num_kv_heads
         u0, u1 = self._units
         q_units = q.reshape(B * self.num_kv_heads, n_rep, D)[u0:u1].contiguous()
-        out = st.attention(q_units, n_rep=n_rep, out_dtype=out_dtype, num_splits=num_splits)
+        out = st.attention(q_units, n_rep=n_rep, out_dtype=out_dtype, num_splits=num_splits, sm_scale=sm_scale)
         if self.shard and self.shard[1] > 1:
             out = all_gather_units(out, B * self.num_kv_heads, self.shard[0], self.shard[1])
         return out.reshape(B, Hq, D)
