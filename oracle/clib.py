@@ -16,7 +16,8 @@ _f32 = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 _u8 = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
 
 
-def build(reference="/root/reference"):
+def build(reference=None):
+    reference = reference or os.environ.get("KIVI_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
     subprocess.run(["make", "-s", "-C", _HERE, f"REFERENCE={reference}"], check=True)
 
 

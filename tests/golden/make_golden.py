@@ -1,8 +1,8 @@
 """Generates tests/golden/*.npz by running the REFERENCE's own code.
 
-Run once in a container that has the reference tree (default /root/reference):
+Run once on a machine that has the reference tree:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference      (or set KIVI_REFERENCE_DIR)
 
 What is imported from the reference (never copied):
   * examples/cpu_sim.py::_roundtrip_2bit                       (torch mirror)
@@ -26,7 +26,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("KIVI_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
 sys.path.insert(0, REPO)
 
 
