@@ -5,7 +5,9 @@
                     [--workload cfg2|cfg1|cfg3|small] [--path auto|fp32|mma]
 
 One "step" = one layer-step of fused decode attention over the packed cache of
-the workload (B*Hkv units, Sq quantized + Sr residual tokens each).  At N GPUs
+the workload (B*Hkv units, Sq quantized + Sr residual tokens each); on one GPU
+the steps are replayed from a CUDA graph (one pass over the rotating layer
+buffers per replay), so small workloads are not bound by host launch overhead.  At N GPUs
 every rank holds the workload's units (weak scaling: global batch = N * B) and
 the per-layer outputs are all-gathered over NCCL.  Prints ONE JSON line.
 
@@ -226,17 +228,52 @@ def run_ours(args, wl):
         step(i)
     launches_per_step = cabi.lib.kivi_last_launch_count()
     barrier()
+    # Launch-bound case (small workloads): capture one pass over the rotating layer
+    # buffers in a CUDA graph and replay it; a "step" is still one layer-step.
+    graph = None
+    if args.graph and world == 1:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for i in range(n_buf):
+                    step(i)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for i in range(n_buf):
+                    step(i)
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+        except Exception as exc:          # capture unavailable: time plain launches instead
+            print(f"[bench] CUDA graph capture failed ({exc}); timing plain launches", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
     windows = []
     w0 = time.time()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    ev[0].record()
-    for i in range(args.steps):
-        step(i)
-        ev[i + 1].record()
-    barrier()
-    windows.append((w0, time.time()))
-    total_ms = ev[0].elapsed_time(ev[-1])
-    per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
+    if graph is not None:
+        n_rep_g = max(1, (args.steps + n_buf - 1) // n_buf)          # replays; each = n_buf steps
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(n_rep_g + 1)]
+        ev[0].record()
+        for i in range(n_rep_g):
+            graph.replay()
+            ev[i + 1].record()
+        barrier()
+        windows.append((w0, time.time()))
+        total_ms = ev[0].elapsed_time(ev[-1]) * args.steps / (n_rep_g * n_buf)
+        per = sorted(ev[i].elapsed_time(ev[i + 1]) / n_buf for i in range(n_rep_g))
+    else:
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+        ev[0].record()
+        for i in range(args.steps):
+            step(i)
+            ev[i + 1].record()
+        barrier()
+        windows.append((w0, time.time()))
+        total_ms = ev[0].elapsed_time(ev[-1])
+        per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
     if world > 1:
         t = torch.tensor([total_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -316,6 +353,7 @@ def run_ours(args, wl):
                 "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": args.workload, "B_per_gpu": B, "Hkv": Hkv, "Hq": Hkv * n_rep, "D": D, "G": G,
                            "n_quant": n_quant, "n_res": n_res, "path": args.path, "layer_buffers_rotated": n_buf,
+                           "cuda_graph": graph is not None,
                            "l2": "inputs larger than L2 (layer buffers rotated)",
                            "parallelism": f"(batch,kv_head) units x{world}, all-gather of outputs"},
                 "decode_tokens_per_s": world * B / (LAYERS * ms_step * 1e-3),
@@ -387,6 +425,8 @@ def main():
     ap.add_argument("--path", default="auto", choices=["auto", "fp32", "mma"])
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-graph", dest="graph", action="store_false",
+                    help="launch every step from Python instead of replaying a CUDA graph (single GPU only)")
     args = ap.parse_args()
     if args.workload == "cfg4":
         return run_quantize(args)
