@@ -32,6 +32,8 @@
 
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 namespace kivi {
 namespace {
 
@@ -357,12 +359,13 @@ __device__ __forceinline__ void residual_part(
         for (int j = 0; j < 4; ++j) {
             const int t = t0 + tl + 8 * j;
             valid[j] = t < t_end;
-            const int slot = (res_start + (valid[j] ? t : t0)) % R;
+            int slot = res_start + (valid[j] ? t : t0);              // both below R
+            if (slot >= R) slot -= R;
             row[j] = k_res + (int64_t)slot * kD + 32 * cq;
 #pragma unroll
             for (int h = 0; h < 4; ++h) acc[j][h] = 0.0f;
         }
-#pragma unroll 1
+#pragma unroll 2
         for (int c = 0; c < 4; ++c) {
             float kv[4][8];
 #pragma unroll
@@ -411,16 +414,23 @@ __device__ __forceinline__ void residual_part(
         const int ntok = t_end - t0 < 32 ? t_end - t0 : 32;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
+            if (8 * j >= ntok) break;
+            // eight value rows in flight at once; a token past the end re-reads
+            // row t0 and carries p = 0
+            float vv[8][4];
+#pragma unroll
             for (int tk = 0; tk < 8; ++tk) {
-                if (8 * j + tk >= ntok) break;
-                const int slot = (res_start + t0 + 8 * j + tk) % R;
-                float vv[4];
-                RowVec<T>::load4(v_res + (int64_t)slot * kD + 4 * lane, vv);
+                int slot = res_start + t0 + (8 * j + tk < ntok ? 8 * j + tk : 0);
+                if (slot >= R) slot -= R;
+                RowVec<T>::load4(v_res + (int64_t)slot * kD + 4 * lane, vv[tk]);
+            }
+#pragma unroll
+            for (int tk = 0; tk < 8; ++tk) {
 #pragma unroll
                 for (int h = 0; h < 4; ++h) {
                     const float ph = __shfl_sync(0xffffffffu, p[j][h], 4 * tk);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) o[h][i] = fmaf(ph, vv[i], o[h][i]);
+                    for (int i = 0; i < 4; ++i) o[h][i] = fmaf(ph, vv[tk][i], o[h][i]);
                 }
             }
         }
@@ -688,10 +698,14 @@ void attn_mma_residual_plan(int res_len, int* n_res_splits, int* res_chunk) {
 int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
                  const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
                  int n_res_splits, int res_chunk, float* part_o, float* part_ml, cudaStream_t st) {
-    static thread_local bool attr_set = false;
-    if (!attr_set) {
+    // the opt-in shared-memory size is a per-device attribute of the kernel
+    static std::atomic<bool> attr_set[64];
+    int dev = 0;
+    KIVI_CUDA_OK(cudaGetDevice(&dev));
+    KIVI_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+    if (!attr_set[dev].load(std::memory_order_acquire)) {
         KIVI_CUDA_OK(cudaFuncSetAttribute(attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-        attr_set = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     dim3 grid((unsigned)(nq_splits + n_res_splits), (unsigned)L->num_units);
     attn_mma_kernel<<<grid, kWarps * 32, kSmemBytes, st>>>(*L, quant_len, res_start, res_len, q, q_dtype, scale_log2,
