@@ -85,19 +85,19 @@ flush_keys_kernel(TokenSource src, uint8_t* __restrict__ k_codes, float* __restr
         if (GT > 0) {
 #pragma unroll
             for (int j = 0; j < GT / 4; ++j) {
-                float q0 = code_of<HALF_EVEN>(x[4 * j], mn, scale, rcp);
-                float q1 = code_of<HALF_EVEN>(x[4 * j + 1], mn, scale, rcp);
-                float q2 = code_of<HALF_EVEN>(x[4 * j + 2], mn, scale, rcp);
-                float q3 = code_of<HALF_EVEN>(x[4 * j + 3], mn, scale, rcp);
+                float q0 = code_magic<HALF_EVEN>(x[4 * j], mn, scale, rcp);
+                float q1 = code_magic<HALF_EVEN>(x[4 * j + 1], mn, scale, rcp);
+                float q2 = code_magic<HALF_EVEN>(x[4 * j + 2], mn, scale, rcp);
+                float q3 = code_magic<HALF_EVEN>(x[4 * j + 3], mn, scale, rcp);
                 s_block[kblock_offset(d, j, Q, W)] =
-                    (uint8_t)__float2int_rn(fmaf(q3, 64.0f, fmaf(q2, 16.0f, fmaf(q1, 4.0f, q0))));
+                    (uint8_t)pack4_magic(q0, q1, q2, q3);
             }
         } else {
             for (int j = 0; j < Q; ++j) {
                 uint32_t byte = 0;
                 for (int e = 0; e < 4; ++e) {
-                    float q = code_of<HALF_EVEN>(src_load(src, u, tau0 + 4 * j + e, d), mn, scale, rcp);
-                    byte |= (uint32_t)__float2int_rn(q) << (2 * e);
+                    const float q = code_magic<HALF_EVEN>(src_load(src, u, tau0 + 4 * j + e, d), mn, scale, rcp);
+                    byte |= (__float_as_uint(q) & 3u) << (2 * e);
                 }
                 s_block[kblock_offset(d, j, Q, W)] = (uint8_t)byte;
             }
@@ -158,9 +158,9 @@ flush_keys_fast_kernel(TokenSource src, uint8_t* __restrict__ k_codes, float* __
     k_zeros[((int64_t)u * max_groups + g) * D + d] = mn;
 #pragma unroll
     for (int j = 0; j < Q; ++j) {
-        const float q0 = code_of<HALF_EVEN>(x[4 * j], mn, scale, rcp), q1 = code_of<HALF_EVEN>(x[4 * j + 1], mn, scale, rcp);
-        const float q2 = code_of<HALF_EVEN>(x[4 * j + 2], mn, scale, rcp), q3 = code_of<HALF_EVEN>(x[4 * j + 3], mn, scale, rcp);
-        s_block[kblock_offset(d, j, Q, 64)] = (uint8_t)__float2int_rn(fmaf(q3, 64.0f, fmaf(q2, 16.0f, fmaf(q1, 4.0f, q0))));
+        const float q0 = code_magic<HALF_EVEN>(x[4 * j], mn, scale, rcp), q1 = code_magic<HALF_EVEN>(x[4 * j + 1], mn, scale, rcp);
+        const float q2 = code_magic<HALF_EVEN>(x[4 * j + 2], mn, scale, rcp), q3 = code_magic<HALF_EVEN>(x[4 * j + 3], mn, scale, rcp);
+        s_block[kblock_offset(d, j, Q, 64)] = (uint8_t)pack4_magic(q0, q1, q2, q3);
     }
     __syncthreads();
     uint8_t* dst = k_codes + ((int64_t)u * max_groups + g) * (D * Q);
@@ -197,8 +197,8 @@ flush_values_kernel(TokenSource src, uint8_t* __restrict__ v_codes, float* __res
         uint32_t byte = 0;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            float q = code_of<HALF_EVEN>(src_load(src, u, tau, gd * G + i + e), mn, scale, rcp);
-            byte |= (uint32_t)__float2int_rn(q) << (2 * e);
+            const float q = code_magic<HALF_EVEN>(src_load(src, u, tau, gd * G + i + e), mn, scale, rcp);
+            byte |= (__float_as_uint(q) & 3u) << (2 * e);
         }
         dst[vcode_offset(t, gd * (G / 4) + i / 4, D, G)] = (uint8_t)byte;
     }
@@ -254,9 +254,9 @@ flush_values_fast_kernel(TokenSource src, uint8_t* __restrict__ v_codes, float* 
         uint32_t bytes = 0;
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
-            const float q0 = code_of<HALF_EVEN>(v[it][4 * b + 0], mn, scale, rcp), q1 = code_of<HALF_EVEN>(v[it][4 * b + 1], mn, scale, rcp);
-            const float q2 = code_of<HALF_EVEN>(v[it][4 * b + 2], mn, scale, rcp), q3 = code_of<HALF_EVEN>(v[it][4 * b + 3], mn, scale, rcp);
-            bytes |= (uint32_t)__float2int_rn(fmaf(q3, 64.0f, fmaf(q2, 16.0f, fmaf(q1, 4.0f, q0)))) << (8 * b);
+            const float q0 = code_magic<HALF_EVEN>(v[it][4 * b + 0], mn, scale, rcp), q1 = code_magic<HALF_EVEN>(v[it][4 * b + 1], mn, scale, rcp);
+            const float q2 = code_magic<HALF_EVEN>(v[it][4 * b + 2], mn, scale, rcp), q3 = code_magic<HALF_EVEN>(v[it][4 * b + 3], mn, scale, rcp);
+            bytes |= pack4_magic(q0, q1, q2, q3) << (8 * b);
         }
         // offsets relative to the CTA's first token (a multiple of 64, so block aligned)
         s_codes[vcode_offset(tl[it], lane16 * 2, D, G)] = (uint8_t)bytes;
@@ -275,6 +275,159 @@ flush_values_fast_kernel(TokenSource src, uint8_t* __restrict__ v_codes, float* 
     float4* gs = reinterpret_cast<float4*>(v_scales + t_first * (D / G));
     float4* gz = reinterpret_cast<float4*>(v_zeros + t_first * (D / G));
     for (int i = threadIdx.x; i < n_here * 2; i += 256) gc[i] = reinterpret_cast<const uint4*>(s_codes)[i];
+    for (int i = threadIdx.x; i < n_here; i += 256) {
+        gs[i] = reinterpret_cast<const float4*>(s_scale)[i];
+        gz[i] = reinterpret_cast<const float4*>(s_zero)[i];
+    }
+}
+
+// ---- bulk prefill: groups cut straight out of the new tensor ----------------
+// Two elements of one token row as floats.
+template <typename T> struct Load2;
+template <> struct Load2<float> {
+    __device__ static void run(const float* p, float& a, float& b) {
+        const float2 t = __ldg(reinterpret_cast<const float2*>(p));
+        a = t.x; b = t.y;
+    }
+};
+template <> struct Load2<__nv_bfloat16> {
+    __device__ static void run(const __nv_bfloat16* p, float& a, float& b) {
+        const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(p));
+        a = __uint_as_float(w << 16); b = __uint_as_float(w & 0xffff0000u);
+    }
+};
+
+// Keys for D = 128, G = 32, every token of the group in the new tensor: a warp
+// owns 64 channels of one group, lane l channels 2l and 2l+1 of that half.  The
+// 32 loads of a lane (one per token) are independent and each covers a full
+// 128- or 256-byte piece of the token row across the warp, so nothing is staged
+// and no barrier is needed; a lane keeps its 64 values in registers, quantizes
+// its two channels over the 32 tokens and writes its byte pairs (channels 2l and
+// 2l+1 are neighbours in the key block) and scale/zero pairs directly.
+// `fresh` points at the first token of the launch's first group;
+// grid = (ceil(2*n_groups / 4), units), 4 warps per CTA.
+template <typename TF, bool HALF_EVEN>
+__global__ void __launch_bounds__(128)
+flush_keys_direct_kernel(const TF* __restrict__ fresh, int64_t unit_stride, int64_t tok_stride,
+                         uint8_t* __restrict__ k_codes, float* __restrict__ k_scales,
+                         float* __restrict__ k_zeros, int64_t max_groups, int64_t group0, int64_t n_groups) {
+    constexpr int D = 128, G = 32, Q = 8;
+    const int u = blockIdx.y;
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);      // (group, half)
+    if (item >= 2 * n_groups) return;
+    const int64_t gi = item >> 1;
+    const int d = 64 * (int)(item & 1) + 2 * lane;
+    const TF* src = fresh + (int64_t)u * unit_stride + gi * G * tok_stride + d;
+    float x0[G], x1[G];
+#pragma unroll
+    for (int t = 0; t < G; ++t) Load2<TF>::run(src + t * tok_stride, x0[t], x1[t]);
+    float mn0 = x0[0], mx0 = x0[0], mn1 = x1[0], mx1 = x1[0];
+#pragma unroll
+    for (int t = 1; t < G; ++t) {
+        mn0 = fminf(mn0, x0[t]); mx0 = fmaxf(mx0, x0[t]);
+        mn1 = fminf(mn1, x1[t]); mx1 = fmaxf(mx1, x1[t]);
+    }
+    // the reference starts its reduction from +-1e30 (quant_tile.hpp:43-44)
+    mn0 = fminf(mn0, 1e30f); mx0 = fmaxf(mx0, -1e30f); mn1 = fminf(mn1, 1e30f); mx1 = fmaxf(mx1, -1e30f);
+    const float s0 = group_scale(mn0, mx0), s1 = group_scale(mn1, mx1);
+    const float r0 = group_rcp(s0), r1 = group_rcp(s1);
+    const int64_t g = group0 + gi;
+    const int64_t meta = ((int64_t)u * max_groups + g) * D + d;
+    *reinterpret_cast<float2*>(k_scales + meta) = make_float2(s0, s1);
+    *reinterpret_cast<float2*>(k_zeros + meta) = make_float2(mn0, mn1);
+    uint8_t* dst = k_codes + ((int64_t)u * max_groups + g) * (D * Q) + kblock_offset(d, 0, Q, 64);
+    if (r0 != 0.0f && r1 != 0.0f) {
+#pragma unroll
+        for (int j = 0; j < Q; ++j) {
+            const uint32_t b0 = pack4_magic(code_magic_rcp<HALF_EVEN>(x0[4 * j], mn0, s0, r0), code_magic_rcp<HALF_EVEN>(x0[4 * j + 1], mn0, s0, r0),
+                                            code_magic_rcp<HALF_EVEN>(x0[4 * j + 2], mn0, s0, r0), code_magic_rcp<HALF_EVEN>(x0[4 * j + 3], mn0, s0, r0));
+            const uint32_t b1 = pack4_magic(code_magic_rcp<HALF_EVEN>(x1[4 * j], mn1, s1, r1), code_magic_rcp<HALF_EVEN>(x1[4 * j + 1], mn1, s1, r1),
+                                            code_magic_rcp<HALF_EVEN>(x1[4 * j + 2], mn1, s1, r1), code_magic_rcp<HALF_EVEN>(x1[4 * j + 3], mn1, s1, r1));
+            *reinterpret_cast<uint16_t*>(dst + j * 64) = (uint16_t)(b0 | (b1 << 8));
+        }
+    } else {
+        // a scale too large for a reciprocal (rare): plain divisions, the values
+        // read again so that the register arrays are never indexed dynamically
+#pragma unroll 1
+        for (int j = 0; j < Q; ++j) {
+            float m0[4], m1[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float a, b;
+                Load2<TF>::run(src + (4 * j + e) * tok_stride, a, b);
+                m0[e] = code_magic<HALF_EVEN>(a, mn0, s0, r0);
+                m1[e] = code_magic<HALF_EVEN>(b, mn1, s1, r1);
+            }
+            *reinterpret_cast<uint16_t*>(dst + j * 64) =
+                (uint16_t)(pack4_magic(m0[0], m0[1], m0[2], m0[3]) | (pack4_magic(m1[0], m1[1], m1[2], m1[3]) << 8));
+        }
+    }
+}
+
+// Values for D = 128, G = 32, every token in the new tensor: a thread owns one
+// (token, channel group) = 32 consecutive channels (four or eight independent
+// 128-bit loads, no shuffles), thread 4*tl + gd of the CTA token tl of the CTA's
+// 64.  The two value blocks of the CTA are assembled in shared memory (planes
+// padded to 68 words so that the byte stores of a warp spread over the banks)
+// and leave with 128-bit stores.  `fresh` points at the launch's first token,
+// tok0 (a multiple of G) is its destination index.
+template <typename TF, bool HALF_EVEN>
+__global__ void __launch_bounds__(256)
+flush_values_direct_kernel(const TF* __restrict__ fresh, int64_t unit_stride, int64_t tok_stride,
+                           uint8_t* __restrict__ v_codes, float* __restrict__ v_scales,
+                           float* __restrict__ v_zeros, int64_t max_tokens, int64_t tok0, int64_t n_tok) {
+    constexpr int D = 128, G = 32, PLANE = 68;          // words per (block, gd) plane in shared memory
+    __shared__ __align__(16) uint32_t s_codes[2 * 4 * PLANE];
+    __shared__ __align__(16) float s_scale[2 * 128];
+    __shared__ __align__(16) float s_zero[2 * 128];
+    const int u = blockIdx.y;
+    const int tl = threadIdx.x >> 2, gd = threadIdx.x & 3;
+    const int64_t cta_tau0 = (int64_t)blockIdx.x * 64;
+    const int64_t tau = cta_tau0 + tl;
+    if (tau < n_tok) {
+        const TF* src = fresh + (int64_t)u * unit_stride + tau * tok_stride + gd * G;
+        float x[G];
+#pragma unroll
+        for (int k = 0; k < G / 8; ++k) Load8<TF>::run(src + 8 * k, *reinterpret_cast<float(*)[8]>(&x[8 * k]));
+        float mn = 1e30f, mx = -1e30f;
+#pragma unroll
+        for (int i = 0; i < G; ++i) { mn = fminf(mn, x[i]); mx = fmaxf(mx, x[i]); }
+        const float scale = group_scale(mn, mx);
+        const float rcp = group_rcp(scale);
+        // token tl = 32*blk + 16*kappa + 4*c + n: byte n of word gd*64 + kappa*32 + r*4 + c
+        const int tt = tl & 31;
+        uint8_t* sc = reinterpret_cast<uint8_t*>(s_codes + ((tl >> 5) * 4 + gd) * PLANE + (tt >> 4) * 32 + ((tt >> 2) & 3)) + (tt & 3);
+        if (rcp != 0.0f) {
+#pragma unroll
+            for (int r = 0; r < G / 4; ++r)
+                sc[r * 16] = (uint8_t)pack4_magic(code_magic_rcp<HALF_EVEN>(x[4 * r], mn, scale, rcp), code_magic_rcp<HALF_EVEN>(x[4 * r + 1], mn, scale, rcp),
+                                                  code_magic_rcp<HALF_EVEN>(x[4 * r + 2], mn, scale, rcp), code_magic_rcp<HALF_EVEN>(x[4 * r + 3], mn, scale, rcp));
+        } else {
+            // a scale too large for a reciprocal (rare): plain divisions on re-read values
+#pragma unroll 1
+            for (int r = 0; r < G / 4; ++r) {
+                float m[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    m[e] = code_magic<HALF_EVEN>(load_as_float(src, sizeof(TF) == 2 ? KIVI_BF16 : KIVI_F32, 4 * r + e), mn, scale, rcp);
+                sc[r * 16] = (uint8_t)pack4_magic(m[0], m[1], m[2], m[3]);
+            }
+        }
+        const int mi = (int)vmeta_index(tl, gd, D, G);
+        s_scale[mi] = scale; s_zero[mi] = mn;
+    }
+    __syncthreads();
+    const int64_t left = n_tok - cta_tau0;
+    const int n_here = left < 64 ? (int)left : 64;                       // multiple of 32
+    const int64_t t_first = (int64_t)u * max_tokens + tok0 + cta_tau0;
+    uint4* gc = reinterpret_cast<uint4*>(v_codes + t_first * (D / 4));
+    float4* gs = reinterpret_cast<float4*>(v_scales + t_first * (D / G));
+    float4* gz = reinterpret_cast<float4*>(v_zeros + t_first * (D / G));
+    for (int i = threadIdx.x; i < n_here * 2; i += 256) {
+        // 16-byte piece i of the CTA's blocks: block i/64, plane (i%64)/16, piece i%16
+        gc[i] = *reinterpret_cast<const uint4*>(s_codes + ((i >> 6) * 4 + ((i >> 4) & 3)) * PLANE + (i & 15) * 4);
+    }
     for (int i = threadIdx.x; i < n_here; i += 256) {
         gs[i] = reinterpret_cast<const float4*>(s_scale)[i];
         gz[i] = reinterpret_cast<const float4*>(s_zero)[i];
@@ -440,59 +593,98 @@ extern "C" int kivi_cache_update(const kivi_layer* L, int64_t quant_len, int res
     if (f > 0) {
         const int64_t group0 = quant_len / G;
         KIVI_REQUIRE(f <= 0x7fffffff && L->num_units <= 65535, "grid too large");
-        dim3 grid((unsigned)f, (unsigned)L->num_units);
         const int threads = D >= 256 ? 256 : (D >= 128 ? 128 : (D >= 64 ? 64 : 32));
         const size_t smem = (size_t)D * G / 4;
         const bool he = rounding == KIVI_ROUND_HALF_EVEN;
-        auto al16k = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-        const int eszk = elem_size(new_dtype);
-        const bool fast_k = D == 128 && G == 32 && al16k(new_k) && al16k(L->k_res) && al16k(L->k_codes) &&
-                            (unit_stride_k * eszk) % 16 == 0 && (tok_stride_k * eszk) % 16 == 0;
-        if (fast_k) {
-#define KIVI_FK(TR, TF)                                                                                              \
-            do {                                                                                                     \
-                if (he) flush_keys_fast_kernel<TR, TF, true><<<grid, 128, 0, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0); \
-                else flush_keys_fast_kernel<TR, TF, false><<<grid, 128, 0, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0);   \
-            } while (0)
-            if (L->res_dtype == KIVI_F32 && new_dtype == KIVI_F32) KIVI_FK(float, float);
-            else if (L->res_dtype == KIVI_F32) KIVI_FK(float, __nv_bfloat16);
-            else if (new_dtype == KIVI_F32) KIVI_FK(__nv_bfloat16, float);
-            else KIVI_FK(__nv_bfloat16, __nv_bfloat16);
-#undef KIVI_FK
-        } else if (G == 32) {
-            if (he) flush_keys_kernel<32, true><<<grid, threads, smem, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0, G);
-            else flush_keys_kernel<32, false><<<grid, threads, smem, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0, G);
-        } else {
-            if (he) flush_keys_kernel<0, true><<<grid, threads, smem, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0, G);
-            else flush_keys_kernel<0, false><<<grid, threads, smem, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0, G);
-        }
-        KIVI_LAUNCH_OK();
-        const int64_t n_tok = (int64_t)f * G;
         auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
         const int esz = elem_size(new_dtype);
+        const bool fast_k = D == 128 && G == 32 && al16(new_k) && al16(L->k_res) && al16(L->k_codes) &&
+                            al16(L->k_scales) && al16(L->k_zeros) &&
+                            (unit_stride_k * esz) % 16 == 0 && (tok_stride_k * esz) % 16 == 0;
+        // Groups that still contain ring tokens go through the kernels that read
+        // the virtual sequence; the rest (a bulk prefill) is cut straight out of
+        // the new tensor by the direct kernels.
+        const int64_t g_ring = fast_k ? ((int64_t)(res_len + G - 1) / G < f ? (int64_t)(res_len + G - 1) / G : f) : f;
+        if (g_ring > 0) {
+            dim3 grid((unsigned)g_ring, (unsigned)L->num_units);
+            if (fast_k) {
+#define KIVI_FK(TR, TF)                                                                                              \
+                do {                                                                                                 \
+                    if (he) flush_keys_fast_kernel<TR, TF, true><<<grid, 128, 0, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0); \
+                    else flush_keys_fast_kernel<TR, TF, false><<<grid, 128, 0, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0);   \
+                } while (0)
+                if (L->res_dtype == KIVI_F32 && new_dtype == KIVI_F32) KIVI_FK(float, float);
+                else if (L->res_dtype == KIVI_F32) KIVI_FK(float, __nv_bfloat16);
+                else if (new_dtype == KIVI_F32) KIVI_FK(__nv_bfloat16, float);
+                else KIVI_FK(__nv_bfloat16, __nv_bfloat16);
+#undef KIVI_FK
+            } else if (G == 32) {
+                if (he) flush_keys_kernel<32, true><<<grid, threads, smem, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0, G);
+                else flush_keys_kernel<32, false><<<grid, threads, smem, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0, G);
+            } else {
+                if (he) flush_keys_kernel<0, true><<<grid, threads, smem, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0, G);
+                else flush_keys_kernel<0, false><<<grid, threads, smem, st>>>(sk, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0, G);
+            }
+            KIVI_LAUNCH_OK();
+            launches += 1;
+        }
+        if (g_ring < f) {
+            const int64_t n_direct = f - g_ring;
+            const int64_t first = g_ring * G - res_len;                       // index in the new tensor
+            dim3 grid((unsigned)((2 * n_direct + 3) / 4), (unsigned)L->num_units);
+#define KIVI_DK(TF)                                                                                                  \
+            do {                                                                                                     \
+                const TF* p = reinterpret_cast<const TF*>(new_k) + first * tok_stride_k;                             \
+                if (he) flush_keys_direct_kernel<TF, true><<<grid, 128, 0, st>>>(p, unit_stride_k, tok_stride_k, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0 + g_ring, n_direct); \
+                else flush_keys_direct_kernel<TF, false><<<grid, 128, 0, st>>>(p, unit_stride_k, tok_stride_k, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0 + g_ring, n_direct);   \
+            } while (0)
+            if (new_dtype == KIVI_F32) KIVI_DK(float); else KIVI_DK(__nv_bfloat16);
+#undef KIVI_DK
+            KIVI_LAUNCH_OK();
+            launches += 1;
+        }
+        const int64_t n_tok = (int64_t)f * G;
         const bool fast_v = D == 128 && G == 32 && al16(new_v) && al16(L->v_res) && al16(L->v_codes) &&
                             al16(L->v_scales) && al16(L->v_zeros) &&
                             (unit_stride_v * esz) % 16 == 0 && (tok_stride_v * esz) % 16 == 0;
-        if (fast_v) {
-            dim3 gridv((unsigned)((n_tok + 63) / 64), (unsigned)L->num_units);
+        // tokens before t_ring (whole 64-token CTAs that may touch the ring) take the virtual-sequence kernels
+        const int64_t t_ring = fast_v ? ((int64_t)(res_len + 63) / 64 * 64 < n_tok ? (int64_t)(res_len + 63) / 64 * 64 : n_tok) : n_tok;
+        if (t_ring > 0) {
+            if (fast_v) {
+                dim3 gridv((unsigned)((t_ring + 63) / 64), (unsigned)L->num_units);
 #define KIVI_FV(TR, TF)                                                                                              \
-            do {                                                                                                     \
-                if (he) flush_values_fast_kernel<TR, TF, true><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, n_tok); \
-                else flush_values_fast_kernel<TR, TF, false><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, n_tok);   \
-            } while (0)
-            if (L->res_dtype == KIVI_F32 && new_dtype == KIVI_F32) KIVI_FV(float, float);
-            else if (L->res_dtype == KIVI_F32) KIVI_FV(float, __nv_bfloat16);
-            else if (new_dtype == KIVI_F32) KIVI_FV(__nv_bfloat16, float);
-            else KIVI_FV(__nv_bfloat16, __nv_bfloat16);
+                do {                                                                                                 \
+                    if (he) flush_values_fast_kernel<TR, TF, true><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, t_ring); \
+                    else flush_values_fast_kernel<TR, TF, false><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, t_ring);   \
+                } while (0)
+                if (L->res_dtype == KIVI_F32 && new_dtype == KIVI_F32) KIVI_FV(float, float);
+                else if (L->res_dtype == KIVI_F32) KIVI_FV(float, __nv_bfloat16);
+                else if (new_dtype == KIVI_F32) KIVI_FV(__nv_bfloat16, float);
+                else KIVI_FV(__nv_bfloat16, __nv_bfloat16);
 #undef KIVI_FV
-        } else {
-            const int64_t items = n_tok * (D / G);
-            dim3 gridv((unsigned)((items + 255) / 256), (unsigned)L->num_units);
-            if (he) flush_values_kernel<true><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, n_tok, G);
-            else flush_values_kernel<false><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, n_tok, G);
+            } else {
+                const int64_t items = n_tok * (D / G);
+                dim3 gridv((unsigned)((items + 255) / 256), (unsigned)L->num_units);
+                if (he) flush_values_kernel<true><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, n_tok, G);
+                else flush_values_kernel<false><<<gridv, 256, 0, st>>>(sv, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len, n_tok, G);
+            }
+            KIVI_LAUNCH_OK();
+            launches += 1;
         }
-        KIVI_LAUNCH_OK();
-        launches += 2;
+        if (t_ring < n_tok) {
+            const int64_t n_direct = n_tok - t_ring;
+            dim3 gridv((unsigned)((n_direct + 63) / 64), (unsigned)L->num_units);
+#define KIVI_DV(TF)                                                                                                  \
+            do {                                                                                                     \
+                const TF* p = reinterpret_cast<const TF*>(new_v) + (t_ring - res_len) * tok_stride_v;                \
+                if (he) flush_values_direct_kernel<TF, true><<<gridv, 256, 0, st>>>(p, unit_stride_v, tok_stride_v, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len + t_ring, n_direct); \
+                else flush_values_direct_kernel<TF, false><<<gridv, 256, 0, st>>>(p, unit_stride_v, tok_stride_v, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len + t_ring, n_direct);   \
+            } while (0)
+            if (new_dtype == KIVI_F32) KIVI_DV(float); else KIVI_DV(__nv_bfloat16);
+#undef KIVI_DV
+            KIVI_LAUNCH_OK();
+            launches += 1;
+        }
     }
     // tokens of the virtual sequence that stay: [f*G, res_len + n_new); those
     // with tau >= res_len come from the new tensor and must be copied in.

@@ -36,8 +36,22 @@ int num_sms();
 
 // ---- arithmetic that must match the reference bit for bit ------------------
 // scale = (max - min) / 3.0f + 1e-10f      (quantize_kernels.cpp:46)
+// The division by 3 is the correctly rounded quotient from a multiply and two
+// FMAs (q0 = RN(r * RN(1/3)), e = r - 3*q0 exact, RN(q0 + e * RN(1/3))); checked
+// equal to r / 3.0f for every mantissa at 18 exponents spanning the range and
+// for every subnormal r.  An infinite range takes the plain division.
 __device__ __forceinline__ float group_scale(float mn, float mx) {
-    return __fadd_rn(__fdiv_rn(__fsub_rn(mx, mn), 3.0f), 1e-10f);
+    const float r = __fsub_rn(mx, mn);
+    const float third = 0.3333333432674407958984375f;    // RN(1/3)
+    float q;
+    if (r <= 3.0e38f) {
+        const float q0 = __fmul_rn(r, third);
+        const float e = __fmaf_rn(-3.0f, q0, r);
+        q = __fmaf_rn(e, third, q0);
+    } else {
+        q = __fdiv_rn(r, 3.0f);
+    }
+    return __fadd_rn(q, 1e-10f);
 }
 
 // Per-group reciprocal for the exact division below; 0 selects the plain IEEE
@@ -46,14 +60,23 @@ __device__ __forceinline__ float group_rcp(float scale) {
     return scale < 1e30f ? __frcp_rn(scale) : 0.0f;
 }
 
-// q = clamp(round((x - min) / scale), 0, 3) as a float in {0,1,2,3}
-// (quant_tile.hpp:61-66).  The quotient is the correctly rounded IEEE quotient:
-// with r = RN(1/scale), q0 = RN(a*r), e = a - scale*q0 (exact in an FMA),
-// RN(q0 + e*r) equals RN(a/scale) (Markstein's correction step; checked against
-// IEEE division on 6e8 samples including tie-heavy bf16 data).  Three
-// instructions instead of a dozen.  HALF_EVEN selects rintf.
+// q = clamp(round((x - min) / scale), 0, 3)   (quant_tile.hpp:61-66), returned
+// as the float 2^23 + q, whose two lowest mantissa bits are the code.
+//
+// The quotient t is the correctly rounded IEEE quotient: with r = RN(1/scale),
+// q0 = RN(a*r), e = a - scale*q0 (exact in an FMA), RN(q0 + e*r) equals
+// RN(a/scale) (Markstein's correction step; checked against IEEE division on
+// 6e8 samples including tie-heavy bf16 data).
+//
+// Rounding without a round instruction: 0 <= t <= 3.0000005 because
+// a <= RN(max - min) and scale >= RN(RN(max - min) / 3), so the clamp never
+// binds and adding 2^23 leaves round(t) in the mantissa.  Half to even is the
+// add's own rounding.  Half away from zero is floor(t + 0.5): the first add
+// rounds down, which cannot cross an integer n (n is representable, so
+// RD(t + 0.5) >= n exactly when t + 0.5 >= n), the second add rounds down to
+// an integer.
 template <bool HALF_EVEN>
-__device__ __forceinline__ float code_of(float x, float mn, float scale, float rcp) {
+__device__ __forceinline__ float code_magic(float x, float mn, float scale, float rcp) {
     const float a = __fsub_rn(x, mn);
     float t;
     if (rcp != 0.0f) {
@@ -63,16 +86,32 @@ __device__ __forceinline__ float code_of(float x, float mn, float scale, float r
     } else {
         t = __fdiv_rn(a, scale);
     }
-    float r;
-    if (HALF_EVEN) {
-        r = rintf(t);
-    } else {
-        // t >= 0 here, so "half away from zero" is floor(t) + (frac(t) >= 0.5);
-        // t - floor(t) is exact, unlike floor(t + 0.5f).
-        const float fl = floorf(t);
-        r = (__fsub_rn(t, fl) >= 0.5f) ? fl + 1.0f : fl;
-    }
-    return fminf(fmaxf(r, 0.0f), 3.0f);
+    if (HALF_EVEN) return __fadd_rn(t, 8388608.0f);
+    return __fadd_rd(__fadd_rd(t, 0.5f), 8388608.0f);
+}
+
+// code_magic for a group whose reciprocal exists (rcp != 0): no branch per element
+template <bool HALF_EVEN>
+__device__ __forceinline__ float code_magic_rcp(float x, float mn, float scale, float rcp) {
+    const float a = __fsub_rn(x, mn);
+    const float q0 = __fmul_rn(a, rcp);
+    const float e = __fmaf_rn(-scale, q0, a);
+    const float t = __fmaf_rn(e, rcp, q0);
+    if (HALF_EVEN) return __fadd_rn(t, 8388608.0f);
+    return __fadd_rd(__fadd_rd(t, 0.5f), 8388608.0f);
+}
+
+// the code as a float in {0, 1, 2, 3}
+template <bool HALF_EVEN>
+__device__ __forceinline__ float code_of(float x, float mn, float scale, float rcp) {
+    return __fsub_rn(code_magic<HALF_EVEN>(x, mn, scale, rcp), 8388608.0f);
+}
+
+// byte q0 | q1<<2 | q2<<4 | q3<<6 (pack_kernels.cpp:20-24) from four code_magic
+// values: the 2^23 offsets only reach bits 8 and up of the integer sum.
+__device__ __forceinline__ uint32_t pack4_magic(float m0, float m1, float m2, float m3) {
+    const uint32_t b = ((__float_as_uint(m3) * 4u + __float_as_uint(m2)) * 4u + __float_as_uint(m1)) * 4u + __float_as_uint(m0);
+    return b & 0xffu;
 }
 
 // out = float(q) * scale + zero with a separate multiply and add

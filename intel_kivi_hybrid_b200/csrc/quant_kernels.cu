@@ -108,12 +108,11 @@ group_quant_kernel(const T* __restrict__ in, uint8_t* __restrict__ packed,
             uint32_t bytes[(BPL + 3) / 4] = {};
 #pragma unroll
             for (int b = 0; b < BPL; ++b) {
-                float q0 = code_of<HALF_EVEN>(v[it][4 * b + 0], mn, scale, rcp);
-                float q1 = code_of<HALF_EVEN>(v[it][4 * b + 1], mn, scale, rcp);
-                float q2 = code_of<HALF_EVEN>(v[it][4 * b + 2], mn, scale, rcp);
-                float q3 = code_of<HALF_EVEN>(v[it][4 * b + 3], mn, scale, rcp);
-                // exact small integers: assemble the byte in fp32, convert once
-                uint32_t byte = (uint32_t)__float2int_rn(fmaf(q3, 64.0f, fmaf(q2, 16.0f, fmaf(q1, 4.0f, q0))));
+                float q0 = code_magic<HALF_EVEN>(v[it][4 * b + 0], mn, scale, rcp);
+                float q1 = code_magic<HALF_EVEN>(v[it][4 * b + 1], mn, scale, rcp);
+                float q2 = code_magic<HALF_EVEN>(v[it][4 * b + 2], mn, scale, rcp);
+                float q3 = code_magic<HALF_EVEN>(v[it][4 * b + 3], mn, scale, rcp);
+                uint32_t byte = pack4_magic(q0, q1, q2, q3);
                 bytes[b / 4] |= byte << (8 * (b % 4));
             }
             uint8_t* dst = s_codes + lg[it] * (G / 4) + sub * BPL;
@@ -187,8 +186,8 @@ group_quant_generic_kernel(const void* __restrict__ in, int in_dtype, uint8_t* _
             uint32_t byte = 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                float q = code_of<HALF_EVEN>(load_as_float(in, in_dtype, base + i + j), mn, scale, rcp);
-                byte |= (uint32_t)__float2int_rn(q) << (2 * j);
+                const float q = code_magic<HALF_EVEN>(load_as_float(in, in_dtype, base + i + j), mn, scale, rcp);
+                byte |= (__float_as_uint(q) & 3u) << (2 * j);
             }
             packed[g * (G / 4) + i / 4] = (uint8_t)byte;
         }

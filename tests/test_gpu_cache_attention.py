@@ -124,6 +124,42 @@ def test_value_blocks_of_llama_shaped_layers_hold_the_reference_bytes(cabi):
     assert torch.equal(k.cpu(), units(sk)) and torch.equal(v.cpu(), units(sv))
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rounding", ["half_away", "half_even"])
+def test_chunked_bulk_prefill_mixes_ring_and_new_tensor_groups(cabi, dtype, rounding):
+    """Bulk updates whose first groups still hold ring tokens (virtual-sequence
+    kernels) and whose remaining groups are cut straight out of the new tensor
+    (direct kernels), in ragged chunks; one key channel and one value group carry
+    a range so large that the scale has no reciprocal (plain-division branch)."""
+    B, H, D, G, R = 1, 3, 128, 32, 128
+    chunks = [50, 333, 1, 700, 95]
+    T = sum(chunks)
+    K = ko.make_keys(B, H, T, D, seed=5)
+    V = ko.make_values(B, H, T, D, seed=6)
+    K[0, 1, 400:420, 7] = 1.6e38; K[0, 1, 420:440, 7] = -1.6e38
+    V[0, 2, 500, 32:48] = 1.6e38; V[0, 2, 500, 48:64] = -1.6e38
+    if dtype == torch.bfloat16:
+        K, V = K.bfloat16().float(), V.bfloat16().float()
+    oc = ko.OracleCache(D, G, R, rounding=rounding)
+    st = cabi.LayerStore(B * H, D, G, R, 1184, dtype, "cuda")
+    mode = cabi.ROUND_HALF_EVEN if rounding == "half_even" else cabi.ROUND_HALF_AWAY
+    Kc, Vc = units(K).cuda().to(dtype), units(V).cuda().to(dtype)
+    t = 0
+    for n in chunks:
+        oc.append(K[:, :, t:t + n], V[:, :, t:t + n])
+        st.update(Kc[:, t:t + n], Vc[:, t:t + n], mode)
+        t += n
+        assert st.quant_len == oc.quantized_len and st.res_len == oc.residual_len
+    ng = st.quant_len // G
+    ks = torch.stack(oc.k_scales, dim=2).reshape(B * H, ng, D)
+    kz = torch.stack(oc.k_zeros, dim=2).reshape(B * H, ng, D)
+    assert torch.equal(st.k_scales[:, :ng].cpu(), ks) and torch.equal(st.k_zeros[:, :ng].cpu(), kz)
+    assert float(ks.max()) >= 1e30
+    k, v = st.materialize()
+    sk, sv = oc.served()
+    assert torch.equal(k.cpu(), units(sk)) and torch.equal(v.cpu(), units(sv))
+
+
 def test_import_keys_from_operator_layout(cabi):
     B, H, D, G, S = 1, 2, 128, 32, 96
     K = ko.make_keys(B, H, S, D, seed=3)
