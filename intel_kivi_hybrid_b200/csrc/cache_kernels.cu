@@ -282,36 +282,52 @@ flush_values_fast_kernel(TokenSource src, uint8_t* __restrict__ v_codes, float* 
 }
 
 // ---- bulk prefill: groups cut straight out of the new tensor ----------------
-// Two elements of one token row as floats.
-template <typename T> struct Load2;
-template <> struct Load2<float> {
-    __device__ static void run(const float* p, float& a, float& b) {
-        const float2 t = __ldg(reinterpret_cast<const float2*>(p));
-        a = t.x; b = t.y;
-    }
+// Two neighbouring elements kept as loaded (one 32-bit word for bf16, so a
+// lane's group costs half the registers), widened to fp32 only where used.
+// Minimum and maximum of bf16 pairs run on both halves at once; they are exact
+// in any format, and which zero wins a tie between -0 and +0 does not change a
+// code or a dequantized value's numeric value.
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+    using raw = float2;
+    using acc = float2;
+    __device__ static raw load(const float* p) { return __ldg(reinterpret_cast<const float2*>(p)); }
+    __device__ static void widen(raw w, float& a, float& b) { a = w.x; b = w.y; }
+    __device__ static acc first(raw w) { return w; }
+    __device__ static acc lo(acc m, raw w) { return make_float2(fminf(m.x, w.x), fminf(m.y, w.y)); }
+    __device__ static acc hi(acc m, raw w) { return make_float2(fmaxf(m.x, w.x), fmaxf(m.y, w.y)); }
+    __device__ static void finish(acc m, float& a, float& b) { a = m.x; b = m.y; }
 };
-template <> struct Load2<__nv_bfloat16> {
-    __device__ static void run(const __nv_bfloat16* p, float& a, float& b) {
-        const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(p));
-        a = __uint_as_float(w << 16); b = __uint_as_float(w & 0xffff0000u);
-    }
+template <> struct Pair<__nv_bfloat16> {
+    using raw = uint32_t;
+    using acc = __nv_bfloat162;
+    __device__ static raw load(const __nv_bfloat16* p) { return __ldg(reinterpret_cast<const uint32_t*>(p)); }
+    __device__ static void widen(raw w, float& a, float& b) { a = __uint_as_float(w << 16); b = __uint_as_float(w & 0xffff0000u); }
+    __device__ static acc first(raw w) { return *reinterpret_cast<const __nv_bfloat162*>(&w); }
+    __device__ static acc lo(acc m, raw w) { return __hmin2(m, *reinterpret_cast<const __nv_bfloat162*>(&w)); }
+    __device__ static acc hi(acc m, raw w) { return __hmax2(m, *reinterpret_cast<const __nv_bfloat162*>(&w)); }
+    __device__ static void finish(acc m, float& a, float& b) { widen(*reinterpret_cast<const uint32_t*>(&m), a, b); }
 };
 
 // Keys for D = 128, G = 32, every token of the group in the new tensor: a warp
 // owns 64 channels of one group, lane l channels 2l and 2l+1 of that half.  The
 // 32 loads of a lane (one per token) are independent and each covers a full
 // 128- or 256-byte piece of the token row across the warp, so nothing is staged
-// and no barrier is needed; a lane keeps its 64 values in registers, quantizes
-// its two channels over the 32 tokens and writes its byte pairs (channels 2l and
+// and no barrier is needed; a lane keeps its group in registers, quantizes its
+// two channels over the 32 tokens and writes its byte pairs (channels 2l and
 // 2l+1 are neighbours in the key block) and scale/zero pairs directly.
-// `fresh` points at the first token of the launch's first group;
+// `fresh` points at the first token of the launch's first group; DENSE says
+// that token rows follow each other without a gap (tok_stride == 128), which
+// turns the 32 row offsets into immediates.
 // grid = (ceil(2*n_groups / 4), units), 4 warps per CTA.
-template <typename TF, bool HALF_EVEN>
+template <typename TF, bool HALF_EVEN, bool DENSE>
 __global__ void __launch_bounds__(128)
-flush_keys_direct_kernel(const TF* __restrict__ fresh, int64_t unit_stride, int64_t tok_stride,
+flush_keys_direct_kernel(const TF* __restrict__ fresh, int64_t unit_stride, int64_t tok_stride_arg,
                          uint8_t* __restrict__ k_codes, float* __restrict__ k_scales,
                          float* __restrict__ k_zeros, int64_t max_groups, int64_t group0, int64_t n_groups) {
     constexpr int D = 128, G = 32, Q = 8;
+    using P = Pair<TF>;
+    const int64_t tok_stride = DENSE ? (int64_t)D : tok_stride_arg;
     const int u = blockIdx.y;
     const int lane = threadIdx.x & 31;
     const int64_t item = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);      // (group, half)
@@ -319,15 +335,15 @@ flush_keys_direct_kernel(const TF* __restrict__ fresh, int64_t unit_stride, int6
     const int64_t gi = item >> 1;
     const int d = 64 * (int)(item & 1) + 2 * lane;
     const TF* src = fresh + (int64_t)u * unit_stride + gi * G * tok_stride + d;
-    float x0[G], x1[G];
+    typename P::raw w[G];
 #pragma unroll
-    for (int t = 0; t < G; ++t) Load2<TF>::run(src + t * tok_stride, x0[t], x1[t]);
-    float mn0 = x0[0], mx0 = x0[0], mn1 = x1[0], mx1 = x1[0];
+    for (int t = 0; t < G; ++t) w[t] = P::load(src + t * tok_stride);
+    typename P::acc lo = P::first(w[0]), hi = P::first(w[0]);
 #pragma unroll
-    for (int t = 1; t < G; ++t) {
-        mn0 = fminf(mn0, x0[t]); mx0 = fmaxf(mx0, x0[t]);
-        mn1 = fminf(mn1, x1[t]); mx1 = fmaxf(mx1, x1[t]);
-    }
+    for (int t = 1; t < G; ++t) { lo = P::lo(lo, w[t]); hi = P::hi(hi, w[t]); }
+    float mn0, mn1, mx0, mx1;
+    P::finish(lo, mn0, mn1);
+    P::finish(hi, mx0, mx1);
     // the reference starts its reduction from +-1e30 (quant_tile.hpp:43-44)
     mn0 = fminf(mn0, 1e30f); mx0 = fmaxf(mx0, -1e30f); mn1 = fminf(mn1, 1e30f); mx1 = fmaxf(mx1, -1e30f);
     const float s0 = group_scale(mn0, mx0), s1 = group_scale(mn1, mx1);
@@ -340,22 +356,27 @@ flush_keys_direct_kernel(const TF* __restrict__ fresh, int64_t unit_stride, int6
     if (r0 != 0.0f && r1 != 0.0f) {
 #pragma unroll
         for (int j = 0; j < Q; ++j) {
-            const uint32_t b0 = pack4_magic(code_magic_rcp<HALF_EVEN>(x0[4 * j], mn0, s0, r0), code_magic_rcp<HALF_EVEN>(x0[4 * j + 1], mn0, s0, r0),
-                                            code_magic_rcp<HALF_EVEN>(x0[4 * j + 2], mn0, s0, r0), code_magic_rcp<HALF_EVEN>(x0[4 * j + 3], mn0, s0, r0));
-            const uint32_t b1 = pack4_magic(code_magic_rcp<HALF_EVEN>(x1[4 * j], mn1, s1, r1), code_magic_rcp<HALF_EVEN>(x1[4 * j + 1], mn1, s1, r1),
-                                            code_magic_rcp<HALF_EVEN>(x1[4 * j + 2], mn1, s1, r1), code_magic_rcp<HALF_EVEN>(x1[4 * j + 3], mn1, s1, r1));
-            *reinterpret_cast<uint16_t*>(dst + j * 64) = (uint16_t)(b0 | (b1 << 8));
+            float m0[4], m1[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float a, b;
+                P::widen(w[4 * j + e], a, b);
+                m0[e] = code_magic_rcp<HALF_EVEN>(a, mn0, s0, r0);
+                m1[e] = code_magic_rcp<HALF_EVEN>(b, mn1, s1, r1);
+            }
+            *reinterpret_cast<uint16_t*>(dst + j * 64) =
+                (uint16_t)(pack4_magic(m0[0], m0[1], m0[2], m0[3]) | (pack4_magic(m1[0], m1[1], m1[2], m1[3]) << 8));
         }
     } else {
         // a scale too large for a reciprocal (rare): plain divisions, the values
-        // read again so that the register arrays are never indexed dynamically
+        // read again so that the register array is never indexed dynamically
 #pragma unroll 1
         for (int j = 0; j < Q; ++j) {
             float m0[4], m1[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 float a, b;
-                Load2<TF>::run(src + (4 * j + e) * tok_stride, a, b);
+                P::widen(P::load(src + (4 * j + e) * tok_stride), a, b);
                 m0[e] = code_magic<HALF_EVEN>(a, mn0, s0, r0);
                 m1[e] = code_magic<HALF_EVEN>(b, mn1, s1, r1);
             }
@@ -365,73 +386,109 @@ flush_keys_direct_kernel(const TF* __restrict__ fresh, int64_t unit_stride, int6
     }
 }
 
+// The 32 channels of one (token, channel group) kept as loaded: four 128-bit
+// words for bf16, eight for fp32.
+template <typename T> struct Row32;
+template <> struct Row32<float> {
+    float4 v[8];
+    __device__ void load(const float* p) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = __ldg(reinterpret_cast<const float4*>(p) + k);
+    }
+    __device__ void minmax(float& mn, float& mx) const {
+        mn = 1e30f; mx = -1e30f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            mn = fminf(fminf(mn, v[k].x), fminf(v[k].y, fminf(v[k].z, v[k].w)));
+            mx = fmaxf(fmaxf(mx, v[k].x), fmaxf(v[k].y, fmaxf(v[k].z, v[k].w)));
+        }
+    }
+    // channels 4r .. 4r+3
+    __device__ void quad(int r, float (&x)[4]) const { x[0] = v[r].x; x[1] = v[r].y; x[2] = v[r].z; x[3] = v[r].w; }
+};
+template <> struct Row32<__nv_bfloat16> {
+    uint32_t w[16];
+    __device__ void load(const __nv_bfloat16* p) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint4 t = __ldg(reinterpret_cast<const uint4*>(p) + k);
+            w[4 * k] = t.x; w[4 * k + 1] = t.y; w[4 * k + 2] = t.z; w[4 * k + 3] = t.w;
+        }
+    }
+    __device__ void minmax(float& mn, float& mx) const {
+        using P = Pair<__nv_bfloat16>;
+        P::acc lo = P::first(w[0]), hi = P::first(w[0]);
+#pragma unroll
+        for (int k = 1; k < 16; ++k) { lo = P::lo(lo, w[k]); hi = P::hi(hi, w[k]); }
+        float a, b;
+        P::finish(lo, a, b); mn = fminf(fminf(a, b), 1e30f);
+        P::finish(hi, a, b); mx = fmaxf(fmaxf(a, b), -1e30f);
+    }
+    __device__ void quad(int r, float (&x)[4]) const {
+        Pair<__nv_bfloat16>::widen(w[2 * r], x[0], x[1]);
+        Pair<__nv_bfloat16>::widen(w[2 * r + 1], x[2], x[3]);
+    }
+};
+
 // Values for D = 128, G = 32, every token in the new tensor: a thread owns one
-// (token, channel group) = 32 consecutive channels (four or eight independent
-// 128-bit loads, no shuffles), thread 4*tl + gd of the CTA token tl of the CTA's
-// 64.  The two value blocks of the CTA are assembled in shared memory (planes
-// padded to 68 words so that the byte stores of a warp spread over the banks)
-// and leave with 128-bit stores.  `fresh` points at the launch's first token,
-// tok0 (a multiple of G) is its destination index.
+// (token, channel group) = 32 consecutive channels (independent 128-bit loads,
+// no shuffles), thread 4*tl + gd of the CTA token tl of the CTA's 32.  The value
+// block of the CTA is assembled in shared memory (planes padded to 68 words so
+// that the byte stores of a warp spread over the banks) and leaves with 128-bit
+// stores.  `fresh` points at the launch's first token, tok0 (a multiple of G)
+// is its destination index; n_tok is a multiple of G.
 template <typename TF, bool HALF_EVEN>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 flush_values_direct_kernel(const TF* __restrict__ fresh, int64_t unit_stride, int64_t tok_stride,
                            uint8_t* __restrict__ v_codes, float* __restrict__ v_scales,
-                           float* __restrict__ v_zeros, int64_t max_tokens, int64_t tok0, int64_t n_tok) {
-    constexpr int D = 128, G = 32, PLANE = 68;          // words per (block, gd) plane in shared memory
-    __shared__ __align__(16) uint32_t s_codes[2 * 4 * PLANE];
-    __shared__ __align__(16) float s_scale[2 * 128];
-    __shared__ __align__(16) float s_zero[2 * 128];
+                           float* __restrict__ v_zeros, int64_t max_tokens, int64_t tok0) {
+    constexpr int D = 128, G = 32, PLANE = 68;          // words per channel-group plane in shared memory
+    __shared__ __align__(16) uint32_t s_codes[4 * PLANE];
+    __shared__ __align__(16) float s_scale[128];
+    __shared__ __align__(16) float s_zero[128];
     const int u = blockIdx.y;
     const int tl = threadIdx.x >> 2, gd = threadIdx.x & 3;
-    const int64_t cta_tau0 = (int64_t)blockIdx.x * 64;
-    const int64_t tau = cta_tau0 + tl;
-    if (tau < n_tok) {
-        const TF* src = fresh + (int64_t)u * unit_stride + tau * tok_stride + gd * G;
-        float x[G];
+    const int64_t cta_tau0 = (int64_t)blockIdx.x * G;
+    const TF* src = fresh + (int64_t)u * unit_stride + (cta_tau0 + tl) * tok_stride + gd * G;
+    Row32<TF> row;
+    row.load(src);
+    float mn, mx;
+    row.minmax(mn, mx);
+    const float scale = group_scale(mn, mx);
+    const float rcp = group_rcp(scale);
+    // token tl = 16*kappa + 4*c + n: byte n of word gd*64 + kappa*32 + r*4 + c
+    uint8_t* sc = reinterpret_cast<uint8_t*>(s_codes + gd * PLANE + (tl >> 4) * 32 + ((tl >> 2) & 3)) + (tl & 3);
+    if (rcp != 0.0f) {
 #pragma unroll
-        for (int k = 0; k < G / 8; ++k) Load8<TF>::run(src + 8 * k, *reinterpret_cast<float(*)[8]>(&x[8 * k]));
-        float mn = 1e30f, mx = -1e30f;
-#pragma unroll
-        for (int i = 0; i < G; ++i) { mn = fminf(mn, x[i]); mx = fmaxf(mx, x[i]); }
-        const float scale = group_scale(mn, mx);
-        const float rcp = group_rcp(scale);
-        // token tl = 32*blk + 16*kappa + 4*c + n: byte n of word gd*64 + kappa*32 + r*4 + c
-        const int tt = tl & 31;
-        uint8_t* sc = reinterpret_cast<uint8_t*>(s_codes + ((tl >> 5) * 4 + gd) * PLANE + (tt >> 4) * 32 + ((tt >> 2) & 3)) + (tt & 3);
-        if (rcp != 0.0f) {
-#pragma unroll
-            for (int r = 0; r < G / 4; ++r)
-                sc[r * 16] = (uint8_t)pack4_magic(code_magic_rcp<HALF_EVEN>(x[4 * r], mn, scale, rcp), code_magic_rcp<HALF_EVEN>(x[4 * r + 1], mn, scale, rcp),
-                                                  code_magic_rcp<HALF_EVEN>(x[4 * r + 2], mn, scale, rcp), code_magic_rcp<HALF_EVEN>(x[4 * r + 3], mn, scale, rcp));
-        } else {
-            // a scale too large for a reciprocal (rare): plain divisions on re-read values
-#pragma unroll 1
-            for (int r = 0; r < G / 4; ++r) {
-                float m[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    m[e] = code_magic<HALF_EVEN>(load_as_float(src, sizeof(TF) == 2 ? KIVI_BF16 : KIVI_F32, 4 * r + e), mn, scale, rcp);
-                sc[r * 16] = (uint8_t)pack4_magic(m[0], m[1], m[2], m[3]);
-            }
+        for (int r = 0; r < G / 4; ++r) {
+            float x[4];
+            row.quad(r, x);
+            sc[r * 16] = (uint8_t)pack4_magic(code_magic_rcp<HALF_EVEN>(x[0], mn, scale, rcp), code_magic_rcp<HALF_EVEN>(x[1], mn, scale, rcp),
+                                              code_magic_rcp<HALF_EVEN>(x[2], mn, scale, rcp), code_magic_rcp<HALF_EVEN>(x[3], mn, scale, rcp));
         }
-        const int mi = (int)vmeta_index(tl, gd, D, G);
-        s_scale[mi] = scale; s_zero[mi] = mn;
+    } else {
+        // a scale too large for a reciprocal (rare): plain divisions on re-read values
+#pragma unroll 1
+        for (int r = 0; r < G / 4; ++r) {
+            float m[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                m[e] = code_magic<HALF_EVEN>(load_as_float(src, sizeof(TF) == 2 ? KIVI_BF16 : KIVI_F32, 4 * r + e), mn, scale, rcp);
+            sc[r * 16] = (uint8_t)pack4_magic(m[0], m[1], m[2], m[3]);
+        }
     }
+    const int mi = (int)vmeta_index(tl, gd, D, G);
+    s_scale[mi] = scale; s_zero[mi] = mn;
     __syncthreads();
-    const int64_t left = n_tok - cta_tau0;
-    const int n_here = left < 64 ? (int)left : 64;                       // multiple of 32
     const int64_t t_first = (int64_t)u * max_tokens + tok0 + cta_tau0;
-    uint4* gc = reinterpret_cast<uint4*>(v_codes + t_first * (D / 4));
-    float4* gs = reinterpret_cast<float4*>(v_scales + t_first * (D / G));
-    float4* gz = reinterpret_cast<float4*>(v_zeros + t_first * (D / G));
-    for (int i = threadIdx.x; i < n_here * 2; i += 256) {
-        // 16-byte piece i of the CTA's blocks: block i/64, plane (i%64)/16, piece i%16
-        gc[i] = *reinterpret_cast<const uint4*>(s_codes + ((i >> 6) * 4 + ((i >> 4) & 3)) * PLANE + (i & 15) * 4);
-    }
-    for (int i = threadIdx.x; i < n_here; i += 256) {
-        gs[i] = reinterpret_cast<const float4*>(s_scale)[i];
-        gz[i] = reinterpret_cast<const float4*>(s_zero)[i];
-    }
+    // 16-byte piece i of the block: plane i/16, piece i%16
+    if (threadIdx.x < 64)
+        reinterpret_cast<uint4*>(v_codes + t_first * (D / 4))[threadIdx.x] =
+            *reinterpret_cast<const uint4*>(s_codes + (threadIdx.x >> 4) * PLANE + (threadIdx.x & 15) * 4);
+    else if (threadIdx.x < 96)
+        reinterpret_cast<float4*>(v_scales + t_first * (D / G))[threadIdx.x - 64] = reinterpret_cast<const float4*>(s_scale)[threadIdx.x - 64];
+    else
+        reinterpret_cast<float4*>(v_zeros + t_first * (D / G))[threadIdx.x - 96] = reinterpret_cast<const float4*>(s_zero)[threadIdx.x - 96];
 }
 
 // Copies virtual tokens [tau_from, tau_to) of the new tensor into their ring
@@ -635,8 +692,13 @@ extern "C" int kivi_cache_update(const kivi_layer* L, int64_t quant_len, int res
 #define KIVI_DK(TF)                                                                                                  \
             do {                                                                                                     \
                 const TF* p = reinterpret_cast<const TF*>(new_k) + first * tok_stride_k;                             \
-                if (he) flush_keys_direct_kernel<TF, true><<<grid, 128, 0, st>>>(p, unit_stride_k, tok_stride_k, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0 + g_ring, n_direct); \
-                else flush_keys_direct_kernel<TF, false><<<grid, 128, 0, st>>>(p, unit_stride_k, tok_stride_k, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0 + g_ring, n_direct);   \
+                if (tok_stride_k == D) {                                                                             \
+                    if (he) flush_keys_direct_kernel<TF, true, true><<<grid, 128, 0, st>>>(p, unit_stride_k, tok_stride_k, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0 + g_ring, n_direct); \
+                    else flush_keys_direct_kernel<TF, false, true><<<grid, 128, 0, st>>>(p, unit_stride_k, tok_stride_k, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0 + g_ring, n_direct);   \
+                } else {                                                                                             \
+                    if (he) flush_keys_direct_kernel<TF, true, false><<<grid, 128, 0, st>>>(p, unit_stride_k, tok_stride_k, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0 + g_ring, n_direct); \
+                    else flush_keys_direct_kernel<TF, false, false><<<grid, 128, 0, st>>>(p, unit_stride_k, tok_stride_k, L->k_codes, L->k_scales, L->k_zeros, max_groups, group0 + g_ring, n_direct);   \
+                }                                                                                                    \
             } while (0)
             if (new_dtype == KIVI_F32) KIVI_DK(float); else KIVI_DK(__nv_bfloat16);
 #undef KIVI_DK
@@ -673,12 +735,12 @@ extern "C" int kivi_cache_update(const kivi_layer* L, int64_t quant_len, int res
         }
         if (t_ring < n_tok) {
             const int64_t n_direct = n_tok - t_ring;
-            dim3 gridv((unsigned)((n_direct + 63) / 64), (unsigned)L->num_units);
+            dim3 gridv((unsigned)(n_direct / G), (unsigned)L->num_units);
 #define KIVI_DV(TF)                                                                                                  \
             do {                                                                                                     \
                 const TF* p = reinterpret_cast<const TF*>(new_v) + (t_ring - res_len) * tok_stride_v;                \
-                if (he) flush_values_direct_kernel<TF, true><<<gridv, 256, 0, st>>>(p, unit_stride_v, tok_stride_v, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len + t_ring, n_direct); \
-                else flush_values_direct_kernel<TF, false><<<gridv, 256, 0, st>>>(p, unit_stride_v, tok_stride_v, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len + t_ring, n_direct);   \
+                if (he) flush_values_direct_kernel<TF, true><<<gridv, 128, 0, st>>>(p, unit_stride_v, tok_stride_v, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len + t_ring); \
+                else flush_values_direct_kernel<TF, false><<<gridv, 128, 0, st>>>(p, unit_stride_v, tok_stride_v, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len + t_ring);   \
             } while (0)
             if (new_dtype == KIVI_F32) KIVI_DV(float); else KIVI_DV(__nv_bfloat16);
 #undef KIVI_DV
