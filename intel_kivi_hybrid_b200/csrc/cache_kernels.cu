@@ -13,6 +13,13 @@
 // straight out of the model's [units, S, D] tensor, the rest appended).
 #include "kivi_common.cuh"
 
+#ifndef KIVI_STAGE_F32
+#define KIVI_STAGE_F32 true
+#endif
+#ifndef KIVI_STAGE_BF16
+#define KIVI_STAGE_BF16 false
+#endif
+
 namespace kivi {
 namespace {
 
@@ -395,6 +402,10 @@ template <> struct Row32<float> {
 #pragma unroll
         for (int k = 0; k < 8; ++k) v[k] = __ldg(reinterpret_cast<const float4*>(p) + k);
     }
+    __device__ void load_staged(const uint8_t* p) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = reinterpret_cast<const float4*>(p)[k];
+    }
     __device__ void minmax(float& mn, float& mx) const {
         mn = 1e30f; mx = -1e30f;
 #pragma unroll
@@ -415,6 +426,13 @@ template <> struct Row32<__nv_bfloat16> {
             w[4 * k] = t.x; w[4 * k + 1] = t.y; w[4 * k + 2] = t.z; w[4 * k + 3] = t.w;
         }
     }
+    __device__ void load_staged(const uint8_t* p) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint4 t = reinterpret_cast<const uint4*>(p)[k];
+            w[4 * k] = t.x; w[4 * k + 1] = t.y; w[4 * k + 2] = t.z; w[4 * k + 3] = t.w;
+        }
+    }
     __device__ void minmax(float& mn, float& mx) const {
         using P = Pair<__nv_bfloat16>;
         P::acc lo = P::first(w[0]), hi = P::first(w[0]);
@@ -431,27 +449,51 @@ template <> struct Row32<__nv_bfloat16> {
 };
 
 // Values for D = 128, G = 32, every token in the new tensor: a thread owns one
-// (token, channel group) = 32 consecutive channels (independent 128-bit loads,
-// no shuffles), thread 4*tl + gd of the CTA token tl of the CTA's 32.  The value
+// (token, channel group) = 32 consecutive channels (no shuffles), thread
+// 4*tl + gd of the CTA token tl of the CTA's 32.  With STAGED a warp first
+// copies the 8 token rows of its threads to shared memory with loads that cover
+// whole rows (a thread's own 128-bit loads would each touch 32 different lines),
+// and every thread then reads its 32 channels from there; rows are padded by 16
+// bytes so that both directions are free of bank conflicts for fp32.  The value
 // block of the CTA is assembled in shared memory (planes padded to 68 words so
 // that the byte stores of a warp spread over the banks) and leaves with 128-bit
 // stores.  `fresh` points at the launch's first token, tok0 (a multiple of G)
-// is its destination index; n_tok is a multiple of G.
-template <typename TF, bool HALF_EVEN>
+// is its destination index; the grid covers whole groups.
+template <typename TF, bool HALF_EVEN, bool STAGED>
 __global__ void __launch_bounds__(128)
 flush_values_direct_kernel(const TF* __restrict__ fresh, int64_t unit_stride, int64_t tok_stride,
                            uint8_t* __restrict__ v_codes, float* __restrict__ v_scales,
                            float* __restrict__ v_zeros, int64_t max_tokens, int64_t tok0) {
     constexpr int D = 128, G = 32, PLANE = 68;          // words per channel-group plane in shared memory
+    constexpr int ROW_BYTES = G * (int)sizeof(TF), ROW_PITCH = ROW_BYTES + 16;
     __shared__ __align__(16) uint32_t s_codes[4 * PLANE];
     __shared__ __align__(16) float s_scale[128];
     __shared__ __align__(16) float s_zero[128];
+    __shared__ __align__(16) uint8_t s_rows[STAGED ? 4 * 32 * ROW_PITCH : 16];
     const int u = blockIdx.y;
     const int tl = threadIdx.x >> 2, gd = threadIdx.x & 3;
     const int64_t cta_tau0 = (int64_t)blockIdx.x * G;
     const TF* src = fresh + (int64_t)u * unit_stride + (cta_tau0 + tl) * tok_stride + gd * G;
     Row32<TF> row;
-    row.load(src);
+    if (STAGED) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        uint8_t* mine = s_rows + warp * 32 * ROW_PITCH;
+        constexpr int LANES_PER_TOKEN = D * (int)sizeof(TF) / 16;          // 32 (fp32) or 16 (bf16)
+        constexpr int TOKENS_PER_LOAD = 32 / LANES_PER_TOKEN;
+        const int piece = lane % LANES_PER_TOKEN;                          // 16-byte piece of the token row
+        const uint8_t* tok = reinterpret_cast<const uint8_t*>(fresh + (int64_t)u * unit_stride + (cta_tau0 + 8 * warp + lane / LANES_PER_TOKEN) * tok_stride) + piece * 16;
+#pragma unroll
+        for (int k = 0; k < 8 / TOKENS_PER_LOAD; ++k) {
+            const uint4 t = __ldg(reinterpret_cast<const uint4*>(tok + (int64_t)k * TOKENS_PER_LOAD * tok_stride * (int)sizeof(TF)));
+            const int token = k * TOKENS_PER_LOAD + lane / LANES_PER_TOKEN;          // of the warp's 8
+            const int r = 4 * token + piece * 16 / ROW_BYTES;                        // row = (token, channel group)
+            *reinterpret_cast<uint4*>(mine + r * ROW_PITCH + (piece * 16) % ROW_BYTES) = t;
+        }
+        __syncwarp();
+        row.load_staged(mine + lane * ROW_PITCH);
+    } else {
+        row.load(src);
+    }
     float mn, mx;
     row.minmax(mn, mx);
     const float scale = group_scale(mn, mx);
@@ -736,14 +778,17 @@ extern "C" int kivi_cache_update(const kivi_layer* L, int64_t quant_len, int res
         if (t_ring < n_tok) {
             const int64_t n_direct = n_tok - t_ring;
             dim3 gridv((unsigned)(n_direct / G), (unsigned)L->num_units);
+// fp32 rows are staged through shared memory, bf16 rows are read directly
+#define KIVI_STAGE(TF) (sizeof(TF) == 4 ? KIVI_STAGE_F32 : KIVI_STAGE_BF16)
 #define KIVI_DV(TF)                                                                                                  \
             do {                                                                                                     \
                 const TF* p = reinterpret_cast<const TF*>(new_v) + (t_ring - res_len) * tok_stride_v;                \
-                if (he) flush_values_direct_kernel<TF, true><<<gridv, 128, 0, st>>>(p, unit_stride_v, tok_stride_v, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len + t_ring); \
-                else flush_values_direct_kernel<TF, false><<<gridv, 128, 0, st>>>(p, unit_stride_v, tok_stride_v, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len + t_ring);   \
+                if (he) flush_values_direct_kernel<TF, true, KIVI_STAGE(TF)><<<gridv, 128, 0, st>>>(p, unit_stride_v, tok_stride_v, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len + t_ring); \
+                else flush_values_direct_kernel<TF, false, KIVI_STAGE(TF)><<<gridv, 128, 0, st>>>(p, unit_stride_v, tok_stride_v, L->v_codes, L->v_scales, L->v_zeros, L->max_tokens, quant_len + t_ring);   \
             } while (0)
             if (new_dtype == KIVI_F32) KIVI_DV(float); else KIVI_DV(__nv_bfloat16);
 #undef KIVI_DV
+#undef KIVI_STAGE
             KIVI_LAUNCH_OK();
             launches += 1;
         }
