@@ -16,6 +16,8 @@
 // alignments the fast kernel does not cover.
 #include "kivi_common.cuh"
 
+#include <type_traits>
+
 namespace kivi {
 namespace {
 
@@ -104,37 +106,44 @@ group_quant_kernel(const T* __restrict__ in, uint8_t* __restrict__ packed,
         const float scale = group_scale(mn, mx);
         const float rcp = group_rcp(scale);
         const int64_t g = tile_g0 + lg[it];
-        if (MODE == 0) {
-            uint32_t bytes[(BPL + 3) / 4] = {};
+        // one branch per group, not per element: groups whose scale has no
+        // reciprocal (>= 1e30) take the plain-division twin of the same code
+        auto emit = [&](auto has_rcp) {
+            constexpr bool RCP = decltype(has_rcp)::value;
+            auto magic = [&](float x) {
+                if constexpr (RCP) return code_magic_rcp<HALF_EVEN>(x, mn, scale, rcp);
+                else return code_magic<HALF_EVEN>(x, mn, scale, rcp);
+            };
+            if (MODE == 0) {
+                uint32_t bytes[(BPL + 3) / 4] = {};
 #pragma unroll
-            for (int b = 0; b < BPL; ++b) {
-                float q0 = code_magic<HALF_EVEN>(v[it][4 * b + 0], mn, scale, rcp);
-                float q1 = code_magic<HALF_EVEN>(v[it][4 * b + 1], mn, scale, rcp);
-                float q2 = code_magic<HALF_EVEN>(v[it][4 * b + 2], mn, scale, rcp);
-                float q3 = code_magic<HALF_EVEN>(v[it][4 * b + 3], mn, scale, rcp);
-                uint32_t byte = pack4_magic(q0, q1, q2, q3);
-                bytes[b / 4] |= byte << (8 * (b % 4));
-            }
-            uint8_t* dst = s_codes + lg[it] * (G / 4) + sub * BPL;
-            if (BPL == 1) *dst = (uint8_t)bytes[0];
-            else if (BPL == 2) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)bytes[0];
-            else {
+                for (int b = 0; b < BPL; ++b) {
+                    const uint32_t byte = pack4_magic(magic(v[it][4 * b + 0]), magic(v[it][4 * b + 1]),
+                                                      magic(v[it][4 * b + 2]), magic(v[it][4 * b + 3]));
+                    bytes[b / 4] |= byte << (8 * (b % 4));
+                }
+                uint8_t* dst = s_codes + lg[it] * (G / 4) + sub * BPL;
+                if (BPL == 1) *dst = (uint8_t)bytes[0];
+                else if (BPL == 2) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)bytes[0];
+                else {
 #pragma unroll
-                for (int w = 0; w < BPL / 4; ++w) reinterpret_cast<uint32_t*>(dst)[w] = bytes[w];
-            }
-            if (sub == 0) { s_scale[lg[it]] = scale; s_zero[lg[it]] = mn; }
-        } else if (g < num_groups) {
-            float* o = rt_out + g * G + sub * EPL;
+                    for (int w = 0; w < BPL / 4; ++w) reinterpret_cast<uint32_t*>(dst)[w] = bytes[w];
+                }
+                if (sub == 0) { s_scale[lg[it]] = scale; s_zero[lg[it]] = mn; }
+            } else if (g < num_groups) {
+                float* o = rt_out + g * G + sub * EPL;
 #pragma unroll
-            for (int k = 0; k < EPL / 4; ++k) {
-                float4 r;
-                r.x = dequant(code_of<HALF_EVEN>(v[it][4 * k + 0], mn, scale, rcp), scale, mn);
-                r.y = dequant(code_of<HALF_EVEN>(v[it][4 * k + 1], mn, scale, rcp), scale, mn);
-                r.z = dequant(code_of<HALF_EVEN>(v[it][4 * k + 2], mn, scale, rcp), scale, mn);
-                r.w = dequant(code_of<HALF_EVEN>(v[it][4 * k + 3], mn, scale, rcp), scale, mn);
-                reinterpret_cast<float4*>(o)[k] = r;
+                for (int k = 0; k < EPL / 4; ++k) {
+                    float4 r;
+                    r.x = dequant(__fsub_rn(magic(v[it][4 * k + 0]), 8388608.0f), scale, mn);
+                    r.y = dequant(__fsub_rn(magic(v[it][4 * k + 1]), 8388608.0f), scale, mn);
+                    r.z = dequant(__fsub_rn(magic(v[it][4 * k + 2]), 8388608.0f), scale, mn);
+                    r.w = dequant(__fsub_rn(magic(v[it][4 * k + 3]), 8388608.0f), scale, mn);
+                    reinterpret_cast<float4*>(o)[k] = r;
+                }
             }
-        }
+        };
+        if (rcp != 0.0f) emit(std::true_type{}); else emit(std::false_type{});
     }
     if (MODE != 0) return;
     __syncthreads();
@@ -203,19 +212,21 @@ group_quant_generic_kernel(const void* __restrict__ in, int in_dtype, uint8_t* _
 __global__ void __launch_bounds__(kThreads)
 group_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ scales,
                      const float* __restrict__ zeros, float* __restrict__ out,
-                     int64_t total_bytes, int bytes_per_group, bool vec_ok) {
+                     int64_t total_bytes, int bytes_per_group, int group_shift, bool vec_ok) {
     for (int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x; b < total_bytes;
          b += (int64_t)gridDim.x * kThreads) {
-        const int64_t g = b / bytes_per_group;
+        // group of this byte: a shift for power-of-two groups (no 64-bit division per element)
+        const int64_t g = group_shift >= 0 ? (b >> group_shift) : b / bytes_per_group;
         const float s = __ldg(scales + g), z = __ldg(zeros + g);
         const uint32_t p = __ldg(packed + b);
+        // code c as a float: the two bits dropped into the mantissa of 2^23, minus 2^23
         float4 r;
-        r.x = dequant((float)(p & 3u), s, z);
-        r.y = dequant((float)((p >> 2) & 3u), s, z);
-        r.z = dequant((float)((p >> 4) & 3u), s, z);
-        r.w = dequant((float)((p >> 6) & 3u), s, z);
+        r.x = dequant(__fsub_rn(__uint_as_float(0x4B000000u | (p & 3u)), 8388608.0f), s, z);
+        r.y = dequant(__fsub_rn(__uint_as_float(0x4B000000u | ((p >> 2) & 3u)), 8388608.0f), s, z);
+        r.z = dequant(__fsub_rn(__uint_as_float(0x4B000000u | ((p >> 4) & 3u)), 8388608.0f), s, z);
+        r.w = dequant(__fsub_rn(__uint_as_float(0x4B000000u | (p >> 6)), 8388608.0f), s, z);
         if (vec_ok) {
-            reinterpret_cast<float4*>(out)[b] = r;
+            __stcs(reinterpret_cast<float4*>(out) + b, r);
         } else {
             out[4 * b] = r.x; out[4 * b + 1] = r.y; out[4 * b + 2] = r.z; out[4 * b + 3] = r.w;
         }
@@ -277,8 +288,8 @@ int run_group_quant(const void* in, int in_dtype, uint8_t* packed, float* scales
             switch (G) {
                 case 16: return launch_fast<__nv_bfloat16, 2, 1>(in, packed, scales, zeros, rt, num_groups, rounding, mode, st);
                 case 32: return launch_fast<__nv_bfloat16, 4, 1>(in, packed, scales, zeros, rt, num_groups, rounding, mode, st);
-                case 64: return launch_fast<__nv_bfloat16, 4, 2>(in, packed, scales, zeros, rt, num_groups, rounding, mode, st);
-                case 128: return launch_fast<__nv_bfloat16, 8, 2>(in, packed, scales, zeros, rt, num_groups, rounding, mode, st);
+                case 64: return launch_fast<__nv_bfloat16, 8, 1>(in, packed, scales, zeros, rt, num_groups, rounding, mode, st);
+                case 128: return launch_fast<__nv_bfloat16, 16, 1>(in, packed, scales, zeros, rt, num_groups, rounding, mode, st);
                 default: break;
             }
         }
@@ -311,7 +322,9 @@ int run_group_dequant(const uint8_t* packed, const float* scales, const float* z
     int64_t blocks = (total_bytes + kThreads - 1) / kThreads;
     const int64_t cap = (int64_t)num_sms() * 64;
     if (blocks > cap) blocks = cap;
-    group_dequant_kernel<<<(unsigned)blocks, kThreads, 0, st>>>(packed, scales, zeros, out, total_bytes, G / 4, aligned16(out));
+    int shift = -1;
+    for (int k = 0; k < 31; ++k) if ((G / 4) == (1 << k)) shift = k;
+    group_dequant_kernel<<<(unsigned)blocks, kThreads, 0, st>>>(packed, scales, zeros, out, total_bytes, G / 4, shift, aligned16(out));
     KIVI_LAUNCH_OK();
     note_launches(1);
     return KIVI_OK;
