@@ -213,11 +213,24 @@ def run_ours(args, wl):
     q = torch.randn(U, n_rep, D, device=dev, generator=torch.Generator(device=dev).manual_seed(7)).to(dtype)
     out = torch.empty_like(q)
     gathered = torch.empty(world * U, n_rep, D, device=dev, dtype=dtype) if world > 1 else None
+    # the exchange of a step: an NCCL all-gather after the kernels, or the
+    # attention's last kernel storing its rows into every rank's buffer itself
+    pg = None
+    if world > 1 and args.gather == "peer":
+        from intel_kivi_hybrid_b200.parallel import PeerGather
+        pg = PeerGather(world * U, n_rep, D, dtype, rank, world)
 
-    def step(i):
-        stores[i % n_buf].attention(q, out=out, n_rep=n_rep, path=path, num_splits=args.splits)
+    def attend(store):
+        if pg is not None:
+            store.attention_gather(q, pg.descriptor(), dtype, n_rep, path=path, num_splits=args.splits)
+            return pg.gathered()[rank * U:(rank + 1) * U]
+        store.attention(q, out=out, n_rep=n_rep, path=path, num_splits=args.splits)
         if world > 1:
             dist.all_gather_into_tensor(gathered, out)
+        return out
+
+    def step(i):
+        attend(stores[i % n_buf])
 
     def barrier():
         if world > 1:
@@ -296,10 +309,7 @@ def run_ours(args, wl):
         q.copy_(h_q, non_blocking=True)
         d_kv.copy_(h_kv, non_blocking=True)
         e2e_store.update(d_kv[0], d_kv[1])
-        e2e_store.attention(q, out=out, n_rep=n_rep, path=path, num_splits=args.splits)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
-        h_out.copy_(out, non_blocking=True)
+        h_out.copy_(attend(e2e_store), non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for _ in range(3):
@@ -334,6 +344,7 @@ def run_ours(args, wl):
             torch.cuda.synchronize()
     barrier()
     windows.append((w0, time.time()))
+    fault = cabi.device_fault()            # non-zero: a bounded wait inside a kernel ran out
     if sampler is not None:
         clocks = sampler.stop(windows)
         clocks["sampled"] = "timed region plus ~1.2 s of the same step loop right after it"
@@ -355,7 +366,9 @@ def run_ours(args, wl):
                            "n_quant": n_quant, "n_res": n_res, "path": args.path, "layer_buffers_rotated": n_buf,
                            "cuda_graph": graph is not None,
                            "l2": "inputs larger than L2 (layer buffers rotated)",
-                           "parallelism": f"(batch,kv_head) units x{world}, all-gather of outputs"},
+                           "parallelism": f"(batch,kv_head) units x{world}, all-gather of outputs"
+                                          + ("" if world == 1 else " by NCCL" if pg is None else
+                                             " inside the merge kernel (peer stores over NVLink)")},
                 "decode_tokens_per_s": world * B / (LAYERS * ms_step * 1e-3),
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                              "peak_source": which, "traffic": by * 1.020,
@@ -367,8 +380,11 @@ def run_ours(args, wl):
                         "h2d_bytes_per_step": h_q.numel() * 2 + h_kv.numel() * 2, "d2h_bytes_per_step": h_out.numel() * 2,
                         "note": "host q + new K/V token -> cache update (flush every G steps) -> attention -> host out"},
                 "gpu_launches": args.steps * launches_per_step,
+                "device_fault": fault,
                 "clocks": clocks}
         print(json.dumps(line))
+    if pg is not None:
+        pg.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -421,6 +437,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--gather", default="nccl", choices=["nccl", "peer"],
+                    help="N>1: how the attention outputs are all-gathered")
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["cfg4"])
     ap.add_argument("--path", default="auto", choices=["auto", "fp32", "mma"])
     ap.add_argument("--splits", type=int, default=0)

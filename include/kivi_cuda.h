@@ -230,9 +230,60 @@ int kivi_decode_attention_noalloc(const kivi_layer* layer, int64_t quant_len, in
                                   int res_len, const void* q, int q_dtype, void* out, int out_dtype,
                                   int n_rep, float sm_scale, int num_splits, int path, void* stream);
 
-/* Reads (and synchronises with) the device fault word: non-zero once any wait
- * inside a kernel of this library ran out (a bulk copy that never completed).
- * Such a kernel returns normally and reports the affected split as empty. */
+/* ------------------------------------------------------------------------
+ * Decode attention whose output goes straight into every GPU's gathered buffer.
+ *
+ * No counterpart in the reference (it is single-device).  With the (batch,
+ * kv_head) units sharded over the GPUs of one node, the one exchange per
+ * layer-step is an all-gather of the attention outputs.  Instead of a separate
+ * collective, the kernel that folds the split partials writes each output row
+ * into the gathered buffer of every rank through peer-mapped pointers (plain
+ * stores over NVLink; no multicast, no TMA), publishes "rank r finished epoch e"
+ * in every rank's flag array and, if asked, waits until all ranks have
+ * published the same epoch -- so when the call's last kernel completes, this
+ * rank's gathered buffer is complete.
+ *
+ * Buffers: kivi_peer_alloc makes a zeroed device allocation and its 64-byte
+ * inter-process handle; every other rank maps it with kivi_peer_open (same
+ * node, peer access over NVLink) and unmaps it with kivi_peer_close before the
+ * owner calls kivi_peer_free.  Exchange the handles with any host-side channel.
+ *
+ * kivi_peer_gather: out_ptrs[r] = rank r's gathered buffer
+ * [total_units][n_rep][D] of out_dtype as addressable from this GPU (own
+ * allocation for r == rank), flag_ptrs[r] = rank r's uint32[world] flag array
+ * (zero before the first call), unit_offset = index of this rank's first unit
+ * in the gathered buffer, epoch = 1, 2, 3, ... identical on all ranks per call.
+ * wait != 0: bounded wait (about a second) for all ranks; if it runs out the
+ * kernel returns and bit 1 of the device fault word is set.
+ * Re-use: a rank may run one call ahead of its peers, so alternate between two
+ * gathered buffers (e.g. by epoch parity) when the consumer of call e may still
+ * be reading while call e+1 of a faster rank writes.
+ * ---------------------------------------------------------------------- */
+#define KIVI_PEER_MAX_WORLD 8
+typedef struct kivi_peer_gather {
+    int rank, world;
+    void* out_ptrs[KIVI_PEER_MAX_WORLD];
+    uint32_t* flag_ptrs[KIVI_PEER_MAX_WORLD];
+    int64_t unit_offset;
+    uint32_t epoch;
+    int wait;
+} kivi_peer_gather;
+
+int kivi_peer_alloc(size_t bytes, void** ptr_out, unsigned char handle_out[64]);
+int kivi_peer_open(const unsigned char handle[64], void** ptr_out);
+int kivi_peer_close(void* ptr);
+int kivi_peer_free(void* ptr);
+
+int kivi_decode_attention_gather(const kivi_layer* layer, int64_t quant_len, int res_start,
+                                 int res_len, const void* q, int q_dtype,
+                                 const kivi_peer_gather* gather, int out_dtype,
+                                 int n_rep, float sm_scale, void* workspace, size_t workspace_bytes,
+                                 int num_splits, int path, void* stream);
+
+/* Reads (and synchronises with) the device fault word: bit 0 is set once a wait
+ * for a bulk copy inside a kernel of this library ran out, bit 1 once a wait for
+ * peer ranks in kivi_decode_attention_gather ran out.  Such a kernel returns
+ * normally (bit 0: the affected split counts as empty). */
 int kivi_device_fault(int* word_out);
 
 /* number of kernels the last successful call on this thread launched */

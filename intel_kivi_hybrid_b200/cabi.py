@@ -29,6 +29,16 @@ class Layer(_c.Structure):
                 ("v_codes", _vp), ("v_scales", _vp), ("v_zeros", _vp), ("k_res", _vp), ("v_res", _vp)]
 
 
+PEER_MAX_WORLD = 8
+
+
+class PeerGatherDesc(_c.Structure):
+    """struct kivi_peer_gather of include/kivi_cuda.h."""
+    _fields_ = [("rank", _c.c_int32), ("world", _c.c_int32), ("out_ptrs", _vp * PEER_MAX_WORLD),
+                ("flag_ptrs", _vp * PEER_MAX_WORLD), ("unit_offset", _c.c_int64), ("epoch", _c.c_uint32),
+                ("wait", _c.c_int32)]
+
+
 SIGNATURES = {
     "kivi_last_error": (_c.c_char_p, []),
     "kivi_version": (_int, []),
@@ -51,6 +61,12 @@ SIGNATURES = {
                                              _int, _int, _vp]),
     "kivi_decode_attention": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _int, _vp, _int, _int, _f,
                                      _vp, _c.c_size_t, _int, _int, _vp]),
+    "kivi_decode_attention_gather": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _int, _c.POINTER(PeerGatherDesc),
+                                            _int, _int, _f, _vp, _c.c_size_t, _int, _int, _vp]),
+    "kivi_peer_alloc": (_int, [_c.c_size_t, _c.POINTER(_vp), _c.c_char_p]),
+    "kivi_peer_open": (_int, [_c.c_char_p, _c.POINTER(_vp)]),
+    "kivi_peer_close": (_int, [_vp]),
+    "kivi_peer_free": (_int, [_vp]),
 }
 
 
@@ -224,6 +240,16 @@ class LayerStore:
                                          ws.data_ptr(), ws.numel(), num_splits, path, _stream()))
         return out
 
+    def attention_gather(self, q, desc: "PeerGatherDesc", out_dtype, n_rep, sm_scale=0.0, num_splits=0, path=ATTN_AUTO):
+        """kivi_decode_attention_gather: the output rows of this store's units go
+        straight into every rank's gathered buffer (see parallel.PeerGather)."""
+        _dev(q)
+        ws = self.workspace(n_rep, num_splits)
+        odt = F32 if out_dtype == torch.float32 else BF16
+        _check(lib.kivi_decode_attention_gather(_c.byref(self.c), self.quant_len, self.res_start, self.res_len,
+                                                q.data_ptr(), _dt(q), _c.byref(desc), odt, n_rep, float(sm_scale),
+                                                ws.data_ptr(), ws.numel(), num_splits, path, _stream()))
+
     def attention_noalloc(self, q, out, n_rep, sm_scale=0.0, num_splits=0, path=ATTN_AUTO):
         """kivi_decode_attention_noalloc: same result as attention(), with the
         split partials in the library's built-in scratch array instead of a
@@ -234,6 +260,28 @@ class LayerStore:
                                                  q.data_ptr(), _dt(q), out.data_ptr(), _dt(out), n_rep,
                                                  float(sm_scale), num_splits, path, _stream()))
         return out
+
+
+def peer_alloc(nbytes: int):
+    """(device pointer, 64-byte handle) of a zeroed allocation other processes of
+    the node can map with peer_open()."""
+    ptr, handle = _vp(), _c.create_string_buffer(64)
+    _check(lib.kivi_peer_alloc(nbytes, _c.byref(ptr), handle))
+    return ptr.value, handle.raw
+
+
+def peer_open(handle: bytes) -> int:
+    ptr = _vp()
+    _check(lib.kivi_peer_open(_c.create_string_buffer(handle, 64), _c.byref(ptr)))
+    return ptr.value
+
+
+def peer_close(ptr: int):
+    _check(lib.kivi_peer_close(ptr))
+
+
+def peer_free(ptr: int):
+    _check(lib.kivi_peer_free(ptr))
 
 
 def load_state(store: "LayerStore", k_all, v_all, n_quant, rounding=ROUND_HALF_AWAY):

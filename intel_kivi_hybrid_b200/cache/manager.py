@@ -15,7 +15,10 @@ packed store directly.  ``get_full_cache`` survives as the compatibility path
 for third-party model code that wants dense past_key_values.
 
 With ``shard=(rank, world)`` a process keeps only its contiguous slice of the
-(batch, kv_head) units; ``decode_attention`` then all-gathers the outputs.
+(batch, kv_head) units; ``decode_attention`` then all-gathers the outputs:
+``gather="nccl"`` with a collective after the kernel, ``gather="peer"`` inside
+the kernel (its last stage stores every row into all ranks' buffers over
+NVLink, ``parallel.PeerGather``).
 """
 from typing import List, Optional, Tuple
 
@@ -23,7 +26,7 @@ import torch
 
 from .. import cabi
 from ..config.model_config import detect_model_config
-from ..parallel import all_gather_units, unit_partition
+from ..parallel import PeerGather, all_gather_units, unit_partition
 
 __all__ = ["KiviCache"]
 
@@ -57,7 +60,8 @@ class KiviCache:
     def __init__(self, num_layers: int, head_dim: int, num_kv_heads: Optional[int] = None,
                  device: str = "cuda", group_size: int = 32, residual_length: int = 128,
                  max_tokens: int = 4096, rounding: str = "half_away",
-                 shard: Optional[Tuple[int, int]] = None):
+                 shard: Optional[Tuple[int, int]] = None, gather: str = "nccl"):
+        assert gather in ("nccl", "peer")
         assert head_dim % group_size == 0, \
             f"head_dim ({head_dim}) must be divisible by group_size ({group_size})"
         assert group_size >= 4 and group_size % 4 == 0, \
@@ -76,6 +80,8 @@ class KiviCache:
         self.batch_size: Optional[int] = None
         self.rounding = cabi.ROUND_HALF_AWAY if rounding == "half_away" else cabi.ROUND_HALF_EVEN
         self.shard = shard
+        self.gather = gather
+        self._peer: dict = {}                              # (n_units, n_rep, dtype) -> PeerGather
         self._capacity = max(max_tokens, group_size)
         self._stores: List[Optional[cabi.LayerStore]] = [None] * num_layers
         self._flush_count: List[int] = [0] * num_layers
@@ -215,6 +221,15 @@ class KiviCache:
         n_rep = Hq // self.num_kv_heads
         u0, u1 = self._units
         q_units = q.reshape(B * self.num_kv_heads, n_rep, D)[u0:u1].contiguous()
+        if self.shard and self.shard[1] > 1 and self.gather == "peer":
+            # collective on first use (buffers are exchanged once); the result is a
+            # view of this rank's gathered buffer, overwritten two calls later
+            key = (B * self.num_kv_heads, n_rep, out_dtype or q.dtype)
+            if key not in self._peer:
+                self._peer[key] = PeerGather(key[0], n_rep, D, key[2], self.shard[0], self.shard[1])
+            pg = self._peer[key]
+            st.attention_gather(q_units, pg.descriptor(), pg.dtype, n_rep, sm_scale=sm_scale, num_splits=num_splits)
+            return pg.gathered().reshape(B, Hq, D)
         out = st.attention(q_units, n_rep=n_rep, out_dtype=out_dtype, num_splits=num_splits, sm_scale=sm_scale)
         if self.shard and self.shard[1] > 1:
             out = all_gather_units(out, B * self.num_kv_heads, self.shard[0], self.shard[1])
@@ -240,6 +255,12 @@ class KiviCache:
         self._cache_view = _build_cache(layers)
         self._cache_view_valid = True
         return self._cache_view
+
+    def close(self):
+        """Collective: unmap and free the peer-gather buffers (gather="peer")."""
+        for pg in self._peer.values():
+            pg.close()
+        self._peer = {}
 
     def reset(self):
         """Clear all cached data so the same object can serve a new sequence

@@ -239,16 +239,17 @@ attn_fp32_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
 
 }  // namespace
 
+namespace {
+
 // out[u][h][:] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
 // grid = (units, n_rep), 128 threads; partials laid out [(u*n_splits + s)*n_rep + h].
 // Thread s loads (m_s, l_s); the maximum and the denominator are block
 // reductions, so no thread walks the splits alone; the channel loop keeps four
-// independent loads in flight.
-__global__ void __launch_bounds__(128)
-merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                    void* __restrict__ out, int out_dtype, int n_splits, int D) {
-    extern __shared__ float w_s[];                   // [n_splits] weights
-    __shared__ float red_s[8];
+// independent loads in flight.  `sink(index, value)` receives element
+// index = (u*n_rep + h)*D + d of the output.
+template <typename Sink>
+__device__ __forceinline__ void merge_body(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                           int n_splits, int D, float* w_s, float* red_s, const Sink& sink) {
     const int u = blockIdx.x, h = blockIdx.y, nrep = gridDim.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int64_t row0 = (int64_t)u * n_splits * nrep + h;   // + s*nrep
@@ -292,8 +293,109 @@ merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ 
             a2 = fmaf(v2, w_s[s + 2], a2); a3 = fmaf(v3, w_s[s + 3], a3);
         }
         for (; s < n_splits; ++s) a0 = fmaf(part_o[(row0 + (int64_t)s * nrep) * D + d], w_s[s], a0);
-        store_from_float(out, out_dtype, ((int64_t)u * nrep + h) * D + d, ((a0 + a1) + (a2 + a3)) * inv);
+        sink(((int64_t)u * nrep + h) * D + d, ((a0 + a1) + (a2 + a3)) * inv);
     }
+}
+
+struct LocalSink {
+    void* out;
+    int out_dtype;
+    __device__ void operator()(int64_t i, float v) const { store_from_float(out, out_dtype, i, v); }
+};
+
+__global__ void __launch_bounds__(128)
+merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                    void* __restrict__ out, int out_dtype, int n_splits, int D) {
+    extern __shared__ float w_s[];                   // [n_splits] weights
+    __shared__ float red_s[8];
+    merge_body(part_o, part_ml, n_splits, D, w_s, red_s, LocalSink{out, out_dtype});
+}
+
+// ---- merge + all-gather over peer memory -------------------------------------------
+// The same fold, but every output row is stored into the gathered buffer of
+// every rank (plain stores through peer-mapped pointers).  When the last CTA of
+// the grid has finished, it publishes this rank's epoch in every rank's flag
+// array and, if asked, waits (bounded) until all ranks have published it.
+__device__ unsigned g_gather_done = 0;      // CTAs of the running launch that have stored their row
+__device__ int g_gather_fault = 0;
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+struct PeerSink {
+    kivi_peer_gather g;
+    int out_dtype;
+    int64_t base;              // element offset of this rank's first row in a gathered buffer
+    __device__ void operator()(int64_t i, float v) const {
+#pragma unroll
+        for (int r = 0; r < KIVI_PEER_MAX_WORLD; ++r)
+            if (r < g.world) store_from_float(g.out_ptrs[r], out_dtype, base + i, v);
+    }
+};
+
+constexpr uint32_t kPeerSpinLimit = 5u << 20;      // x 200 ns sleeps: about a second
+
+__global__ void __launch_bounds__(128)
+merge_gather_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                    kivi_peer_gather g, int out_dtype, int n_splits, int D) {
+    extern __shared__ float w_s[];
+    __shared__ float red_s[8];
+    merge_body(part_o, part_ml, n_splits, D, w_s, red_s,
+               PeerSink{g, out_dtype, g.unit_offset * (int64_t)gridDim.y * D});
+    __syncthreads();                                  // the CTA's stores are issued
+    if (threadIdx.x != 0) return;
+    __threadfence_system();                           // ... and ordered before the count below, system-wide
+    const unsigned total = gridDim.x * gridDim.y;
+    if (atomicAdd(&g_gather_done, 1u) + 1u != total) return;
+    g_gather_done = 0;                                // re-armed for the next launch (stream order)
+    __threadfence_system();
+    for (int r = 0; r < g.world; ++r) st_release_sys(g.flag_ptrs[r] + g.rank, g.epoch);
+    if (!g.wait) return;
+    const uint32_t* mine = g.flag_ptrs[g.rank];
+    for (int r = 0; r < g.world; ++r) {
+        uint32_t it = 0;
+        while ((int32_t)(ld_acquire_sys(mine + r) - g.epoch) < 0) {
+            if (++it > kPeerSpinLimit) { atomicOr(&g_gather_fault, 2); return; }
+            __nanosleep(200);
+        }
+    }
+}
+
+}  // namespace
+
+int gather_fault_word(int* out) {
+    KIVI_CUDA_OK(cudaMemcpyFromSymbol(out, g_gather_fault, sizeof(int)));
+    return KIVI_OK;
+}
+
+// merge of the split partials into `out`, or (gather != nullptr) into every
+// rank's gathered buffer; queued behind the attention kernel with programmatic
+// stream serialization, so its launch latency overlaps that kernel's tail
+int run_merge(const float* part_o, const float* part_ml, void* out, const kivi_peer_gather* gather,
+              int out_dtype, int num_units, int n_rep, int n_splits, int D, cudaStream_t st) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)num_units, (unsigned)n_rep);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = n_splits * sizeof(float);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (gather) {
+        kivi_peer_gather g = *gather;
+        KIVI_CUDA_OK(cudaLaunchKernelEx(&cfg, merge_gather_kernel, part_o, part_ml, g, out_dtype, n_splits, D));
+    } else {
+        KIVI_CUDA_OK(cudaLaunchKernelEx(&cfg, merge_splits_kernel, part_o, part_ml, out, out_dtype, n_splits, D));
+    }
+    return KIVI_OK;
 }
 
 template <int NREP>

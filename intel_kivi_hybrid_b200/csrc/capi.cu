@@ -52,8 +52,9 @@ int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_
                  const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
                  int n_res_splits, int res_chunk, float* part_o, float* part_ml, cudaStream_t st);
 int attn_mma_fault_word(int* out);
-__global__ void merge_splits_kernel(const float* part_o, const float* part_ml, void* out,
-                                    int out_dtype, int n_splits, int D);
+int gather_fault_word(int* out);
+int run_merge(const float* part_o, const float* part_ml, void* out, const kivi_peer_gather* gather,
+              int out_dtype, int num_units, int n_rep, int n_splits, int D, cudaStream_t st);
 
 }  // namespace kivi
 
@@ -64,7 +65,11 @@ extern "C" int kivi_version(void) { return 100; }
 extern "C" int kivi_last_launch_count(void) { return g_launches; }
 extern "C" int kivi_device_fault(int* word_out) {
     KIVI_REQUIRE(word_out != nullptr, "word_out is null");
-    return attn_mma_fault_word(word_out);
+    int copy_wait = 0, peer_wait = 0;
+    if (int rc = attn_mma_fault_word(&copy_wait)) return rc;
+    if (int rc = gather_fault_word(&peer_wait)) return rc;
+    *word_out = (copy_wait ? 1 : 0) | (peer_wait ? 2 : 0);
+    return KIVI_OK;
 }
 
 static int check_values_args(int64_t num_tokens, int head_dim, int group_size) {
@@ -168,13 +173,14 @@ static int plan_splits_mma(int num_units, int64_t n_groups, int requested, int n
     return clamp_splits(s, n_groups);
 }
 
-extern "C" int kivi_decode_attention(const kivi_layer* L, int64_t quant_len, int res_start,
-                                     int res_len, const void* q, int q_dtype, void* out, int out_dtype,
-                                     int n_rep, float sm_scale, void* workspace, size_t workspace_bytes,
-                                     int num_splits, int path, void* stream) {
+static int decode_attention_impl(const kivi_layer* L, int64_t quant_len, int res_start,
+                                 int res_len, const void* q, int q_dtype, void* out,
+                                 const kivi_peer_gather* gather, int out_dtype,
+                                 int n_rep, float sm_scale, void* workspace, size_t workspace_bytes,
+                                 int num_splits, int path, void* stream) {
     if (int rc = validate_layer(L)) return rc;
     if (int rc = validate_state(L, quant_len, res_start, res_len)) return rc;
-    KIVI_REQUIRE(q && out, "q / out are null");
+    KIVI_REQUIRE(q && (out || gather), "q / out are null");
     KIVI_REQUIRE(q_dtype == KIVI_F32 || q_dtype == KIVI_BF16, "q dtype must be KIVI_F32 or KIVI_BF16");
     KIVI_REQUIRE(out_dtype == KIVI_F32 || out_dtype == KIVI_BF16, "out dtype must be KIVI_F32 or KIVI_BF16");
     KIVI_REQUIRE(n_rep >= 1 && n_rep <= 8, "n_rep (%d) outside 1..8", n_rep);
@@ -215,24 +221,74 @@ extern "C" int kivi_decode_attention(const kivi_layer* L, int64_t quant_len, int
         ? run_attn_mma(L, quant_len, res_start, res_len, q, q_dtype, n_rep, scale_log2, nq_splits, gps, n_res_splits, res_chunk, part_o, part_ml, st)
         : run_attn_fp32(L, quant_len, res_start, res_len, q, q_dtype, n_rep, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st);
     if (rc) return rc;
-    {
-        // the merge is queued behind the attention kernel with programmatic stream
-        // serialization, so its launch latency overlaps that kernel's tail
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)L->num_units, (unsigned)n_rep);
-        cfg.blockDim = dim3(128);
-        cfg.dynamicSmemBytes = n_splits * sizeof(float);
-        cfg.stream = st;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        const float* po = part_o;
-        const float* pm = part_ml;
-        KIVI_CUDA_OK(cudaLaunchKernelEx(&cfg, merge_splits_kernel, po, pm, out, out_dtype, n_splits, D));
-    }
+    if (int rc2 = run_merge(part_o, part_ml, out, gather, out_dtype, L->num_units, n_rep, n_splits, D, st)) return rc2;
     note_launches(2);
+    return KIVI_OK;
+}
+
+extern "C" int kivi_decode_attention(const kivi_layer* L, int64_t quant_len, int res_start,
+                                     int res_len, const void* q, int q_dtype, void* out, int out_dtype,
+                                     int n_rep, float sm_scale, void* workspace, size_t workspace_bytes,
+                                     int num_splits, int path, void* stream) {
+    return decode_attention_impl(L, quant_len, res_start, res_len, q, q_dtype, out, nullptr, out_dtype, n_rep,
+                                 sm_scale, workspace, workspace_bytes, num_splits, path, stream);
+}
+
+// ---- decode attention + all-gather over peer memory -------------------------------
+extern "C" int kivi_decode_attention_gather(const kivi_layer* L, int64_t quant_len, int res_start,
+                                            int res_len, const void* q, int q_dtype,
+                                            const kivi_peer_gather* gather, int out_dtype,
+                                            int n_rep, float sm_scale, void* workspace, size_t workspace_bytes,
+                                            int num_splits, int path, void* stream) {
+    KIVI_REQUIRE(gather != nullptr, "gather is null");
+    KIVI_REQUIRE(gather->world >= 1 && gather->world <= KIVI_PEER_MAX_WORLD, "world (%d) outside 1..%d", gather->world, KIVI_PEER_MAX_WORLD);
+    KIVI_REQUIRE(gather->rank >= 0 && gather->rank < gather->world, "rank (%d) outside 0..%d", gather->rank, gather->world - 1);
+    KIVI_REQUIRE(gather->unit_offset >= 0, "unit_offset is negative");
+    KIVI_REQUIRE(gather->epoch != 0, "epoch starts at 1");
+    for (int r = 0; r < gather->world; ++r)
+        KIVI_REQUIRE(gather->out_ptrs[r] != nullptr && gather->flag_ptrs[r] != nullptr, "buffer or flag pointer of rank %d is null", r);
+    return decode_attention_impl(L, quant_len, res_start, res_len, q, q_dtype, nullptr, gather, out_dtype, n_rep,
+                                 sm_scale, workspace, workspace_bytes, num_splits, path, stream);
+}
+
+// Inter-process buffers for the gather: plain cudaMalloc memory shared through
+// CUDA IPC handles (same node; the driver maps the peer's memory over NVLink).
+extern "C" int kivi_peer_alloc(size_t bytes, void** ptr_out, unsigned char handle_out[64]) {
+    KIVI_REQUIRE(bytes > 0 && ptr_out != nullptr && handle_out != nullptr, "bytes, ptr_out and handle_out must be given");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    void* p = nullptr;
+    KIVI_CUDA_OK(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        set_error("kivi_peer_alloc failed: %s", cudaGetErrorString(e));
+        return KIVI_ERR_CUDA;
+    }
+    memcpy(handle_out, &h, 64);
+    *ptr_out = p;
+    return KIVI_OK;
+}
+
+extern "C" int kivi_peer_open(const unsigned char handle[64], void** ptr_out) {
+    KIVI_REQUIRE(handle != nullptr && ptr_out != nullptr, "handle and ptr_out must be given");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    KIVI_CUDA_OK(cudaIpcOpenMemHandle(ptr_out, h, cudaIpcMemLazyEnablePeerAccess));
+    return KIVI_OK;
+}
+
+extern "C" int kivi_peer_close(void* ptr) {
+    KIVI_REQUIRE(ptr != nullptr, "ptr is null");
+    KIVI_CUDA_OK(cudaIpcCloseMemHandle(ptr));
+    return KIVI_OK;
+}
+
+extern "C" int kivi_peer_free(void* ptr) {
+    KIVI_REQUIRE(ptr != nullptr, "ptr is null");
+    KIVI_CUDA_OK(cudaFree(ptr));
     return KIVI_OK;
 }
 

@@ -5,12 +5,17 @@ of `world` permanently owns a contiguous run of units and no KV ever crosses
 NVLink.  The one exchange per layer-step is an all-gather of the attention
 outputs [units, n_rep, D] (the reference is single-device: nothing to cite).
 Works on any torch.distributed backend: NCCL on GPUs, gloo in the CPU tests.
+
+`PeerGather` is the fused form of that exchange on GPUs: the attention's last
+kernel stores every output row into all ranks' gathered buffers through
+peer-mapped memory and the ranks synchronise through flags in the same memory,
+so no separate collective is launched.
 """
 from typing import Tuple
 
 import torch
 
-__all__ = ["unit_partition", "all_gather_units"]
+__all__ = ["unit_partition", "all_gather_units", "PeerGather"]
 
 
 def unit_partition(n_units: int, rank: int, world: int) -> Tuple[int, int]:
@@ -41,3 +46,78 @@ def all_gather_units(local: torch.Tensor, n_units: int, rank: int, world: int, g
     buf = torch.empty((world * biggest,) + tuple(tail), dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(buf, padded, group=group)
     return torch.cat([buf[r * biggest: r * biggest + (b - a)] for r, (a, b) in enumerate(sizes)], dim=0)
+
+
+class PeerGather:
+    """Gathered attention-output buffers of the ranks of one node, mapped into
+    every rank (CUDA IPC through kivi_peer_alloc / kivi_peer_open), for
+    LayerStore.attention_gather.
+
+    Each rank owns two gathered buffers [n_units * n_rep * D] (alternated by
+    epoch parity, so a rank that runs one call ahead never overwrites what a
+    slower rank's consumer is still reading) and one flag array.  Setup is
+    collective over `group` (handles travel by all_gather_object); equal unit
+    counts per rank are not required.
+    """
+
+    def __init__(self, n_units: int, n_rep: int, head_dim: int, dtype, rank: int, world: int, group=None):
+        import torch.distributed as dist
+        from . import cabi
+        assert 1 <= world <= cabi.PEER_MAX_WORLD
+        self._cabi, self.rank, self.world, self.dtype = cabi, rank, world, dtype
+        self.n_units, self.n_rep, self.D = n_units, n_rep, head_dim
+        self.u0, self.u1 = unit_partition(n_units, rank, world)
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        esz = torch.empty((), dtype=dtype).element_size()
+        self._buf_bytes = -(-n_units * n_rep * head_dim * esz // 256) * 256
+        # one allocation per rank: [buffer 0 | buffer 1 | flags]
+        self._own_ptr, handle = cabi.peer_alloc(2 * self._buf_bytes + 256)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle, group=group)
+        self._ptrs = [self._own_ptr if r == rank else cabi.peer_open(handles[r]) for r in range(world)]
+        self.epoch = 0
+        dist.barrier(group=group)
+
+    def descriptor(self, wait: bool = True):
+        """The kivi_peer_gather of the next call (advances the epoch)."""
+        c = self._cabi
+        self.epoch += 1
+        d = c.PeerGatherDesc()
+        d.rank, d.world, d.unit_offset, d.epoch, d.wait = self.rank, self.world, self.u0, self.epoch, int(wait)
+        half = (self.epoch & 1) * self._buf_bytes
+        for r in range(self.world):
+            d.out_ptrs[r] = self._ptrs[r] + half
+            d.flag_ptrs[r] = self._ptrs[r] + 2 * self._buf_bytes
+        return d
+
+    def gathered(self) -> torch.Tensor:
+        """[n_units, n_rep, D] view of this rank's gathered buffer of the last
+        call (valid once that call's kernels have completed on the stream)."""
+        n = self.n_units * self.n_rep * self.D
+        half = (self.epoch & 1) * self._buf_bytes
+        return _tensor_from_ptr(self._own_ptr + half, n, self.dtype, self.device).view(self.n_units, self.n_rep, self.D)
+
+    def close(self, group=None):
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier(group=group)                       # nobody still writes into a peer
+        for r, p in enumerate(self._ptrs):
+            if r != self.rank and p:
+                self._cabi.peer_close(p)
+        dist.barrier(group=group)                       # every mapping is gone before the owner frees
+        if self._own_ptr:
+            self._cabi.peer_free(self._own_ptr)
+        self._ptrs, self._own_ptr = [], 0
+
+
+class _CudaArray:
+    """__cuda_array_interface__ holder so that torch can view foreign device memory."""
+
+    def __init__(self, ptr, n, typestr):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 3}
+
+
+def _tensor_from_ptr(ptr: int, n: int, dtype, device) -> torch.Tensor:
+    if dtype == torch.bfloat16:          # no typestr for bf16: view 16-bit words
+        return torch.as_tensor(_CudaArray(ptr, n, "<i2"), device=device).view(torch.bfloat16)
+    return torch.as_tensor(_CudaArray(ptr, n, "<f4"), device=device)

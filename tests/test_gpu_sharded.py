@@ -1,8 +1,12 @@
 """Sharded KiviCache on two GPUs (skipped when fewer are visible): every rank
 keeps half of the (batch, kv_head) units, the all-gathered decode-attention
 output must equal the single-GPU output bit for bit (same kernel, same number
-of splits per unit) and the oracle within tolerance.  Ranks are child processes over
-NCCL; each leaves only after its last collective has completed."""
+of splits per unit) and the oracle within tolerance; the same holds when the
+all-gather happens inside the attention's last kernel through peer-mapped memory
+(gather="peer", three calls in a row so that both halves of the double buffer
+and the epoch flags are exercised).  Ranks are child processes over NCCL; each
+leaves only after its last collective has completed.  A world of one (gloo, one
+GPU) runs the same peer-gather kernel without peers."""
 import os
 import subprocess
 import sys
@@ -21,7 +25,10 @@ from oracle import kivi_oracle as ko
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
 dev = f"cuda:{rank}"
-dist.init_process_group("nccl", device_id=torch.device(dev), timeout=datetime.timedelta(seconds=60))
+if world > 1:
+    dist.init_process_group("nccl", device_id=torch.device(dev), timeout=datetime.timedelta(seconds=60))
+else:
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=60))
 B, Hkv, n_rep, D, T = 2, 4, 4, 128, 650
 K = ko.make_keys(B, Hkv, T, D, 5).to(torch.bfloat16)
 V = ko.make_values(B, Hkv, T, D, 5).to(torch.bfloat16)
@@ -39,6 +46,27 @@ assert torch.equal(out_s, out_1), "sharded output differs from the single-GPU ou
 ref = ko.kivi_decode_attention(q, K, V, single._quant_token_count[0], 32, "half_away", dtype=torch.float64).float()
 err = ((out_s.cpu() - ref).abs().amax(-1) / ref.abs().amax(-1)).max().item()
 assert err < 2e-3, err
+from intel_kivi_hybrid_b200 import cabi
+if world == 1:
+    # a world of one: the gather kernel, the shared allocation and the flags, no peer
+    from intel_kivi_hybrid_b200.parallel import PeerGather
+    pg = PeerGather(B * Hkv, n_rep, D, torch.float32, 0, 1)
+    st = single._stores[0]
+    for _ in range(3):
+        st.attention_gather(q.to(dev).reshape(B * Hkv, n_rep, D), pg.descriptor(), torch.float32, n_rep, num_splits=3)
+        torch.cuda.synchronize()
+        assert torch.equal(pg.gathered().reshape(B, Hkv * n_rep, D), out_1), "peer-gather output differs"
+    pg.close()
+else:
+    peer = KiviCache(num_layers=1, head_dim=D, device=dev, shard=(rank, world), gather="peer")
+    peer.add_tokens(((K[:, :, :T - 3].to(dev), V[:, :, :T - 3].to(dev)),))
+    peer.add_tokens(((K.to(dev), V.to(dev)),))
+    for _ in range(3):
+        out_p = peer.decode_attention(0, q.to(dev), out_dtype=torch.float32, num_splits=3)
+        torch.cuda.synchronize()
+        assert torch.equal(out_p, out_1), "peer-gather output differs from the single-GPU output"
+    peer.close()
+assert cabi.device_fault() == 0
 dist.barrier()
 torch.cuda.synchronize()
 dist.destroy_process_group()
@@ -63,3 +91,13 @@ def test_sharded_cache_equals_single_gpu(tmp_path):
             outs.append("timeout")
     assert all(p.returncode == 0 for p in procs), outs
     assert all("ok" in o for o in outs), outs
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 1, reason="needs a GPU")
+def test_peer_gather_kernel_world_of_one(tmp_path):
+    script = tmp_path / "worker1.py"
+    script.write_text(_WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29657", WORLD_SIZE="1", RANK="0")
+    p = subprocess.run([sys.executable, str(script), ROOT], env=env, stdout=subprocess.PIPE,
+                       stderr=subprocess.STDOUT, text=True, timeout=240)
+    assert p.returncode == 0 and "ok" in p.stdout, p.stdout
