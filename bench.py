@@ -218,7 +218,11 @@ def run_ours(args, wl):
     pg = None
     if world > 1 and args.gather == "peer":
         from intel_kivi_hybrid_b200.parallel import PeerGather
-        pg = PeerGather(world * U, n_rep, D, dtype, rank, world)
+        try:                                   # raises on every rank or on none
+            pg = PeerGather(world * U, n_rep, D, dtype, rank, world)
+        except RuntimeError as exc:
+            if rank == 0:
+                print(f"[bench] {exc}; falling back to the NCCL all-gather", file=sys.stderr)
 
     def attend(store):
         if pg is not None:

@@ -67,14 +67,36 @@ class PeerGather:
         self._cabi, self.rank, self.world, self.dtype = cabi, rank, world, dtype
         self.n_units, self.n_rep, self.D = n_units, n_rep, head_dim
         self.u0, self.u1 = unit_partition(n_units, rank, world)
-        self.device = torch.device("cuda", torch.cuda.current_device())
         esz = torch.empty((), dtype=dtype).element_size()
         self._buf_bytes = -(-n_units * n_rep * head_dim * esz // 256) * 256
-        # one allocation per rank: [buffer 0 | buffer 1 | flags]
-        self._own_ptr, handle = cabi.peer_alloc(2 * self._buf_bytes + 256)
+        # one allocation per rank: [buffer 0 | buffer 1 | flags].  Every rank takes
+        # part in every exchange below even after a local failure, so that all
+        # ranks raise together instead of one of them leaving the others waiting.
+        self._own_ptr, self._ptrs, handle, err = 0, [], None, None
+        try:
+            self._own_ptr, handle = cabi.peer_alloc(2 * self._buf_bytes + 256)
+        except RuntimeError as exc:
+            err = f"rank {rank}: {exc}"
         handles = [None] * world
-        dist.all_gather_object(handles, handle, group=group)
-        self._ptrs = [self._own_ptr if r == rank else cabi.peer_open(handles[r]) for r in range(world)]
+        dist.all_gather_object(handles, (handle, err), group=group)
+        if all(h is not None for h, _ in handles):
+            try:
+                for r in range(world):
+                    self._ptrs.append(self._own_ptr if r == rank else cabi.peer_open(handles[r][0]))
+            except RuntimeError as exc:
+                err = f"rank {rank}: {exc}"
+        errs = [None] * world
+        dist.all_gather_object(errs, err, group=group)
+        failed = [e for e in errs if e] + [e for _, e in handles if e]
+        if failed:
+            for r, p in enumerate(self._ptrs):
+                if r != rank:
+                    cabi.peer_close(p)
+            dist.barrier(group=group)
+            if self._own_ptr:
+                cabi.peer_free(self._own_ptr)
+            self._ptrs, self._own_ptr = [], 0
+            raise RuntimeError("peer-gather setup failed: " + "; ".join(sorted(set(failed))))
         self.epoch = 0
         dist.barrier(group=group)
 
@@ -95,7 +117,8 @@ class PeerGather:
         call (valid once that call's kernels have completed on the stream)."""
         n = self.n_units * self.n_rep * self.D
         half = (self.epoch & 1) * self._buf_bytes
-        return _tensor_from_ptr(self._own_ptr + half, n, self.dtype, self.device).view(self.n_units, self.n_rep, self.D)
+        device = torch.device("cuda", torch.cuda.current_device())
+        return _tensor_from_ptr(self._own_ptr + half, n, self.dtype, device).view(self.n_units, self.n_rep, self.D)
 
     def close(self, group=None):
         import torch.distributed as dist

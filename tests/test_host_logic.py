@@ -93,6 +93,53 @@ def test_all_gather_units_gloo_world2(tmp_path):
     assert all("ok" in o for o in outs)
 
 
+_PEER_FAIL_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from intel_kivi_hybrid_b200.parallel import PeerGather
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo")
+try:
+    PeerGather(8, 4, 128, torch.bfloat16, rank, world)      # no GPU here: the allocation fails on every rank
+    print("no error", rank)
+except RuntimeError as exc:
+    assert "peer-gather setup failed" in str(exc) and "rank 0" in str(exc) and "rank 1" in str(exc), exc
+    print("ok", rank)
+dist.barrier()
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the failure path of a box without GPUs")
+def test_peer_gather_setup_fails_on_all_ranks_together(tmp_path):
+    """A rank whose buffer cannot be allocated still takes part in every exchange
+    of the setup, so all ranks raise the same error and none is left waiting."""
+    script = tmp_path / "worker.py"
+    script.write_text(_PEER_FAIL_WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29643", WORLD_SIZE="2")
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT], env=dict(env, RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=120)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    assert all("ok" in o for o in outs), outs
+
+
+def test_peer_gather_descriptor_alternates_buffers():
+    from intel_kivi_hybrid_b200 import cabi
+    from intel_kivi_hybrid_b200.parallel import PeerGather
+    pg = PeerGather.__new__(PeerGather)          # no allocation: only the descriptor arithmetic
+    pg._cabi, pg.rank, pg.world, pg.u0, pg.epoch = cabi, 1, 2, 4, 0
+    pg._buf_bytes, pg._ptrs = 4096, [0x10000, 0x20000]
+    d1, d2, d3 = pg.descriptor(), pg.descriptor(wait=False), pg.descriptor()
+    assert (d1.epoch, d2.epoch, d3.epoch) == (1, 2, 3) and (d1.wait, d2.wait) == (1, 0)
+    assert (d1.rank, d1.world, d1.unit_offset) == (1, 2, 4)
+    assert [d1.out_ptrs[r] for r in range(2)] == [0x10000 + 4096, 0x20000 + 4096]      # odd epoch: second half
+    assert [d2.out_ptrs[r] for r in range(2)] == [0x10000, 0x20000]
+    assert [d3.out_ptrs[r] for r in range(2)] == [d1.out_ptrs[r] for r in range(2)]
+    assert [d1.flag_ptrs[r] for r in range(2)] == [0x10000 + 8192, 0x20000 + 8192]
+    assert d1.out_ptrs[2] is None
+
+
 def test_detect_model_config_families():
     from intel_kivi_hybrid_b200.config.model_config import detect_model_config
     mk = lambda **kw: types.SimpleNamespace(config=types.SimpleNamespace(**kw))
