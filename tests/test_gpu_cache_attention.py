@@ -340,3 +340,53 @@ def test_full_size_config2_properties(cabi):
     kk, vv = k[:1].cpu().reshape(1, 1, T, D), v[:1].cpu().reshape(1, 1, T, D)
     ref = ko.kivi_decode_attention(q[:1].cpu().reshape(1, n_rep, D), kk, vv, n_quant, G, "half_away", dtype=torch.float64)
     assert rel_err(o_auto[:1], ref.float().reshape(1, n_rep, D)) < TOL_BF16
+
+
+def test_full_size_config4_prefill_properties(cabi):
+    """Bulk prefill at the benchmark's full size (256 units, 8192 tokens, bf16):
+    the round trip through the packed store stays within half a quantization
+    step of the input for every element (step = the stored scale of its group),
+    ring tokens come back exactly, and two sampled units equal the CPU oracle bit
+    for bit (codes through the dequantized values, scales and zeros directly)."""
+    U, S, D, G, R = 256, 8192, 128, 32, 128
+    g = torch.Generator(device="cuda").manual_seed(77)
+    k = torch.empty(U, S, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.empty(U, S, D, device="cuda", dtype=torch.bfloat16)
+    for u0 in range(0, U, 64):
+        k[u0:u0 + 64] = torch.randn(64, S, D, device="cuda", generator=g).to(torch.bfloat16)
+        v[u0:u0 + 64] = torch.randn(64, S, D, device="cuda", generator=g).to(torch.bfloat16)
+    k[:, :, 9] *= 10.0
+    st = cabi.LayerStore(U, D, G, R, S, torch.bfloat16, "cuda")
+    st.update(k, v)
+    n_flush, ql, rl = cabi.cache_plan(0, 0, S, G, R)
+    assert (st.quant_len, st.res_len) == (ql, rl) == (S - 96, 96)
+    ng = ql // G
+    for name, x, by_token in (("k", k, False), ("v", v, True)):
+        served = st.materialize()[1 if by_token else 0]                     # fp32 [U, S, D]
+        assert torch.equal(served[:, ql:], x[:, ql:].float()), f"{name}: ring tokens must come back exactly"
+        if by_token:        # scale of (token t, channel group gd); stored rows are permuted inside 32-token blocks
+            rows = st.v_scales[:, :ql].reshape(U, ng, 2, 4, 4, D // G).permute(0, 1, 2, 4, 3, 5).reshape(U, ql, D // G)
+            step = rows.repeat_interleave(G, dim=2)
+        else:               # scale of (group g, channel d)
+            step = st.k_scales[:, :ng].repeat_interleave(G, dim=1)
+        worst = 0.0
+        for u0 in range(0, U, 32):                                           # bounded temporaries
+            err = (served[u0:u0 + 32, :ql] - x[u0:u0 + 32, :ql].float()).abs()
+            bound = step[u0:u0 + 32] * 0.5 * (1 + 1e-5) + 1e-30
+            assert bool((err <= bound).all()), f"{name}: round trip off by more than half a step"
+            worst = max(worst, float((err / step[u0:u0 + 32]).max()))
+        print(f"[cfg4 full size] {name}: worst |error| / step = {worst:.4f}")
+        del served, step
+    # two units against the oracle
+    for u in (3, 200):
+        oc = ko.OracleCache(D, G, R, rounding="half_away")
+        ku, vu = k[u].float().cpu().reshape(1, 1, S, D), v[u].float().cpu().reshape(1, 1, S, D)
+        oc.append(ku, vu)
+        sk, sv = oc.served()
+        one = cabi.LayerStore(1, D, G, R, S, torch.bfloat16, "cuda")
+        one.update(k[u:u + 1], v[u:u + 1])
+        gk, gv = one.materialize()
+        assert torch.equal(gk.cpu(), sk.reshape(1, S, D)) and torch.equal(gv.cpu(), sv.reshape(1, S, D))
+        assert torch.equal(one.k_scales[0, :ng].cpu(), torch.stack(oc.k_scales, dim=2).reshape(ng, D))
+        assert torch.equal(st.k_scales[u, :ng].cpu(), one.k_scales[0, :ng].cpu())
+        assert torch.equal(st.v_codes[u, :ql].cpu(), one.v_codes[0, :ql].cpu())
