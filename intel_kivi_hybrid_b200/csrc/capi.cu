@@ -158,16 +158,31 @@ static int plan_splits_fp32(int num_units, int64_t n_groups, int requested) {
 // copy, the merge of its warps) plus c1 = 0.47 us per token group, so with
 // `slots` resident CTAs the time of s splits per unit is about
 //   units*s*c0/slots + units*n_groups*c1/slots + (c0 + n_groups*c1/s)/2,
-// minimal at s = sqrt(n_groups*c1*slots / (2*units*c0)).  When that lands
-// between one and two waves of CTAs, one full wave is faster.
+// minimal at s = sqrt(n_groups*c1*slots / (2*units*c0)).
+// One exactly filled wave beats that whenever it exists: if the quantized CTAs
+// of all units fill at least 90 % of the slots without exceeding them, every
+// CTA starts at once and they all end together.  The ring CTAs come first in
+// the grid and last about t_ring = 7 us; if they push the total past one wave,
+// the quantized CTAs that had to wait start that much later, which is weighed
+// against the longer CTAs of one split less (measured at 128k tokens, 32 units:
+// 13 splits 144 us, 12 splits 149 us, 14 splits 179 us, the formula's 36: 150-157 us;
+// at 64k tokens, 16 units: 26 splits 48 us, 27 splits 51 us).
 static int plan_splits_mma(int num_units, int64_t n_groups, int requested, int n_res_splits) {
     if (n_groups <= 0) return 0;
     if (requested > 0) return clamp_splits(requested, n_groups);
     const double slots = 3.0 * num_sms();
-    const double c1_over_c0 = 0.047;
-    int64_t s = (int64_t)llround(sqrt(0.5 * (double)n_groups * c1_over_c0 * slots / num_units));
+    const double c0 = 10.0, c1 = 0.425, t_ring = 7.0;
+    const int64_t s_wave = (int64_t)(slots / num_units);                    // quantized CTAs alone fill one wave
+    if (s_wave >= 1 && (double)(s_wave * num_units) >= 0.9 * slots) {
+        const int64_t s_all = s_wave - n_res_splits;                        // ring CTAs fit into the wave as well
+        auto cta_us = [&](int64_t sp) { return c0 + (double)((n_groups + sp - 1) / sp) * c1; };
+        const double t_wave = cta_us(s_wave) + (n_res_splits > 0 ? t_ring : 0.0);
+        if (s_all >= 1 && cta_us(s_all) <= t_wave) return clamp_splits(s_all, n_groups);
+        return clamp_splits(s_wave, n_groups);
+    }
+    int64_t s = (int64_t)llround(sqrt(0.5 * (double)n_groups * (0.47 / c0) * slots / num_units));
     if (s < 1) s = 1;
-    const int64_t s_fill = (int64_t)(slots / num_units) - n_res_splits;     // most splits that still fit one wave
+    const int64_t s_fill = s_wave - n_res_splits;                           // most splits that still fit one wave
     const double waves = (double)num_units * (double)(s + n_res_splits) / slots;
     if (waves < 2.0 && s_fill >= 1) s = s_fill;
     return clamp_splits(s, n_groups);
