@@ -191,6 +191,60 @@ void* enqueue_roundtrip_values(torch::Tensor& input, torch::Tensor& output, int 
 
 void block_on(void* st) { C10_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)st)); }
 
+
+
+// ---- the cache operators (no counterpart in the reference's module: there the
+// cache is Python over round-trip kernels, cache/manager.py:162-374) -------------
+// The packed store of one layer as tensors the caller owns:
+//   k_packed [units, max_groups, D*G/4] u8, k_scales / k_zeros [units, max_groups, D] f32,
+//   v_packed [units, max_tokens, D/4] u8,   v_scales / v_zeros [units, max_tokens, D/G] f32,
+//   k_res / v_res [units, R, D] f32 or bf16 (the residual ring),
+// with max_tokens = max_groups * G.  Only dtypes, devices, contiguity and numel
+// relations are checked, like the reference's validators.
+kivi_layer layer_of(const torch::Tensor& k_packed, const torch::Tensor& k_scales, const torch::Tensor& k_zeros,
+                    const torch::Tensor& v_packed, const torch::Tensor& v_scales, const torch::Tensor& v_zeros,
+                    const torch::Tensor& k_res, const torch::Tensor& v_res, int group_size) {
+    check_tensor(k_packed, "k_packed", torch::kUInt8);
+    check_tensor(v_packed, "v_packed", torch::kUInt8);
+    check_tensor(k_scales, "k_scales", torch::kFloat32);
+    check_tensor(k_zeros, "k_zeros", torch::kFloat32);
+    check_tensor(v_scales, "v_scales", torch::kFloat32);
+    check_tensor(v_zeros, "v_zeros", torch::kFloat32);
+    TORCH_CHECK(k_res.dim() == 3 && v_res.sizes() == k_res.sizes(), "k_res and v_res must both be [units, R, D]");
+    TORCH_CHECK(k_res.scalar_type() == torch::kFloat32 || k_res.scalar_type() == torch::kBFloat16,
+                "k_res must be Float or BFloat16 but got ", torch::toString(k_res.scalar_type()));
+    check_tensor(k_res, "k_res", k_res.scalar_type());
+    check_tensor(v_res, "v_res", k_res.scalar_type());
+    const int64_t units = k_res.size(0), R = k_res.size(1), D = k_res.size(2);
+    const int G = group_size;
+    TORCH_CHECK(G > 0 && G % 4 == 0, "group_size must be positive and divisible by 4, got ", G);
+    TORCH_CHECK(D > 0 && D % G == 0, "head_dim (", D, ") must be divisible by group_size (", G, ")");
+    TORCH_CHECK(units > 0 && k_scales.numel() % (units * D) == 0, "k_scales size (", k_scales.numel(),
+                ") must be units(", units, ") * max_groups * head_dim(", D, ")");
+    const int64_t max_groups = k_scales.numel() / (units * D), max_tokens = max_groups * G;
+    TORCH_CHECK(k_zeros.numel() == k_scales.numel(), "k_zeros size must match k_scales size");
+    TORCH_CHECK(k_packed.numel() == units * max_groups * (D * G / 4), "k_packed size (", k_packed.numel(),
+                ") must equal units * max_groups * head_dim * group_size / 4 = ", units * max_groups * (D * G / 4));
+    TORCH_CHECK(v_packed.numel() == units * max_tokens * (D / 4), "v_packed size (", v_packed.numel(),
+                ") must equal units * max_tokens * head_dim / 4 = ", units * max_tokens * (D / 4));
+    TORCH_CHECK(v_scales.numel() == units * max_tokens * (D / G) && v_zeros.numel() == v_scales.numel(),
+                "v_scales / v_zeros size must equal units * max_tokens * head_dim / group_size = ", units * max_tokens * (D / G));
+    kivi_layer L;
+    L.num_units = (int32_t)units; L.head_dim = (int32_t)D; L.group_size = G; L.residual_cap = (int32_t)R;
+    L.max_tokens = max_tokens; L.res_dtype = k_res.scalar_type() == torch::kFloat32 ? KIVI_F32 : KIVI_BF16; L.reserved = 0;
+    L.k_codes = k_packed.data_ptr<uint8_t>(); L.k_scales = k_scales.data_ptr<float>(); L.k_zeros = k_zeros.data_ptr<float>();
+    L.v_codes = v_packed.data_ptr<uint8_t>(); L.v_scales = v_scales.data_ptr<float>(); L.v_zeros = v_zeros.data_ptr<float>();
+    L.k_res = k_res.data_ptr(); L.v_res = v_res.data_ptr();
+    return L;
+}
+
+int dtype_code(const torch::Tensor& t, const char* name) {
+    TORCH_CHECK(t.scalar_type() == torch::kFloat32 || t.scalar_type() == torch::kBFloat16, name,
+                " must be Float or BFloat16 but got ", torch::toString(t.scalar_type()));
+    TORCH_CHECK(t.is_cuda(), name, " must be on cuda but got ", t.device().str());
+    return t.scalar_type() == torch::kFloat32 ? KIVI_F32 : KIVI_BF16;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -256,4 +310,57 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
               return KiviEvent(enqueue_roundtrip_values(input, output, head_dim, group_size, rounding)); },
           "Non-blocking quant_dequant_roundtrip_values - returns a KiviEvent, does not wait.",
           py::arg("input"), py::arg("output"), py::arg("head_dim"), py::arg("group_size"), py::arg("rounding") = R0);
+
+    // ---- cache operators ---------------------------------------------------------
+    m.def("append_and_flush",
+          [](T new_k, T new_v, T k_packed, T k_scales, T k_zeros, T v_packed, T v_scales, T v_zeros, T k_res, T v_res,
+             int64_t quant_len, int res_start, int res_len, int group_size, int rounding) {
+              c10::cuda::CUDAGuard guard(k_res.device());
+              kivi_layer L = layer_of(k_packed, k_scales, k_zeros, v_packed, v_scales, v_zeros, k_res, v_res, group_size);
+              const int dt = dtype_code(new_k, "new_k");
+              TORCH_CHECK(new_v.scalar_type() == new_k.scalar_type() && new_v.is_cuda(), "new_v must match new_k's dtype and device");
+              TORCH_CHECK(new_k.dim() == 3 && new_k.sizes() == new_v.sizes() && new_k.size(0) == L.num_units && new_k.size(2) == L.head_dim,
+                          "new_k / new_v must be [units, n_new, head_dim]");
+              TORCH_CHECK(new_k.stride(2) == 1 && new_v.stride(2) == 1, "the last dimension of new_k / new_v must be contiguous");
+              int64_t ql = 0; int rs = 0, rl = 0;
+              check(kivi_cache_update(&L, quant_len, res_start, res_len, new_k.data_ptr(), new_v.data_ptr(), dt,
+                                      new_k.stride(0), new_k.stride(1), new_v.stride(0), new_v.stride(1), (int)new_k.size(1),
+                                      rounding, &ql, &rs, &rl, stream_of(k_res)));
+              return std::make_tuple(ql, rs, rl);
+          },
+          "Append n_new tokens to a layer's cache: while the ring holds >= R tokens its oldest group_size tokens are "
+          "quantized into the packed store (add_tokens + _flush_group of the reference, cache/manager.py:162-374), all on "
+          "the device and in stream order.  Returns the new (quant_len, res_start, res_len).",
+          py::arg("new_k"), py::arg("new_v"), py::arg("k_packed"), py::arg("k_scales"), py::arg("k_zeros"),
+          py::arg("v_packed"), py::arg("v_scales"), py::arg("v_zeros"), py::arg("k_res"), py::arg("v_res"),
+          py::arg("quant_len"), py::arg("res_start"), py::arg("res_len"), py::arg("group_size"), py::arg("rounding") = R0);
+    m.def("decode_attention",
+          [](T q, T k_packed, T k_scales, T k_zeros, T v_packed, T v_scales, T v_zeros, T k_res, T v_res,
+             int64_t quant_len, int res_start, int res_len, T out, int group_size, c10::optional<T> workspace,
+             double sm_scale, int num_splits, int path) {
+              c10::cuda::CUDAGuard guard(k_res.device());
+              kivi_layer L = layer_of(k_packed, k_scales, k_zeros, v_packed, v_scales, v_zeros, k_res, v_res, group_size);
+              const int qd = dtype_code(q, "q"), od = dtype_code(out, "out");
+              TORCH_CHECK(q.is_contiguous() && out.is_contiguous(), "q and out must be contiguous");
+              TORCH_CHECK(q.numel() == out.numel() && q.numel() % ((int64_t)L.num_units * L.head_dim) == 0 && q.numel() > 0,
+                          "q and out must both hold units * n_rep * head_dim elements");
+              const int n_rep = (int)(q.numel() / ((int64_t)L.num_units * L.head_dim));
+              const size_t need = kivi_decode_attention_workspace(L.num_units, n_rep, L.head_dim, num_splits);
+              T ws = workspace.has_value() ? *workspace
+                                           : torch::empty({(int64_t)need}, torch::TensorOptions().dtype(torch::kUInt8).device(q.device()));
+              check_tensor(ws, "workspace", torch::kUInt8);
+              check(kivi_decode_attention(&L, quant_len, res_start, res_len, q.data_ptr(), qd, out.data_ptr(), od, n_rep,
+                                          (float)sm_scale, ws.data_ptr(), (size_t)ws.numel(), num_splits, path, stream_of(q)));
+          },
+          "Fused decode attention over a layer's packed cache: out = softmax(q K^T * sm_scale) V over [quantized history || "
+          "residual ring] (the math of tests/integration/test_attention_fix.py:40-43), no dequantized cache is built.  "
+          "q, out: [units, n_rep, head_dim]; stream-ordered; workspace: optional uint8 scratch "
+          "(kivi_decode_attention_workspace bytes), allocated per call when omitted.",
+          py::arg("q"), py::arg("k_packed"), py::arg("k_scales"), py::arg("k_zeros"), py::arg("v_packed"), py::arg("v_scales"),
+          py::arg("v_zeros"), py::arg("k_res"), py::arg("v_res"), py::arg("quant_len"), py::arg("res_start"), py::arg("res_len"),
+          py::arg("out"), py::arg("group_size"), py::arg("workspace") = py::none(), py::arg("sm_scale") = 0.0,
+          py::arg("num_splits") = 0, py::arg("path") = 0);
+    m.def("decode_attention_workspace", [](int num_units, int n_rep, int head_dim, int num_splits) {
+              return (int64_t)kivi_decode_attention_workspace(num_units, n_rep, head_dim, num_splits); },
+          "Bytes of scratch decode_attention needs.", py::arg("num_units"), py::arg("n_rep"), py::arg("head_dim"), py::arg("num_splits") = 0);
 }

@@ -264,3 +264,56 @@ def test_state_dict_round_trip_resumes_bit_identically():
     assert a._quant_token_count == b._quant_token_count and a.total_flushes == b.total_flushes
     assert torch.equal(a.decode_attention(0, q), b.decode_attention(0, q))
     assert a.get_stats() == b.get_stats()
+
+
+@pytest.mark.parametrize("dtype,D,G,n_rep", [(torch.bfloat16, 128, 32, 4), (torch.float32, 64, 32, 1)])
+def test_cache_operators_of_the_extension(native, dtype, D, G, n_rep):
+    """_C.append_and_flush + _C.decode_attention on caller-owned tensors: same
+    counters and bit-identical stores / outputs as the ctypes path over the same
+    library, and the attention within tolerance of the oracle."""
+    from intel_kivi_hybrid_b200 import cabi
+    B, H, R, T, cap = 1, 3, 128, 333, 512
+    U = B * H
+    K = ko.make_keys(B, H, T, D, seed=31)
+    V = ko.make_values(B, H, T, D, seed=31)
+    q = ko.make_queries(B, H * n_rep, D, seed=31)
+    if dtype == torch.bfloat16:
+        K, V, q = K.bfloat16().float(), V.bfloat16().float(), q.bfloat16().float()
+    kc = K.reshape(U, T, D).to(DEV, dtype)
+    vc = V.reshape(U, T, D).to(DEV, dtype)
+    mg = cap // G
+    t = dict(k_packed=torch.zeros(U, mg, D * G // 4, dtype=torch.uint8, device=DEV),
+             k_scales=torch.zeros(U, mg, D, device=DEV), k_zeros=torch.zeros(U, mg, D, device=DEV),
+             v_packed=torch.zeros(U, cap, D // 4, dtype=torch.uint8, device=DEV),
+             v_scales=torch.zeros(U, cap, D // G, device=DEV), v_zeros=torch.zeros(U, cap, D // G, device=DEV),
+             k_res=torch.zeros(U, R, D, dtype=dtype, device=DEV), v_res=torch.zeros(U, R, D, dtype=dtype, device=DEV))
+    st = cabi.LayerStore(U, D, G, R, cap, dtype, DEV)
+    state = (0, 0, 0)
+    for a, b in ((0, 200), (200, 201), (201, T)):
+        state = native.append_and_flush(kc[:, a:b], vc[:, a:b], quant_len=state[0], res_start=state[1], res_len=state[2],
+                                        group_size=G, **t)
+        st.update(kc[:, a:b], vc[:, a:b])
+        assert tuple(state) == (st.quant_len, st.res_start, st.res_len)
+    for name in t:
+        assert torch.equal(t[name], getattr(st, {"k_packed": "k_codes", "v_packed": "v_codes"}.get(name, name))), name
+    qd = q.reshape(U, n_rep, D).to(DEV, dtype)
+    out = torch.full((U, n_rep, D), float("nan"), device=DEV, dtype=torch.float32)
+    native.decode_attention(qd, quant_len=state[0], res_start=state[1], res_len=state[2], out=out, group_size=G, **t)
+    ws = torch.empty(native.decode_attention_workspace(U, n_rep, D), dtype=torch.uint8, device=DEV)
+    out2 = torch.empty_like(out)
+    native.decode_attention(qd, t["k_packed"], t["k_scales"], t["k_zeros"], t["v_packed"], t["v_scales"], t["v_zeros"],
+                            t["k_res"], t["v_res"], state[0], state[1], state[2], out2, G, workspace=ws)
+    ref_out = st.attention(qd, n_rep=n_rep, out_dtype=torch.float32)
+    assert torch.equal(out, ref_out) and torch.equal(out2, ref_out)
+    oracle = ko.kivi_decode_attention(q, K, V, state[0], G, "half_away", dtype=torch.float64).float().reshape(U, n_rep, D)
+    err = float(((out.cpu() - oracle).abs().amax(-1) / oracle.abs().amax(-1)).max())
+    assert err < (2e-3 if dtype == torch.bfloat16 else 1e-5), err
+    # validation: numel relations and dtypes, raised before anything is launched
+    with pytest.raises(RuntimeError, match="k_packed size"):
+        native.decode_attention(qd, t["k_packed"][:, :-1].contiguous(), t["k_scales"], t["k_zeros"], t["v_packed"], t["v_scales"],
+                                t["v_zeros"], t["k_res"], t["v_res"], state[0], state[1], state[2], out, G)
+    with pytest.raises(RuntimeError, match="must be on cuda"):
+        native.decode_attention(qd.cpu(), quant_len=state[0], res_start=state[1], res_len=state[2], out=out, group_size=G, **t)
+    with pytest.raises(RuntimeError, match="n_new, head_dim"):
+        native.append_and_flush(kc[:, :4, : D // 2], vc[:, :4, : D // 2], quant_len=state[0], res_start=state[1],
+                                res_len=state[2], group_size=G, **t)
