@@ -202,6 +202,17 @@ int kivi_decode_attention(const kivi_layer* layer, int64_t quant_len, int res_st
                           int n_rep, float sm_scale, void* workspace, size_t workspace_bytes,
                           int num_splits, int path, void* stream);
 
+/* Same as kivi_decode_attention, and also writes lse_out[num_units][n_rep]
+ * (fp32): the natural logarithm of the sum over all attended tokens of
+ * exp(q.k * sm_scale).  With it, outputs computed over disjoint token ranges of
+ * one sequence (a history sharded across GPUs, or a cache attended in pieces)
+ * combine exactly: out = sum_i out_i * exp(lse_i - LSE), LSE = log sum_i exp(lse_i).
+ * No counterpart in the reference.  The cache must hold at least one token. */
+int kivi_decode_attention_lse(const kivi_layer* layer, int64_t quant_len, int res_start,
+                              int res_len, const void* q, int q_dtype, void* out, int out_dtype,
+                              float* lse_out, int n_rep, float sm_scale, void* workspace,
+                              size_t workspace_bytes, int num_splits, int path, void* stream);
+
 /* Decode attention for callers that cannot allocate device memory.
  *
  * No counterpart in the reference.  Some hosts of this library may not call

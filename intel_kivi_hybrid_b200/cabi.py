@@ -61,6 +61,8 @@ SIGNATURES = {
                                              _int, _int, _vp]),
     "kivi_decode_attention": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _int, _vp, _int, _int, _f,
                                      _vp, _c.c_size_t, _int, _int, _vp]),
+    "kivi_decode_attention_lse": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _int, _vp, _int, _vp, _int, _f,
+                                         _vp, _c.c_size_t, _int, _int, _vp]),
     "kivi_decode_attention_gather": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _int, _c.POINTER(PeerGatherDesc),
                                             _int, _int, _f, _vp, _c.c_size_t, _int, _int, _vp]),
     "kivi_peer_alloc": (_int, [_c.c_size_t, _c.POINTER(_vp), _c.c_char_p]),
@@ -239,6 +241,19 @@ class LayerStore:
                                          q.data_ptr(), _dt(q), out.data_ptr(), _dt(out), n_rep, float(sm_scale),
                                          ws.data_ptr(), ws.numel(), num_splits, path, _stream()))
         return out
+
+    def attention_lse(self, q, n_rep=None, sm_scale=0.0, num_splits=0, path=ATTN_AUTO, out_dtype=None):
+        """attention() plus the natural-log sum of exponentials per (unit, head):
+        returns (out [like q], lse [num_units, n_rep] fp32)."""
+        _dev(q)
+        n_rep = n_rep or q.numel() // (self.num_units * self.D)
+        out = torch.empty(q.shape, dtype=out_dtype or q.dtype, device=q.device)
+        lse = torch.empty(self.num_units, n_rep, dtype=torch.float32, device=q.device)
+        ws = self.workspace(n_rep, num_splits)
+        _check(lib.kivi_decode_attention_lse(_c.byref(self.c), self.quant_len, self.res_start, self.res_len,
+                                             q.data_ptr(), _dt(q), out.data_ptr(), _dt(out), lse.data_ptr(), n_rep,
+                                             float(sm_scale), ws.data_ptr(), ws.numel(), num_splits, path, _stream()))
+        return out, lse
 
     def attention_gather(self, q, desc: "PeerGatherDesc", out_dtype, n_rep, sm_scale=0.0, num_splits=0, path=ATTN_AUTO):
         """kivi_decode_attention_gather: the output rows of this store's units go

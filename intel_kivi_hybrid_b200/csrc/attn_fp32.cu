@@ -249,7 +249,8 @@ namespace {
 // index = (u*n_rep + h)*D + d of the output.
 template <typename Sink>
 __device__ __forceinline__ void merge_body(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                           int n_splits, int D, float* w_s, float* red_s, const Sink& sink) {
+                                           int n_splits, int D, float* w_s, float* red_s, const Sink& sink,
+                                           float* __restrict__ lse = nullptr) {
     const int u = blockIdx.x, h = blockIdx.y, nrep = gridDim.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int64_t row0 = (int64_t)u * n_splits * nrep + h;   // + s*nrep
@@ -281,6 +282,8 @@ __device__ __forceinline__ void merge_body(const float* __restrict__ part_o, con
     den = 0.0f;
     for (int w = 0; w < nwarps; ++w) den += red_s[4 + w];
     const float inv = 1.0f / den;
+    // natural-log sum of exponentials of the scaled scores (M and den live in the log2 domain)
+    if (lse != nullptr && threadIdx.x == 0) lse[(int64_t)u * nrep + h] = (M + log2f(den)) * 0.6931471805599453f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
         int s = 0;
@@ -305,10 +308,10 @@ struct LocalSink {
 
 __global__ void __launch_bounds__(128)
 merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                    void* __restrict__ out, int out_dtype, int n_splits, int D) {
+                    void* __restrict__ out, int out_dtype, int n_splits, int D, float* __restrict__ lse) {
     extern __shared__ float w_s[];                   // [n_splits] weights
     __shared__ float red_s[8];
-    merge_body(part_o, part_ml, n_splits, D, w_s, red_s, LocalSink{out, out_dtype});
+    merge_body(part_o, part_ml, n_splits, D, w_s, red_s, LocalSink{out, out_dtype}, lse);
 }
 
 // ---- merge + all-gather over peer memory -------------------------------------------
@@ -377,7 +380,7 @@ int gather_fault_word(int* out) {
 // merge of the split partials into `out`, or (gather != nullptr) into every
 // rank's gathered buffer; queued behind the attention kernel with programmatic
 // stream serialization, so its launch latency overlaps that kernel's tail
-int run_merge(const float* part_o, const float* part_ml, void* out, const kivi_peer_gather* gather,
+int run_merge(const float* part_o, const float* part_ml, void* out, const kivi_peer_gather* gather, float* lse,
               int out_dtype, int num_units, int n_rep, int n_splits, int D, cudaStream_t st) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)num_units, (unsigned)n_rep);
@@ -393,7 +396,7 @@ int run_merge(const float* part_o, const float* part_ml, void* out, const kivi_p
         kivi_peer_gather g = *gather;
         KIVI_CUDA_OK(cudaLaunchKernelEx(&cfg, merge_gather_kernel, part_o, part_ml, g, out_dtype, n_splits, D));
     } else {
-        KIVI_CUDA_OK(cudaLaunchKernelEx(&cfg, merge_splits_kernel, part_o, part_ml, out, out_dtype, n_splits, D));
+        KIVI_CUDA_OK(cudaLaunchKernelEx(&cfg, merge_splits_kernel, part_o, part_ml, out, out_dtype, n_splits, D, lse));
     }
     return KIVI_OK;
 }

@@ -53,7 +53,7 @@ int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_
                  int n_res_splits, int res_chunk, float* part_o, float* part_ml, cudaStream_t st);
 int attn_mma_fault_word(int* out);
 int gather_fault_word(int* out);
-int run_merge(const float* part_o, const float* part_ml, void* out, const kivi_peer_gather* gather,
+int run_merge(const float* part_o, const float* part_ml, void* out, const kivi_peer_gather* gather, float* lse,
               int out_dtype, int num_units, int n_rep, int n_splits, int D, cudaStream_t st);
 
 }  // namespace kivi
@@ -190,7 +190,7 @@ static int plan_splits_mma(int num_units, int64_t n_groups, int requested, int n
 
 static int decode_attention_impl(const kivi_layer* L, int64_t quant_len, int res_start,
                                  int res_len, const void* q, int q_dtype, void* out,
-                                 const kivi_peer_gather* gather, int out_dtype,
+                                 const kivi_peer_gather* gather, float* lse, int out_dtype,
                                  int n_rep, float sm_scale, void* workspace, size_t workspace_bytes,
                                  int num_splits, int path, void* stream) {
     if (int rc = validate_layer(L)) return rc;
@@ -236,7 +236,7 @@ static int decode_attention_impl(const kivi_layer* L, int64_t quant_len, int res
         ? run_attn_mma(L, quant_len, res_start, res_len, q, q_dtype, n_rep, scale_log2, nq_splits, gps, n_res_splits, res_chunk, part_o, part_ml, st)
         : run_attn_fp32(L, quant_len, res_start, res_len, q, q_dtype, n_rep, scale_log2, nq_splits, gps, n_splits, part_o, part_ml, st);
     if (rc) return rc;
-    if (int rc2 = run_merge(part_o, part_ml, out, gather, out_dtype, L->num_units, n_rep, n_splits, D, st)) return rc2;
+    if (int rc2 = run_merge(part_o, part_ml, out, gather, lse, out_dtype, L->num_units, n_rep, n_splits, D, st)) return rc2;
     note_launches(2);
     return KIVI_OK;
 }
@@ -245,7 +245,17 @@ extern "C" int kivi_decode_attention(const kivi_layer* L, int64_t quant_len, int
                                      int res_len, const void* q, int q_dtype, void* out, int out_dtype,
                                      int n_rep, float sm_scale, void* workspace, size_t workspace_bytes,
                                      int num_splits, int path, void* stream) {
-    return decode_attention_impl(L, quant_len, res_start, res_len, q, q_dtype, out, nullptr, out_dtype, n_rep,
+    return decode_attention_impl(L, quant_len, res_start, res_len, q, q_dtype, out, nullptr, nullptr, out_dtype, n_rep,
+                                 sm_scale, workspace, workspace_bytes, num_splits, path, stream);
+}
+
+extern "C" int kivi_decode_attention_lse(const kivi_layer* L, int64_t quant_len, int res_start,
+                                         int res_len, const void* q, int q_dtype, void* out, int out_dtype,
+                                         float* lse_out, int n_rep, float sm_scale, void* workspace,
+                                         size_t workspace_bytes, int num_splits, int path, void* stream) {
+    KIVI_REQUIRE(lse_out != nullptr, "lse_out is null");
+    KIVI_REQUIRE(quant_len + res_len > 0, "the log-sum-exp of an empty cache is undefined");
+    return decode_attention_impl(L, quant_len, res_start, res_len, q, q_dtype, out, nullptr, lse_out, out_dtype, n_rep,
                                  sm_scale, workspace, workspace_bytes, num_splits, path, stream);
 }
 
@@ -262,7 +272,7 @@ extern "C" int kivi_decode_attention_gather(const kivi_layer* L, int64_t quant_l
     KIVI_REQUIRE(gather->epoch != 0, "epoch starts at 1");
     for (int r = 0; r < gather->world; ++r)
         KIVI_REQUIRE(gather->out_ptrs[r] != nullptr && gather->flag_ptrs[r] != nullptr, "buffer or flag pointer of rank %d is null", r);
-    return decode_attention_impl(L, quant_len, res_start, res_len, q, q_dtype, nullptr, gather, out_dtype, n_rep,
+    return decode_attention_impl(L, quant_len, res_start, res_len, q, q_dtype, nullptr, gather, nullptr, out_dtype, n_rep,
                                  sm_scale, workspace, workspace_bytes, num_splits, path, stream);
 }
 

@@ -15,7 +15,7 @@ from typing import Tuple
 
 import torch
 
-__all__ = ["unit_partition", "all_gather_units", "PeerGather"]
+__all__ = ["unit_partition", "all_gather_units", "PeerGather", "merge_token_shards"]
 
 
 def unit_partition(n_units: int, rank: int, world: int) -> Tuple[int, int]:
@@ -46,6 +46,18 @@ def all_gather_units(local: torch.Tensor, n_units: int, rank: int, world: int, g
     buf = torch.empty((world * biggest,) + tuple(tail), dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(buf, padded, group=group)
     return torch.cat([buf[r * biggest: r * biggest + (b - a)] for r, (a, b) in enumerate(sizes)], dim=0)
+
+
+def merge_token_shards(outs: torch.Tensor, lses: torch.Tensor) -> torch.Tensor:
+    """Combine attention outputs computed over disjoint token ranges of the same
+    sequences (sequence sharding: every rank holds a slice of each unit's
+    history and runs LayerStore.attention_lse on it).
+    outs [n_shards, ..., D], lses [n_shards, ...] (natural-log sums of
+    exponentials) -> [..., D] in fp32:  sum_i out_i * exp(lse_i - LSE)."""
+    lses = lses.float()
+    total = torch.logsumexp(lses, dim=0, keepdim=True)
+    w = torch.exp(lses - total).unsqueeze(-1)
+    return (outs.float() * w).sum(dim=0)
 
 
 class PeerGather:

@@ -390,3 +390,44 @@ def test_full_size_config4_prefill_properties(cabi):
         assert torch.equal(one.k_scales[0, :ng].cpu(), torch.stack(oc.k_scales, dim=2).reshape(ng, D))
         assert torch.equal(st.k_scales[u, :ng].cpu(), one.k_scales[0, :ng].cpu())
         assert torch.equal(st.v_codes[u, :ql].cpu(), one.v_codes[0, :ql].cpu())
+
+
+@pytest.mark.parametrize("dtype,path", [(torch.bfloat16, "mma"), (torch.float32, "fp32")])
+def test_attention_lse_combines_token_shards(cabi, dtype, path):
+    """kivi_decode_attention_lse: the log-sum-exp equals the oracle's, and two
+    stores holding disjoint token ranges of the same sequences (sequence
+    sharding on one GPU) combine into the single-store result."""
+    from intel_kivi_hybrid_b200.parallel import merge_token_shards
+    B, H, n_rep, D, G, R = 1, 4, 4, 128, 32, 128
+    n_quant, n_res, n1 = 1024, 77, 384
+    T, U = n_quant + n_res, B * H
+    K = ko.make_keys(B, H, T, D, seed=13)
+    V = ko.make_values(B, H, T, D, seed=13)
+    q = ko.make_queries(B, H * n_rep, D, seed=13)
+    if dtype == torch.bfloat16:
+        K, V, q = K.bfloat16().float(), V.bfloat16().float(), q.bfloat16().float()
+    kc, vc = units(K).cuda().to(dtype), units(V).cuda().to(dtype)
+    qd = q.reshape(U, n_rep, D).cuda().to(dtype)
+    p = cabi.ATTN_MMA if path == "mma" else cabi.ATTN_FP32
+    whole = cabi.LayerStore(U, D, G, R, n_quant, dtype, "cuda")
+    cabi.load_state(whole, kc, vc, n_quant)
+    out_w, lse_w = whole.attention_lse(qd, n_rep=n_rep, path=p, out_dtype=torch.float32)
+    assert torch.equal(out_w, whole.attention(qd, n_rep=n_rep, path=p, out_dtype=torch.float32))
+    # oracle log-sum-exp over the served cache
+    kd, vd = whole.materialize()
+    s = torch.einsum("uhd,utd->uht", qd.double().cpu(), kd.double().cpu()) * D ** -0.5
+    assert torch.allclose(lse_w.cpu().double(), torch.logsumexp(s, -1), atol=2e-3 if dtype == torch.bfloat16 else 2e-5)
+    # shard 0: the first n1 tokens, all quantized; shard 1: the rest with the ring
+    s0 = cabi.LayerStore(U, D, G, R, n1, dtype, "cuda")
+    cabi.load_state(s0, kc[:, :n1], vc[:, :n1], n1)
+    s1 = cabi.LayerStore(U, D, G, R, n_quant - n1, dtype, "cuda")
+    cabi.load_state(s1, kc[:, n1:], vc[:, n1:], n_quant - n1)
+    o0, l0 = s0.attention_lse(qd, n_rep=n_rep, path=p, out_dtype=torch.float32)
+    o1, l1 = s1.attention_lse(qd, n_rep=n_rep, path=p, out_dtype=torch.float32)
+    merged = merge_token_shards(torch.stack([o0, o1]), torch.stack([l0, l1]))
+    tol = TOL_BF16 if dtype == torch.bfloat16 else TOL_F32
+    assert rel_err(merged, out_w) < tol
+    ref = ko.kivi_decode_attention(q, K, V, n_quant, G, "half_away", dtype=torch.float64).float().reshape(U, n_rep, D)
+    assert rel_err(merged, ref) < tol
+    with pytest.raises(RuntimeError, match="empty cache"):
+        cabi.LayerStore(U, D, G, R, 64, dtype, "cuda").attention_lse(qd, n_rep=n_rep)

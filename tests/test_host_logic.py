@@ -193,3 +193,22 @@ def test_drop_in_surface():
     x = torch.zeros(64)
     with pytest.raises(RuntimeError, match="must be on cuda"):
         _C.quant_dequant_roundtrip_keys(input=x, output=torch.zeros(64), group_size=32)
+
+
+def test_merge_token_shards_equals_attention_over_the_whole_sequence():
+    """Outputs over disjoint token ranges + their log-sum-exps combine into the
+    attention over the union (the host side of sequence sharding)."""
+    from intel_kivi_hybrid_b200.parallel import merge_token_shards
+    torch.manual_seed(3)
+    U, H, D, T = 3, 4, 16, 50
+    q = torch.randn(U, H, D, dtype=torch.float64)
+    k = torch.randn(U, T, D, dtype=torch.float64)
+    v = torch.randn(U, T, D, dtype=torch.float64)
+    s = torch.einsum("uhd,utd->uht", q, k) * D ** -0.5
+    whole = torch.einsum("uht,utd->uhd", torch.softmax(s, -1), v)
+    outs, lses = [], []
+    for a, b in ((0, 7), (7, 31), (31, T)):
+        outs.append(torch.einsum("uht,utd->uhd", torch.softmax(s[..., a:b], -1), v[:, a:b]))
+        lses.append(torch.logsumexp(s[..., a:b], -1))
+    got = merge_token_shards(torch.stack(outs).float(), torch.stack(lses).float())
+    assert got.dtype == torch.float32 and torch.allclose(got.double(), whole, atol=1e-6)
