@@ -557,37 +557,70 @@ ring_append_kernel(TokenSource src, void* __restrict__ k_ring, void* __restrict_
 }
 
 // fp32 [units][T][D] keys and values: dequantized history then the window.
+// A thread produces channels 4q .. 4q+3 of one token for both tensors: the four
+// key codes sit in one aligned 32-bit word of the key block (the block's channel
+// permutation keeps the two low bits), the four value codes in one byte, scales
+// and zeros come as one 128-bit load (keys) or one scalar (values), and the
+// results leave as two 128-bit stores.
 __global__ void __launch_bounds__(256)
 materialize_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
                    float* __restrict__ k_out, float* __restrict__ v_out) {
-    const int D = L.head_dim, G = L.group_size, Q = G / 4, W = D < 64 ? D : 64, ng = D / G;
+    const int D = L.head_dim, G = L.group_size, Q = G / 4, W = D < 64 ? D : 64, ng = D / G, D4 = D / 4;
     const int u = blockIdx.y;
     const int64_t T = quant_len + res_len;
     const int64_t max_groups = L.max_tokens / G;
-    const int64_t n = T * D;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
-         i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t t = i / D;
-        const int d = (int)(i % D);
-        float kv, vv;
+    const uint32_t n4 = (uint32_t)(T * D4);             // the host checks that this fits 31 bits
+    const bool vec_out = ((reinterpret_cast<uintptr_t>(k_out) | reinterpret_cast<uintptr_t>(v_out)) & 15u) == 0;
+    const bool vec_meta = ((reinterpret_cast<uintptr_t>(L.k_scales) | reinterpret_cast<uintptr_t>(L.k_zeros)) & 15u) == 0;
+    const bool word_codes = (reinterpret_cast<uintptr_t>(L.k_codes) & 3u) == 0;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+        const uint32_t t = i / (uint32_t)D4;             // 32-bit index arithmetic: no 64-bit divisions per element
+        const int d = (int)(i - t * (uint32_t)D4) * 4;
+        float kv[4], vv[4];
         if (t < quant_len) {
-            const int64_t g = t / G;
-            const int tt = (int)(t % G);
-            const int j = tt / 4, e = tt % 4;
+            const uint32_t g = t / (uint32_t)G;
+            const int tt = (int)(t - g * (uint32_t)G);
+            const int j = tt >> 2, e = tt & 3;
             const int64_t gb = (int64_t)u * max_groups + g;
-            uint32_t kb = L.k_codes[gb * (D * Q) + kblock_offset(d, j, Q, W)];
-            kv = dequant((float)((kb >> (2 * e)) & 3u), L.k_scales[gb * D + d], L.k_zeros[gb * D + d]);
-            uint32_t vb = L.v_codes[(int64_t)u * L.max_tokens * (D / 4) + vcode_offset(t, d / 4, D, G)];
+            const uint8_t* kc = L.k_codes + gb * (D * Q) + kblock_offset(d, j, Q, W);      // channels d..d+3: 4 adjacent bytes
+            const uint32_t kw = word_codes ? *reinterpret_cast<const uint32_t*>(kc)
+                                           : (uint32_t)kc[0] | ((uint32_t)kc[1] << 8) | ((uint32_t)kc[2] << 16) | ((uint32_t)kc[3] << 24);
+            float ks[4], kz[4];
+            if (vec_meta) {
+                const float4 s4 = *reinterpret_cast<const float4*>(L.k_scales + gb * D + d);
+                const float4 z4 = *reinterpret_cast<const float4*>(L.k_zeros + gb * D + d);
+                ks[0] = s4.x; ks[1] = s4.y; ks[2] = s4.z; ks[3] = s4.w;
+                kz[0] = z4.x; kz[1] = z4.y; kz[2] = z4.z; kz[3] = z4.w;
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) { ks[c] = L.k_scales[gb * D + d + c]; kz[c] = L.k_zeros[gb * D + d + c]; }
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                kv[c] = dequant((float)((kw >> (8 * c + 2 * e)) & 3u), ks[c], kz[c]);
+            const uint32_t vb = L.v_codes[(int64_t)u * L.max_tokens * D4 + vcode_offset(t, d >> 2, D, G)];
             const int64_t mi = (int64_t)u * L.max_tokens * ng + vmeta_index(t, d / G, D, G);
-            vv = dequant((float)((vb >> (2 * (d % 4))) & 3u), L.v_scales[mi], L.v_zeros[mi]);
+            const float vs = L.v_scales[mi], vz = L.v_zeros[mi];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) vv[c] = dequant((float)((vb >> (2 * c)) & 3u), vs, vz);
         } else {
-            const int slot = (int)((res_start + (t - quant_len)) % L.residual_cap);
+            int slot = res_start + (int)(t - quant_len);
+            if (slot >= L.residual_cap) slot -= L.residual_cap;
             const int64_t o = ((int64_t)u * L.residual_cap + slot) * D + d;
-            kv = load_as_float(L.k_res, L.res_dtype, o);
-            vv = load_as_float(L.v_res, L.res_dtype, o);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                kv[c] = load_as_float(L.k_res, L.res_dtype, o + c);
+                vv[c] = load_as_float(L.v_res, L.res_dtype, o + c);
+            }
         }
-        k_out[(int64_t)u * n + i] = kv;
-        v_out[(int64_t)u * n + i] = vv;
+        const int64_t o = (int64_t)u * T * D + (int64_t)i * 4;
+        if (vec_out) {
+            __stcs(reinterpret_cast<float4*>(k_out + o), make_float4(kv[0], kv[1], kv[2], kv[3]));
+            __stcs(reinterpret_cast<float4*>(v_out + o), make_float4(vv[0], vv[1], vv[2], vv[3]));
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) { k_out[o + c] = kv[c]; v_out[o + c] = vv[c]; }
+        }
     }
 }
 
@@ -818,10 +851,11 @@ extern "C" int kivi_cache_materialize(const kivi_layer* L, int64_t quant_len, in
     if (int rc = validate_layer(L)) return rc;
     if (int rc = validate_state(L, quant_len, res_start, res_len)) return rc;
     KIVI_REQUIRE(k_out && v_out, "output pointers are null");
-    const int64_t n = (quant_len + res_len) * L->head_dim;
+    const int64_t n = (quant_len + res_len) * (L->head_dim / 4);
     if (n == 0) { note_launches(0); return KIVI_OK; }
+    KIVI_REQUIRE(n < (1ll << 31), "too many tokens for one materialize call: %lld", (long long)(quant_len + res_len));
     unsigned bx = (unsigned)((n + 255) / 256);
-    if (bx > 1024) bx = 1024;
+    if (bx > 4096) bx = 4096;
     dim3 grid(bx, (unsigned)L->num_units);
     materialize_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(*L, quant_len, res_start, res_len, k_out, v_out);
     KIVI_LAUNCH_OK();
