@@ -216,13 +216,36 @@ def run_ours(args, wl):
     # the exchange of a step: an NCCL all-gather after the kernels, or the
     # attention's last kernel storing its rows into every rank's buffer itself
     pg = None
-    if world > 1 and args.gather == "peer":
+    if world > 1 and args.gather in ("peer", "auto"):
         from intel_kivi_hybrid_b200.parallel import PeerGather
         try:                                   # raises on every rank or on none
             pg = PeerGather(world * U, n_rep, D, dtype, rank, world)
         except RuntimeError as exc:
             if rank == 0:
                 print(f"[bench] {exc}; falling back to the NCCL all-gather", file=sys.stderr)
+        if pg is not None:
+            # self-check before anything is timed: two fused steps (both halves of the
+            # double buffer) must reproduce the NCCL all-gather bit for bit on every
+            # rank with no wait having run out; otherwise all ranks use NCCL
+            ok = 1
+            try:
+                stores[0].attention(q, out=out, n_rep=n_rep, path=path, num_splits=args.splits)
+                dist.all_gather_into_tensor(gathered, out)
+                for _ in range(2):
+                    stores[0].attention_gather(q, pg.descriptor(), dtype, n_rep, path=path, num_splits=args.splits)
+                    torch.cuda.synchronize()
+                    ok &= int(torch.equal(pg.gathered(), gathered))
+                ok &= int(cabi.device_fault() == 0)
+            except RuntimeError as exc:
+                print(f"[bench] rank {rank}: fused gather failed its self-check: {exc}", file=sys.stderr)
+                ok = 0
+            t_ok = torch.tensor([ok], device=dev)
+            dist.all_reduce(t_ok, op=dist.ReduceOp.MIN)
+            if int(t_ok.item()) == 0:
+                if rank == 0:
+                    print("[bench] fused gather failed its self-check; using the NCCL all-gather", file=sys.stderr)
+                pg.close()
+                pg = None
 
     def attend(store):
         if pg is not None:
@@ -441,8 +464,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--gather", default="nccl", choices=["nccl", "peer"],
-                    help="N>1: how the attention outputs are all-gathered")
+    ap.add_argument("--gather", default="auto", choices=["auto", "nccl", "peer"],
+                    help="N>1: how the attention outputs are all-gathered: by NCCL after the kernels, or by the "
+                         "attention's last kernel through peer memory (auto = the latter if it passes a self-check)")
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["cfg4"])
     ap.add_argument("--path", default="auto", choices=["auto", "fp32", "mma"])
     ap.add_argument("--splits", type=int, default=0)
