@@ -563,7 +563,7 @@ ring_append_kernel(TokenSource src, void* __restrict__ k_ring, void* __restrict_
 // and zeros come as one 128-bit load (keys) or one scalar (values), and the
 // results leave as two 128-bit stores.
 __global__ void __launch_bounds__(256)
-materialize_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
+materialize_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len, int64_t t_begin,
                    float* __restrict__ k_out, float* __restrict__ v_out) {
     const int D = L.head_dim, G = L.group_size, Q = G / 4, W = D < 64 ? D : 64, ng = D / G, D4 = D / 4;
     const int u = blockIdx.y;
@@ -573,7 +573,8 @@ materialize_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
     const bool vec_out = ((reinterpret_cast<uintptr_t>(k_out) | reinterpret_cast<uintptr_t>(v_out)) & 15u) == 0;
     const bool vec_meta = ((reinterpret_cast<uintptr_t>(L.k_scales) | reinterpret_cast<uintptr_t>(L.k_zeros)) & 15u) == 0;
     const bool word_codes = (reinterpret_cast<uintptr_t>(L.k_codes) & 3u) == 0;
-    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+    for (uint32_t i = (uint32_t)t_begin * (uint32_t)D4 + blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+         i += gridDim.x * blockDim.x) {                  // tokens t_begin .. T-1
         const uint32_t t = i / (uint32_t)D4;             // 32-bit index arithmetic: no 64-bit divisions per element
         const int d = (int)(i - t * (uint32_t)D4) * 4;
         float kv[4], vv[4];
@@ -620,6 +621,75 @@ materialize_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
         } else {
 #pragma unroll
             for (int c = 0; c < 4; ++c) { k_out[o + c] = kv[c]; v_out[o + c] = vv[c]; }
+        }
+    }
+}
+
+// Dequantized history for D = 128, G = 32: one warp per (unit, token group).
+// Keys: lane l owns channels 4l .. 4l+3; its scales and zeros are two 128-bit
+// loads for the whole group, each of its eight code words holds those channels
+// for four tokens, and every store instruction of the warp writes one complete
+// 512-byte token row.  Values: the lane dequantizes the eight words of the value
+// block it loaded with two 128-bit loads (word (gd, kappa, r, c): natural byte
+// 8*gd + r of tokens 16*kappa + 4*c + n); a store instruction writes 128-byte
+// pieces of four token rows.  grid = (ceil(groups / 8), units), 8 warps.
+__global__ void __launch_bounds__(256)
+materialize_groups_kernel(kivi_layer L, int64_t n_groups, int64_t T,
+                          float* __restrict__ k_out, float* __restrict__ v_out) {
+    constexpr int D = 128, G = 32;
+    const int u = blockIdx.y, lane = threadIdx.x & 31;
+    const int64_t g = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (g >= n_groups) return;
+    const int64_t max_groups = L.max_tokens / G;
+    const int64_t gb = (int64_t)u * max_groups + g;
+    float* ko = k_out + ((int64_t)u * T + g * G) * D;
+    float* vo = v_out + ((int64_t)u * T + g * G) * D;
+    {   // ---- keys
+        const int d = 4 * lane;
+        const float4 s4 = *reinterpret_cast<const float4*>(L.k_scales + gb * D + d);
+        const float4 z4 = *reinterpret_cast<const float4*>(L.k_zeros + gb * D + d);
+        const uint8_t* kc = L.k_codes + gb * (D * 8) + kblock_offset(d, 0, 8, 64);
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w[j] = *reinterpret_cast<const uint32_t*>(kc + j * 64);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float4 r;
+                r.x = dequant((float)((w[j] >> (2 * e)) & 3u), s4.x, z4.x);
+                r.y = dequant((float)((w[j] >> (8 + 2 * e)) & 3u), s4.y, z4.y);
+                r.z = dequant((float)((w[j] >> (16 + 2 * e)) & 3u), s4.z, z4.z);
+                r.w = dequant((float)((w[j] >> (24 + 2 * e)) & 3u), s4.w, z4.w);
+                __stcs(reinterpret_cast<float4*>(ko + (4 * j + e) * D + d), r);
+            }
+    }
+    {   // ---- values
+        const uint32_t* vb = reinterpret_cast<const uint32_t*>(L.v_codes + ((int64_t)u * L.max_tokens + g * G) * (D / 4));
+        const float* vs = L.v_scales + ((int64_t)u * L.max_tokens + g * G) * 4;
+        const float* vz = L.v_zeros + ((int64_t)u * L.max_tokens + g * G) * 4;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const uint4 q4 = *reinterpret_cast<const uint4*>(vb + half * 128 + 4 * lane);
+            const uint32_t w[4] = {q4.x, q4.y, q4.z, q4.w};
+            // word 128*half + 4*lane + c: gd = 2*half + lane/16, kappa = (lane/8)%2, r = lane%8
+            const int gd = 2 * half + (lane >> 4), kap = (lane >> 3) & 1, r = lane & 7;
+            const int quad = 8 * gd + r;                                 // channels 4*quad .. 4*quad+3
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int n = 0; n < 4; ++n) {
+                    const int tt = 16 * kap + 4 * c + n;                 // token inside the group
+                    const int row = 16 * kap + 4 * n + c;                // its scale / zero row
+                    const float s = vs[row * 4 + gd], z = vz[row * 4 + gd];
+                    const uint32_t b = (w[c] >> (8 * n)) & 0xffu;
+                    float4 o;
+                    o.x = dequant((float)(b & 3u), s, z);
+                    o.y = dequant((float)((b >> 2) & 3u), s, z);
+                    o.z = dequant((float)((b >> 4) & 3u), s, z);
+                    o.w = dequant((float)(b >> 6), s, z);
+                    __stcs(reinterpret_cast<float4*>(vo + tt * D + 4 * quad), o);
+                }
         }
     }
 }
@@ -854,12 +924,31 @@ extern "C" int kivi_cache_materialize(const kivi_layer* L, int64_t quant_len, in
     const int64_t n = (quant_len + res_len) * (L->head_dim / 4);
     if (n == 0) { note_launches(0); return KIVI_OK; }
     KIVI_REQUIRE(n < (1ll << 31), "too many tokens for one materialize call: %lld", (long long)(quant_len + res_len));
-    unsigned bx = (unsigned)((n + 255) / 256);
-    if (bx > 4096) bx = 4096;
-    dim3 grid(bx, (unsigned)L->num_units);
-    materialize_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(*L, quant_len, res_start, res_len, k_out, v_out);
-    KIVI_LAUNCH_OK();
-    note_launches(1);
+    cudaStream_t st = (cudaStream_t)stream;
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    int launches = 0;
+    int64_t t_begin = 0;
+    // whole groups of the usual layer shape take the warp-per-group kernel; the
+    // ring (and every other shape) the per-element one
+    if (L->head_dim == 128 && L->group_size == 32 && quant_len > 0 && al16(k_out) && al16(v_out) && al16(L->k_codes) &&
+        al16(L->k_scales) && al16(L->k_zeros) && al16(L->v_codes)) {
+        const int64_t n_groups = quant_len / 32;
+        dim3 grid((unsigned)((n_groups + 7) / 8), (unsigned)L->num_units);
+        materialize_groups_kernel<<<grid, 256, 0, st>>>(*L, n_groups, quant_len + res_len, k_out, v_out);
+        KIVI_LAUNCH_OK();
+        ++launches;
+        t_begin = quant_len;
+    }
+    const int64_t rest = (quant_len + res_len - t_begin) * (L->head_dim / 4);
+    if (rest > 0) {
+        unsigned bx = (unsigned)((rest + 255) / 256);
+        if (bx > 4096) bx = 4096;
+        dim3 grid(bx, (unsigned)L->num_units);
+        materialize_kernel<<<grid, 256, 0, st>>>(*L, quant_len, res_start, res_len, t_begin, k_out, v_out);
+        KIVI_LAUNCH_OK();
+        ++launches;
+    }
+    note_launches(launches);
     return KIVI_OK;
 }
 
