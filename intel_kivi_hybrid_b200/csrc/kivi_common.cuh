@@ -134,6 +134,89 @@ __device__ __forceinline__ void store_from_float(void* p, int dtype, int64_t i, 
     else reinterpret_cast<float*>(p)[i] = v;
 }
 
+// ---- groups kept in registers as loaded -----------------------------------------
+// Two neighbouring elements kept as loaded (one 32-bit word for bf16, so a
+// lane's group costs half the registers), widened to fp32 only where used.
+// Minimum and maximum of bf16 pairs run on both halves at once; they are exact
+// in any format, and which zero wins a tie between -0 and +0 does not change a
+// code or a dequantized value's numeric value.
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+    using raw = float2;
+    using acc = float2;
+    __device__ static raw load(const float* p) { return __ldg(reinterpret_cast<const float2*>(p)); }
+    __device__ static void widen(raw w, float& a, float& b) { a = w.x; b = w.y; }
+    __device__ static acc first(raw w) { return w; }
+    __device__ static acc lo(acc m, raw w) { return make_float2(fminf(m.x, w.x), fminf(m.y, w.y)); }
+    __device__ static acc hi(acc m, raw w) { return make_float2(fmaxf(m.x, w.x), fmaxf(m.y, w.y)); }
+    __device__ static void finish(acc m, float& a, float& b) { a = m.x; b = m.y; }
+};
+template <> struct Pair<__nv_bfloat16> {
+    using raw = uint32_t;
+    using acc = __nv_bfloat162;
+    __device__ static raw load(const __nv_bfloat16* p) { return __ldg(reinterpret_cast<const uint32_t*>(p)); }
+    __device__ static void widen(raw w, float& a, float& b) { a = __uint_as_float(w << 16); b = __uint_as_float(w & 0xffff0000u); }
+    __device__ static acc first(raw w) { return *reinterpret_cast<const __nv_bfloat162*>(&w); }
+    __device__ static acc lo(acc m, raw w) { return __hmin2(m, *reinterpret_cast<const __nv_bfloat162*>(&w)); }
+    __device__ static acc hi(acc m, raw w) { return __hmax2(m, *reinterpret_cast<const __nv_bfloat162*>(&w)); }
+    __device__ static void finish(acc m, float& a, float& b) { widen(*reinterpret_cast<const uint32_t*>(&m), a, b); }
+};
+
+// The 32 channels of one (token, channel group) kept as loaded: four 128-bit
+// words for bf16, eight for fp32.
+template <typename T> struct Row32;
+template <> struct Row32<float> {
+    float4 v[8];
+    __device__ void load(const float* p) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = __ldg(reinterpret_cast<const float4*>(p) + k);
+    }
+    __device__ void load_staged(const uint8_t* p) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = reinterpret_cast<const float4*>(p)[k];
+    }
+    __device__ void minmax(float& mn, float& mx) const {
+        mn = 1e30f; mx = -1e30f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            mn = fminf(fminf(mn, v[k].x), fminf(v[k].y, fminf(v[k].z, v[k].w)));
+            mx = fmaxf(fmaxf(mx, v[k].x), fmaxf(v[k].y, fmaxf(v[k].z, v[k].w)));
+        }
+    }
+    // channels 4r .. 4r+3
+    __device__ void quad(int r, float (&x)[4]) const { x[0] = v[r].x; x[1] = v[r].y; x[2] = v[r].z; x[3] = v[r].w; }
+};
+template <> struct Row32<__nv_bfloat16> {
+    uint32_t w[16];
+    __device__ void load(const __nv_bfloat16* p) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint4 t = __ldg(reinterpret_cast<const uint4*>(p) + k);
+            w[4 * k] = t.x; w[4 * k + 1] = t.y; w[4 * k + 2] = t.z; w[4 * k + 3] = t.w;
+        }
+    }
+    __device__ void load_staged(const uint8_t* p) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint4 t = reinterpret_cast<const uint4*>(p)[k];
+            w[4 * k] = t.x; w[4 * k + 1] = t.y; w[4 * k + 2] = t.z; w[4 * k + 3] = t.w;
+        }
+    }
+    __device__ void minmax(float& mn, float& mx) const {
+        using P = Pair<__nv_bfloat16>;
+        P::acc lo = P::first(w[0]), hi = P::first(w[0]);
+#pragma unroll
+        for (int k = 1; k < 16; ++k) { lo = P::lo(lo, w[k]); hi = P::hi(hi, w[k]); }
+        float a, b;
+        P::finish(lo, a, b); mn = fminf(fminf(a, b), 1e30f);
+        P::finish(hi, a, b); mx = fmaxf(fmaxf(a, b), -1e30f);
+    }
+    __device__ void quad(int r, float (&x)[4]) const {
+        Pair<__nv_bfloat16>::widen(w[2 * r], x[0], x[1]);
+        Pair<__nv_bfloat16>::widen(w[2 * r + 1], x[2], x[3]);
+    }
+};
+
 // ---- key block layout --------------------------------------------------------
 // Byte offset inside one key block of the codes of channel d, token quad j
 // (tokens 4j .. 4j+3 of the group in bits 0-1, 2-3, 4-5, 6-7; 0 <= j < Q = G/4);

@@ -208,6 +208,80 @@ group_quant_generic_kernel(const void* __restrict__ in, int in_dtype, uint8_t* _
     }
 }
 
+// bf16 input, G = 32*NR (32, 64 or 128), quantize only: one thread per group.
+// The group arrives as independent 128-bit loads and stays in registers as
+// loaded (min/max on bf16 pairs, widened only when quantized); the packed bytes
+// leave as 64- or 128-bit stores, so a warp writes contiguous runs of codes,
+// scales and zeros: no shuffles, no staging, no barrier.
+template <bool HALF_EVEN, int NR>
+__global__ void __launch_bounds__(kThreads)
+group_quant_bf16_rows_kernel(const __nv_bfloat16* __restrict__ in, uint8_t* __restrict__ packed,
+                             float* __restrict__ scales, float* __restrict__ zeros, int64_t num_groups) {
+    constexpr int G = 32 * NR;
+    const int64_t g = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (g >= num_groups) return;
+    const __nv_bfloat16* src = in + g * G;
+    Row32<__nv_bfloat16> row[NR];
+#pragma unroll
+    for (int k = 0; k < NR; ++k) row[k].load(src + 32 * k);
+    float mn = 1e30f, mx = -1e30f;
+#pragma unroll
+    for (int k = 0; k < NR; ++k) {
+        float a, b;
+        row[k].minmax(a, b);
+        mn = fminf(mn, a); mx = fmaxf(mx, b);
+    }
+    const float scale = group_scale(mn, mx);
+    const float rcp = group_rcp(scale);
+    uint32_t w[2 * NR];
+#pragma unroll
+    for (int i = 0; i < 2 * NR; ++i) w[i] = 0u;
+    if (rcp != 0.0f) {
+#pragma unroll
+        for (int k = 0; k < NR; ++k)
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                float x[4];
+                row[k].quad(r, x);
+                w[2 * k + (r >> 2)] |= pack4_magic(code_magic_rcp<HALF_EVEN>(x[0], mn, scale, rcp), code_magic_rcp<HALF_EVEN>(x[1], mn, scale, rcp),
+                                                   code_magic_rcp<HALF_EVEN>(x[2], mn, scale, rcp), code_magic_rcp<HALF_EVEN>(x[3], mn, scale, rcp))
+                                       << (8 * (r & 3));
+            }
+        if (NR == 1) {
+            *reinterpret_cast<uint2*>(packed + g * 8) = make_uint2(w[0], w[1]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < NR / 2; ++i)
+                reinterpret_cast<uint4*>(packed + g * (G / 4))[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
+    } else {
+        // a scale too large for a reciprocal (rare): plain divisions on re-read values
+        for (int b = 0; b < G / 4; ++b) {
+            float m[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) m[e] = code_magic<HALF_EVEN>(__bfloat162float(src[4 * b + e]), mn, scale, rcp);
+            packed[g * (G / 4) + b] = (uint8_t)pack4_magic(m[0], m[1], m[2], m[3]);
+        }
+    }
+    scales[g] = scale;
+    zeros[g] = mn;
+}
+
+template <int NR>
+int launch_bf16_rows(const void* in, uint8_t* packed, float* scales, float* zeros, int64_t num_groups, int rounding,
+                     cudaStream_t st) {
+    const int64_t blocks = (num_groups + kThreads - 1) / kThreads;
+    KIVI_REQUIRE(blocks <= 0x7fffffffLL, "too many groups for one launch: %lld", (long long)num_groups);
+    const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(in);
+    if (rounding == KIVI_ROUND_HALF_EVEN)
+        group_quant_bf16_rows_kernel<true, NR><<<(unsigned)blocks, kThreads, 0, st>>>(p, packed, scales, zeros, num_groups);
+    else
+        group_quant_bf16_rows_kernel<false, NR><<<(unsigned)blocks, kThreads, 0, st>>>(p, packed, scales, zeros, num_groups);
+    KIVI_LAUNCH_OK();
+    note_launches(1);
+    return KIVI_OK;
+}
+
 // One thread per packed byte -> one float4 store (dequantize_kernels.cpp:50-61).
 __global__ void __launch_bounds__(kThreads)
 group_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ scales,
@@ -285,6 +359,11 @@ int run_group_quant(const void* in, int in_dtype, uint8_t* packed, float* scales
                 default: break;
             }
         } else {
+            if (mode == 0) {
+                if (G == 32) return launch_bf16_rows<1>(in, packed, scales, zeros, num_groups, rounding, st);
+                if (G == 64) return launch_bf16_rows<2>(in, packed, scales, zeros, num_groups, rounding, st);
+                if (G == 128) return launch_bf16_rows<4>(in, packed, scales, zeros, num_groups, rounding, st);
+            }
             switch (G) {
                 case 16: return launch_fast<__nv_bfloat16, 2, 1>(in, packed, scales, zeros, rt, num_groups, rounding, mode, st);
                 case 32: return launch_fast<__nv_bfloat16, 4, 1>(in, packed, scales, zeros, rt, num_groups, rounding, mode, st);
