@@ -352,7 +352,8 @@ extern "C" int kivi_decode_attention_noalloc(const kivi_layer* L, int64_t quant_
                                          sm_scale, scratch, (size_t)KIVI_NOALLOC_SCRATCH_BYTES, num_splits, path, stream);
     if (rc == KIVI_ERR_INVALID_ARGUMENT && strstr(g_err, "workspace too small") != nullptr) {
         char detail[256];
-        snprintf(detail, sizeof(detail), "%s", g_err);
+        strncpy(detail, g_err, sizeof(detail) - 1);          // the message above is far shorter than this
+        detail[sizeof(detail) - 1] = 0;
         set_error("problem too large for the built-in scratch of kivi_decode_attention_noalloc (%u bytes): %s; "
                   "pass a smaller num_splits or call kivi_decode_attention with your own workspace",
                   (unsigned)KIVI_NOALLOC_SCRATCH_BYTES, detail);
