@@ -462,6 +462,68 @@ def run_quantize(args):
     print(json.dumps(line))
 
 
+def run_operators(args):
+    """--workload ops: the flat-group operators of the reference's module
+    (quantize / dequantize / fused round trip on 2^28 elements, G=32 and 128,
+    fp32 and bf16 input) and the dense-cache materialisation behind
+    get_full_cache (64 units x 8288 tokens), CUDA-event medians."""
+    from intel_kivi_hybrid_b200 import cabi
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    N = 1 << 28
+
+    def timed(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+        ev[0].record()
+        for i in range(args.steps):
+            fn()
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        return statistics.median(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
+
+    res = {}
+    for name, dtype, eb in (("f32", torch.float32, 4), ("bf16", torch.bfloat16, 2)):
+        x = torch.randn(N, device=dev, generator=torch.Generator(device=dev).manual_seed(5)).to(dtype)
+        out = torch.empty(N, device=dev)
+        for G in (32, 128):
+            packed = torch.empty(N // 4, dtype=torch.uint8, device=dev)
+            sc, ze = torch.empty(N // G, device=dev), torch.empty(N // G, device=dev)
+            ms = timed(lambda: cabi.quantize_keys(x, packed, sc, ze, G))
+            res[f"quantize_{name}_G{G}"] = {"ms": ms, "gbs": (N * eb + N // 4 + 8 * N // G) / ms / 1e6}
+            ms = timed(lambda: cabi.roundtrip_keys(x, out, G))
+            res[f"roundtrip_{name}_G{G}"] = {"ms": ms, "gbs": (N * eb + 4 * N) / ms / 1e6}
+            if name == "f32":
+                ms = timed(lambda: cabi.dequantize_keys(packed, sc, ze, out, G))
+                res[f"dequantize_G{G}"] = {"ms": ms, "gbs": (N // 4 + 8 * N // G + 4 * N) / ms / 1e6}
+            del packed, sc, ze
+        del x, out
+        torch.cuda.empty_cache()
+    U, T, D, G, R = 64, 8192 + 96, 128, 32, 128
+    k, v = make_unit_tensors(8, 8, T, D, 9, dev, torch.bfloat16)
+    st = cabi.LayerStore(U, D, G, R, T, torch.bfloat16, dev)
+    st.update(k, v)
+    ko_, vo_ = st.materialize()
+    del ko_, vo_
+    ms = timed(lambda: st.materialize())
+    res["materialize_bf16_ring"] = {"ms": ms, "gbs": (2 * U * T * D * 4 + U * st.quant_len * 128) / ms / 1e6,
+                                    "note": "includes the allocation of the two output tensors"}
+    peak, which = peaks()
+    head = res["quantize_bf16_G32"]
+    line = {"metric": "kivi_operator_gbs", "value": head["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": head["ms"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "ops", "elements": N, "headline": "quantize_bf16_G32",
+                       "l2": "inputs larger than L2 (0.5-1 GB per tensor)"},
+            "operators": res,
+            "roofline": {"bound": "hbm", "achieved": head["gbs"], "peak": peak, "unit": "GB/s", "frac": head["gbs"] / peak,
+                         "peak_source": which, "traffic": None},
+            "gpu_launches": args.steps}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -471,13 +533,15 @@ def main():
     ap.add_argument("--gather", default="auto", choices=["auto", "nccl", "peer"],
                     help="N>1: how the attention outputs are all-gathered: by NCCL after the kernels, or by the "
                          "attention's last kernel through peer memory (auto = the latter if it passes a self-check)")
-    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["cfg4"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["cfg4", "ops"])
     ap.add_argument("--path", default="auto", choices=["auto", "fp32", "mma"])
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", dest="graph", action="store_false",
                     help="launch every step from Python instead of replaying a CUDA graph (single GPU only)")
     args = ap.parse_args()
+    if args.workload == "ops":
+        return run_operators(args)
     if args.workload == "cfg4":
         return run_quantize(args)
     wl = WORKLOADS[args.workload]
