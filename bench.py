@@ -400,6 +400,8 @@ def run_ours(args, wl):
                            "parallelism": f"(batch,kv_head) units x{world}, all-gather of outputs"
                                           + ("" if world == 1 else " by NCCL" if pg is None else
                                              " inside the merge kernel (peer stores over NVLink)")},
+                "ms_per_step_median": statistics.median(per), "ms_per_step_p10": per[len(per) // 10],
+                "ms_per_step_p90": per[min(len(per) - 1, (9 * len(per)) // 10)],
                 "decode_tokens_per_s": world * B / (LAYERS * ms_step * 1e-3),
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                              "peak_source": which, "traffic": by * 1.026,
