@@ -264,8 +264,10 @@ int kivi_decode_attention_noalloc(const kivi_layer* layer, int64_t quant_len, in
  * allocation for r == rank), flag_ptrs[r] = rank r's uint32[world] flag array
  * (zero before the first call), unit_offset = index of this rank's first unit
  * in the gathered buffer, epoch = 1, 2, 3, ... identical on all ranks per call.
- * wait != 0: bounded wait (about a second) for all ranks; if it runs out the
- * kernel returns and bit 1 of the device fault word is set.
+ * wait != 0: bounded wait for all ranks (spin_limit polls of about 200 ns, 0 =
+ * about a second); if it runs out the kernel returns, bit 1 of the device fault
+ * word is set and the rows of the ranks that did not arrive are stale -- read
+ * kivi_device_fault at the next point where the host synchronises anyway.
  * Re-use: a rank may run one call ahead of its peers, so alternate between two
  * gathered buffers (e.g. by epoch parity) when the consumer of call e may still
  * be reading while call e+1 of a faster rank writes.
@@ -278,6 +280,8 @@ typedef struct kivi_peer_gather {
     int64_t unit_offset;
     uint32_t epoch;
     int wait;
+    uint32_t spin_limit; /* polls (about 200 ns each) the wait may take; 0 = about a second */
+    uint32_t reserved;
 } kivi_peer_gather;
 
 int kivi_peer_alloc(size_t bytes, void** ptr_out, unsigned char handle_out[64]);
@@ -294,8 +298,10 @@ int kivi_decode_attention_gather(const kivi_layer* layer, int64_t quant_len, int
 /* Reads (and synchronises with) the device fault word: bit 0 is set once a wait
  * for a bulk copy inside a kernel of this library ran out, bit 1 once a wait for
  * peer ranks in kivi_decode_attention_gather ran out.  Such a kernel returns
- * normally (bit 0: the affected split counts as empty). */
+ * normally (bit 0: the affected split counts as empty).  The word is sticky
+ * until kivi_device_fault_clear() resets it (current device; synchronises). */
 int kivi_device_fault(int* word_out);
+int kivi_device_fault_clear(void);
 
 /* number of kernels the last successful call on this thread launched */
 int kivi_last_launch_count(void);

@@ -36,7 +36,7 @@ class PeerGatherDesc(_c.Structure):
     """struct kivi_peer_gather of include/kivi_cuda.h."""
     _fields_ = [("rank", _c.c_int32), ("world", _c.c_int32), ("out_ptrs", _vp * PEER_MAX_WORLD),
                 ("flag_ptrs", _vp * PEER_MAX_WORLD), ("unit_offset", _c.c_int64), ("epoch", _c.c_uint32),
-                ("wait", _c.c_int32)]
+                ("wait", _c.c_int32), ("spin_limit", _c.c_uint32), ("reserved", _c.c_uint32)]
 
 
 SIGNATURES = {
@@ -44,6 +44,7 @@ SIGNATURES = {
     "kivi_version": (_int, []),
     "kivi_last_launch_count": (_int, []),
     "kivi_device_fault": (_int, [_c.POINTER(_int)]),
+    "kivi_device_fault_clear": (_int, []),
     "kivi_quantize_keys_per_channel": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _int, _int, _vp]),
     "kivi_quantize_values_per_token": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _int, _int, _int, _vp]),
     "kivi_dequantize_keys_per_channel": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _vp]),
@@ -109,11 +110,16 @@ def _stream() -> int:
 
 
 def _dev(*ts):
+    """Every tensor of one call: on a CUDA device, contiguous, and all on the
+    same device (the kernel runs on one GPU and must not be handed another
+    GPU's pointers).  Raises before anything is launched."""
     for t in ts:
         if not t.is_cuda:
             raise RuntimeError("tensor must be on a CUDA device")
         if not t.is_contiguous():
             raise RuntimeError("tensor must be contiguous")
+        if t.device != ts[0].device:
+            raise RuntimeError(f"all tensors of one call must be on the same device, got {ts[0].device} and {t.device}")
 
 
 def quantize_keys(x, packed, scales, zeros, group_size, rounding=ROUND_HALF_AWAY):
@@ -157,6 +163,11 @@ def device_fault() -> int:
     w = _int()
     _check(lib.kivi_device_fault(_c.byref(w)))
     return w.value
+
+
+def device_fault_clear():
+    """Reset the sticky fault word of the current device (after it was reported)."""
+    _check(lib.kivi_device_fault_clear())
 
 
 def cache_plan(quant_len, res_len, n_new, G, R):

@@ -177,6 +177,11 @@ class KiviCache:
             self.num_kv_heads = k.shape[1]
             self._serve_device, self._serve_dtype = k.device, k.dtype
             n_units = self.batch_size * self.num_kv_heads
+            if self.shard:
+                # a rank without units would never launch, and its peers would wait for it
+                assert n_units >= self.shard[1], (
+                    f"{n_units} (batch, kv_head) units cannot be sharded over {self.shard[1]} ranks: "
+                    f"every rank must hold at least one unit")
             self._units = unit_partition(n_units, *self.shard) if self.shard else (0, n_units)
         else:
             assert k.shape[0] == self.batch_size, (
@@ -256,15 +261,37 @@ class KiviCache:
         self._cache_view_valid = True
         return self._cache_view
 
+    def check_device_fault(self) -> None:
+        """Raise if a bounded wait inside one of the library's kernels has run out
+        on this device since the last check: a bulk copy that never landed (bit 0,
+        the affected split was dropped) or, with gather="peer", a rank that did
+        not publish its rows in time (bit 1: the gathered rows of that rank were
+        stale).  Reading the word synchronises the device, so this is not called
+        per step; close(), reset() and state_dict() call it, and a serving loop
+        should call it wherever it synchronises anyway.  The word is cleared
+        before raising so the next check reports new faults only."""
+        word = cabi.device_fault()
+        if word:
+            cabi.device_fault_clear()
+            what = [name for bit, name in ((1, "a bulk copy inside the attention kernel did not land in time"),
+                                           (2, "a peer rank did not publish its attention outputs in time")) if word & bit]
+            raise RuntimeError("kivi_cuda device fault word = %d: %s; outputs since the last check may be wrong"
+                               % (word, "; ".join(what)))
+
     def close(self):
-        """Collective: unmap and free the peer-gather buffers (gather="peer")."""
+        """Collective: unmap and free the peer-gather buffers (gather="peer");
+        reports a peer wait that ran out since the last check."""
         for pg in self._peer.values():
             pg.close()
         self._peer = {}
+        if torch.cuda.is_available():
+            self.check_device_fault()
 
     def reset(self):
         """Clear all cached data so the same object can serve a new sequence
         (manager.py:292-303); device buffers are released and re-created lazily."""
+        if any(s is not None for s in self._stores) and torch.cuda.is_available():
+            self.check_device_fault()
         self._flush_count = [0] * self.num_layers
         self._stores = [None] * self.num_layers
         self.batch_size = None
@@ -278,6 +305,7 @@ class KiviCache:
         counters, plus the shape bookkeeping.  Tensors are clones on the cache
         device.  (The reference has no checkpointing; its reset() is the only
         state operation, manager.py:292-303.)"""
+        self.check_device_fault()
         layers = []
         for st in self._stores:
             if st is None:

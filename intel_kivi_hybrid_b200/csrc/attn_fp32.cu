@@ -342,7 +342,7 @@ struct PeerSink {
     }
 };
 
-constexpr uint32_t kPeerSpinLimit = 5u << 20;      // x 200 ns sleeps: about a second
+constexpr uint32_t kPeerSpinLimit = 5u << 20;      // default bound: x 200 ns sleeps, about a second
 
 __global__ void __launch_bounds__(128)
 merge_gather_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -361,10 +361,11 @@ merge_gather_kernel(const float* __restrict__ part_o, const float* __restrict__ 
     for (int r = 0; r < g.world; ++r) st_release_sys(g.flag_ptrs[r] + g.rank, g.epoch);
     if (!g.wait) return;
     const uint32_t* mine = g.flag_ptrs[g.rank];
+    const uint32_t limit = g.spin_limit ? g.spin_limit : kPeerSpinLimit;
     for (int r = 0; r < g.world; ++r) {
         uint32_t it = 0;
         while ((int32_t)(ld_acquire_sys(mine + r) - g.epoch) < 0) {
-            if (++it > kPeerSpinLimit) { atomicOr(&g_gather_fault, 2); return; }
+            if (++it > limit) { atomicOr(&g_gather_fault, 2); return; }
             __nanosleep(200);
         }
     }
@@ -374,6 +375,12 @@ merge_gather_kernel(const float* __restrict__ part_o, const float* __restrict__ 
 
 int gather_fault_word(int* out) {
     KIVI_CUDA_OK(cudaMemcpyFromSymbol(out, g_gather_fault, sizeof(int)));
+    return KIVI_OK;
+}
+
+int gather_fault_clear() {
+    const int zero = 0;
+    KIVI_CUDA_OK(cudaMemcpyToSymbol(g_gather_fault, &zero, sizeof(int)));
     return KIVI_OK;
 }
 

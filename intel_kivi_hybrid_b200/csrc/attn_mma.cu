@@ -10,21 +10,22 @@
 //
 //   q.k   score[t,h] = sum_d (q[h,d]*s[g,d]) * c[d,t]  +  sum_d q[h,d]*z[g,d]
 //         A = codes of 16 tokens x 16 channels; a code is used where it lies in
-//         its byte, as the fp16 subnormal c*4^e*2^-24 (one AND per register
-//         pair, no shift); B = q*s split into fp16 hi + lo parts (the 8 columns
+//         its 16-bit half, as the fp16 subnormal c*4^e*2^-24 (one AND per
+//         register pair); B = q*s split into fp16 hi + lo parts (the 8 columns
 //         are 4 heads x {hi, lo}), 22 significant bits; the zero term is an
-//         fp32 dot product per (group, head).
+//         fp32 dot product per (group, head), computed once per column pair.
 //   p.v   out[h,d]   = sum_t (p[h,t]*s[t,gd]) * c[t,d]  +  sum_t p[h,t]*z[t,gd]
 //         A = codes of 16 channels x 16 tokens, same encoding; B = p*s in fp16
-//         (rounding errors of independent tokens average out); the zero term
-//         accumulates in fp32.
+//         (rounding errors of independent tokens average out), built once per
+//         column pair and exchanged by shuffle; the zero term accumulates in fp32.
 //   Requires |q*s*sm_scale*log2(e)| and p*s below 65504 (fp16 range).
 //
 // Data movement: every warp streams its own token groups from HBM into a
 // private shared-memory ring with bulk asynchronous copies (cp.async.bulk,
-// completion on an mbarrier), two groups (8 KB) per stage, and unpacks codes in
-// registers.  Nothing dequantized is ever written anywhere.  The residual ring
-// (full precision) is one extra split handled with fp32 FMAs.
+// completion on an mbarrier; six lanes issue one copy each), two groups (8 KB)
+// per stage, and unpacks codes in registers.  The unit's queries sit in shared
+// memory, pre-scaled.  Nothing dequantized is ever written anywhere.  The
+// residual ring (full precision) is handled by extra CTAs with fp32 FMAs.
 //
 // Every wait on an mbarrier is bounded; on expiry the warp raises the device
 // fault word, stops consuming and its partial is written as "empty".
@@ -90,24 +91,27 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
-#ifndef KIVI_MMA_EVICT_FIRST
-#define KIVI_MMA_EVICT_FIRST 1      /* 1: the packed cache is streamed through L2 with an evict-first hint */
-#endif
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-#if KIVI_MMA_EVICT_FIRST
+// The packed cache is read once per step: stream it through L2 with an
+// evict-first hint (one policy value per thread, made once).
+__device__ __forceinline__ uint64_t l2_stream_policy() {
     uint64_t policy;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t policy) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
-#else
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-#endif
 }
 __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// same with a zero addend: starts an accumulator without initialising registers
+__device__ __forceinline__ void mma_f16_first(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
 }
 // {lo16, hi16} = {f16(lo), f16(hi)}
 __device__ __forceinline__ uint32_t pack_f16_rz(float lo, float hi) {
@@ -128,36 +132,61 @@ __device__ __forceinline__ float ex2(float x) {
 
 
 // ---- code -> MMA operand encoding ----------------------------------------------
-// A 2-bit code c sitting at bits 2e..2e+1 of the low byte of a 16-bit half is,
-// read as an fp16 bit pattern with a zero exponent field, the subnormal number
+// A 2-bit code c sitting at bits 2e..2e+1 (e <= 4) of a 16-bit half is, read as
+// an fp16 bit pattern with a zero exponent field, the subnormal number
 // c * 4^e * 2^-24 -- exactly.  So one AND per register pair turns packed codes
 // into a tensor-core operand: no shift, no offset.  The factor 4^e * 2^-24
 // belongs to a whole accumulator row and is undone (exactly, a power of two)
 // when the accumulator is read.
+//
+// The tensor core aligns the products of one MMA on their exponent *fields* and
+// keeps about 26 bits below the largest (measured: truncation, not rounding).
+// A subnormal's field is fixed, so the zero bits above a low-lying code come out
+// of that budget: a code at e = 0 is left with 18 bits.  A 32-bit word holds
+// four bytes = four codes each; with the bytes of each half swapped (one PRMT,
+// in place of the shift that would otherwise bring the odd bytes down) the
+// first code of every byte can be taken from bits 8-9 (e = 4) and the other
+// three from where they lie (e = 1..3): no row is left with fewer than 20 bits.
 template <int E> __device__ __forceinline__ uint32_t code_pair(uint32_t w) {
+    static_assert(E >= 0 && E <= 4, "bits 10 and up are the exponent field");
     return w & (0x00030003u << (2 * E));
 }
-constexpr float kRow0 = 16777216.0f;          // 2^24 * 4^-0
+__device__ __forceinline__ uint32_t swap_bytes_in_halves(uint32_t w) { return __byte_perm(w, 0u, 0x2301u); }
+constexpr float kRow0 = 65536.0f;             // first code of a byte, taken at e = 4:  2^24 * 4^-4
 constexpr float kRow1 = 4194304.0f;           // 2^24 * 4^-1
 constexpr float kRow2 = 1048576.0f;           // 2^24 * 4^-2
 constexpr float kRow3 = 262144.0f;            // 2^24 * 4^-3
 
+// The eight operand registers of one 32-bit word `w` of codes (bytes b0..b3; the
+// halves of a register are MMA k-slots): lo[e] = code e of bytes (b0, b2),
+// hi[e] = code e of bytes (b1, b3).
+struct CodeRegs { uint32_t lo[4], hi[4]; };
+__device__ __forceinline__ CodeRegs code_regs(uint32_t w) {
+    const uint32_t ws = swap_bytes_in_halves(w);
+    CodeRegs r;
+    r.lo[0] = code_pair<4>(ws); r.hi[0] = code_pair<4>(w);
+    r.lo[1] = code_pair<1>(w);  r.hi[1] = code_pair<1>(ws);
+    r.lo[2] = code_pair<2>(w);  r.hi[2] = code_pair<2>(ws);
+    r.lo[3] = code_pair<3>(w);  r.hi[3] = code_pair<3>(ws);
+    return r;
+}
+
 struct WarpState {
     float m, l;            // running max / sum of head `tig` (score layout)
-    float o[8][4];         // p.v accumulators, 8 channel tiles (rows still carry 4^I * 2^-24)
-    float oz[4];           // zero-point term, head gid>>1, partial over lanes
+    float o[8][2];         // p.v sums of 8 channel tiles, rows gid / gid+8 (they still carry 4^I * 2^-24)
+    float oz[2];           // zero-point term of head gid>>1, channel groups 2*part and 2*part+1, partial over lanes
 };
 
 // ---- one token group (32 tokens) in three phases ----------------------------------
 // q.k: scores of the lane's four tokens (4*gid + e) for head `tig`, log2 domain.
+// `qx` points at the lane's query slice in shared memory (head hB, pre-scaled,
+// channel 4*tig), `qzp`/`kz` at the slice the lane owns for the zero term: the
+// hi lane of a column pair takes the even 16-channel steps, the lo lane the odd
+// ones, so the dot product q.z is computed once, not twice.
 __device__ __forceinline__ void qk_phase(
     const uint8_t* __restrict__ kc, const float* __restrict__ ks, const float* __restrict__ kz,
-    const float* __restrict__ qreg, uint32_t part_mask, int gid, int tig, float (&s)[4]) {
+    const float* __restrict__ qx, const float* __restrict__ qzp, uint32_t part_mask, int gid, int tig, float (&s)[4]) {
     float c0[KIVI_MMA_CHAINS][4], c1[KIVI_MMA_CHAINS][4];
-#pragma unroll
-    for (int ch_ = 0; ch_ < KIVI_MMA_CHAINS; ++ch_)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { c0[ch_][i] = 0.f; c1[ch_][i] = 0.f; }
     float qz = 0.0f;
 #pragma unroll
     for (int qh = 0; qh < 2; ++qh) {
@@ -166,13 +195,16 @@ __device__ __forceinline__ void qk_phase(
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
             const int kt = 4 * qh + m;
-            const int ch = 64 * qh + 16 * m + 4 * tig;
+            const int ch = 64 * qh + 16 * m;                 // + 4*tig through the lane pointers
             const float4 s4 = *reinterpret_cast<const float4*>(ks + ch);
-            const float4 z4 = *reinterpret_cast<const float4*>(kz + ch);
-            const float4 q4 = *reinterpret_cast<const float4*>(qreg + 4 * kt);
+            const float4 q4 = *reinterpret_cast<const float4*>(qx + ch);
+            if ((m & 1) == 0) {                              // channel steps kt, kt+1 -> one of them per lane
+                const float4 z4 = *reinterpret_cast<const float4*>(kz + ch);
+                const float4 y4 = *reinterpret_cast<const float4*>(qzp + ch);
+                qz = fmaf(y4.x, z4.x, qz); qz = fmaf(y4.y, z4.y, qz);
+                qz = fmaf(y4.z, z4.z, qz); qz = fmaf(y4.w, z4.w, qz);
+            }
             const float x0 = q4.x * s4.x, x1 = q4.y * s4.y, x2 = q4.z * s4.z, x3 = q4.w * s4.w;
-            qz = fmaf(q4.x, z4.x, qz); qz = fmaf(q4.y, z4.y, qz);
-            qz = fmaf(q4.z, z4.z, qz); qz = fmaf(q4.w, z4.w, qz);
             // fp16 hi/lo split of q*s: hi lanes keep x truncated to 11 significant
             // bits, lo lanes keep the remainder (part_mask = 0 on hi lanes)
             const float r0 = x0 - __uint_as_float(__float_as_uint(x0) & part_mask);
@@ -181,12 +213,14 @@ __device__ __forceinline__ void qk_phase(
             const float r3 = x3 - __uint_as_float(__float_as_uint(x3) & part_mask);
             const uint32_t b0 = pack_f16_rz(r0, r2);
             const uint32_t b1 = pack_f16_rz(r1, r3);
-            const uint32_t we = w[m], wo = w[m] >> 8;
+            const CodeRegs cr = code_regs(w[m]);
             uint32_t a[4];
-            a[0] = code_pair<0>(we); a[1] = code_pair<1>(we); a[2] = code_pair<0>(wo); a[3] = code_pair<1>(wo);
-            mma_f16(c0[kt % KIVI_MMA_CHAINS], a, b0, b1);
-            a[0] = code_pair<2>(we); a[1] = code_pair<3>(we); a[2] = code_pair<2>(wo); a[3] = code_pair<3>(wo);
-            mma_f16(c1[kt % KIVI_MMA_CHAINS], a, b0, b1);
+            a[0] = cr.lo[0]; a[1] = cr.lo[1]; a[2] = cr.hi[0]; a[3] = cr.hi[1];          // tokens 4*gid, 4*gid + 1
+            if (kt < KIVI_MMA_CHAINS) mma_f16_first(c0[kt % KIVI_MMA_CHAINS], a, b0, b1);
+            else mma_f16(c0[kt % KIVI_MMA_CHAINS], a, b0, b1);
+            a[0] = cr.lo[2]; a[1] = cr.lo[3]; a[2] = cr.hi[2]; a[3] = cr.hi[3];          // tokens 4*gid + 2, + 3
+            if (kt < KIVI_MMA_CHAINS) mma_f16_first(c1[kt % KIVI_MMA_CHAINS], a, b0, b1);
+            else mma_f16(c1[kt % KIVI_MMA_CHAINS], a, b0, b1);
         }
     }
 #pragma unroll
@@ -195,9 +229,10 @@ __device__ __forceinline__ void qk_phase(
         for (int ch_ = 0; ch_ < step; ++ch_)
 #pragma unroll
             for (int i = 0; i < 4; ++i) { c0[ch_][i] += c0[ch_ + step][i]; c1[ch_][i] += c1[ch_ + step][i]; }
-    // zero term of head gid>>1 (both lanes of a gid pair hold the same partial)
+    // zero term of head gid>>1: the eight lanes of a column pair hold disjoint partials
     qz += __shfl_xor_sync(0xffffffffu, qz, 1);
     qz += __shfl_xor_sync(0xffffffffu, qz, 2);
+    qz += __shfl_xor_sync(0xffffffffu, qz, 4);
     const float qz_t = __shfl_sync(0xffffffffu, qz, 8 * tig);
     s[0] = fmaf(c0[0][0] + c0[0][1], kRow0, qz_t);   // token 4*gid
     s[1] = fmaf(c0[0][2] + c0[0][3], kRow1, qz_t);   // token 4*gid + 1
@@ -222,12 +257,9 @@ __device__ __forceinline__ void softmax_phase(float (&s)[NG][4], int gid, int la
         st.m = m_new;
         st.l *= alpha;
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) st.o[mt][i] *= alpha;
+        for (int mt = 0; mt < 8; ++mt) { st.o[mt][0] *= alpha; st.o[mt][1] *= alpha; }
         const float alpha_b = __shfl_sync(0xffffffffu, alpha, (lane & ~3) | (gid >> 1));
-#pragma unroll
-        for (int gd = 0; gd < 4; ++gd) st.oz[gd] *= alpha_b;
+        st.oz[0] *= alpha_b; st.oz[1] *= alpha_b;
     }
 #pragma unroll
     for (int g = 0; g < NG; ++g)
@@ -239,7 +271,13 @@ __device__ __forceinline__ void softmax_phase(float (&s)[NG][4], int gid, int la
 // Value block words (kivi_common.cuh): word (gd, kappa, r, c) holds natural byte
 // 8*gd + r (channels 32*gd + 4*r + i) of tokens 16*kappa + 4*c + n in bytes n.
 // A lane (gid, tig) reads word (gd, kappa, gid, tig): bytes 0/2 are its k-slots
-// 2tig / 2tig+1, bytes 1/3 (after >> 8) its k-slots 2tig+8 / 2tig+9.
+// 2tig / 2tig+1, bytes 1/3 its k-slots 2tig+8 / 2tig+9 (code_regs).
+// The hi and the lo lane of a column pair (gid, gid^1) hold the same head and the
+// same tokens, and only the hi lane's B column is ever read.  So the pair splits
+// the work by channel group: the hi lane builds p*s and the zero term for groups
+// 0,1, the lo lane for groups 2,3, and one exchange hands the hi lane the
+// operands it lacks (what the lo lane feeds into its own column is never read).
+template <bool FIRST>
 __device__ __forceinline__ void pv_phase(
     const uint8_t* __restrict__ vc, const float* __restrict__ vs, const float* __restrict__ vz,
     const float (&p)[4], int part, int gid, int tig, float (&acc)[8][4], WarpState& st) {
@@ -250,36 +288,40 @@ __device__ __forceinline__ void pv_phase(
         float pe[4];
 #pragma unroll
         for (int n = 0; n < 4; ++n) pe[n] = __shfl_sync(0xffffffffu, p[n], src);
-        // scales / zeros of token 16*kap + 4*tig + n sit at row 16*kap + 4*n + tig
-        float4 sv[4];
+        // scales / zeros of token 16*kap + 4*tig + n sit at row 16*kap + 4*n + tig;
+        // the lane takes the two channel groups 2*part, 2*part + 1 of each row
+        float2 sv[4], zv[4];
 #pragma unroll
-        for (int n = 0; n < 4; ++n) sv[n] = *reinterpret_cast<const float4*>(vs + (16 * kap + 4 * n + tig) * 4);
-        {   // zero term: hi lanes take n = 0,1, lo lanes n = 2,3
-            const float pa = part ? pe[2] : pe[0], pb = part ? pe[3] : pe[1];
-            const int ra = 16 * kap + 8 * part + tig;
-            const float4 za = *reinterpret_cast<const float4*>(vz + ra * 4);
-            const float4 zb = *reinterpret_cast<const float4*>(vz + (ra + 4) * 4);
-            st.oz[0] = fmaf(pa, za.x, fmaf(pb, zb.x, st.oz[0]));
-            st.oz[1] = fmaf(pa, za.y, fmaf(pb, zb.y, st.oz[1]));
-            st.oz[2] = fmaf(pa, za.z, fmaf(pb, zb.z, st.oz[2]));
-            st.oz[3] = fmaf(pa, za.w, fmaf(pb, zb.w, st.oz[3]));
+        for (int n = 0; n < 4; ++n) {
+            sv[n] = *reinterpret_cast<const float2*>(vs + (16 * kap + 4 * n + tig) * 4 + 2 * part);
+            zv[n] = *reinterpret_cast<const float2*>(vz + (16 * kap + 4 * n + tig) * 4 + 2 * part);
         }
-        // lo lanes feed the odd B columns with the same p*s: those columns of the
-        // accumulators are never read
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            st.oz[0] = fmaf(pe[n], zv[n].x, st.oz[0]);
+            st.oz[1] = fmaf(pe[n], zv[n].y, st.oz[1]);
+        }
+        uint32_t own[2][2], got[2][2];
+        own[0][0] = pack_f16_rn(pe[0] * sv[0].x, pe[2] * sv[2].x);     // k-slots 2tig, 2tig+1: tokens n = 0, 2
+        own[0][1] = pack_f16_rn(pe[1] * sv[1].x, pe[3] * sv[3].x);     // k-slots 2tig+8, +9:   tokens n = 1, 3
+        own[1][0] = pack_f16_rn(pe[0] * sv[0].y, pe[2] * sv[2].y);
+        own[1][1] = pack_f16_rn(pe[1] * sv[1].y, pe[3] * sv[3].y);
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) got[i][j] = __shfl_xor_sync(0xffffffffu, own[i][j], 4);
 #pragma unroll
         for (int gd = 0; gd < 4; ++gd) {
-            const float s0 = gd == 0 ? sv[0].x : gd == 1 ? sv[0].y : gd == 2 ? sv[0].z : sv[0].w;
-            const float s1 = gd == 0 ? sv[1].x : gd == 1 ? sv[1].y : gd == 2 ? sv[1].z : sv[1].w;
-            const float s2 = gd == 0 ? sv[2].x : gd == 1 ? sv[2].y : gd == 2 ? sv[2].z : sv[2].w;
-            const float s3 = gd == 0 ? sv[3].x : gd == 1 ? sv[3].y : gd == 2 ? sv[3].z : sv[3].w;
-            const uint32_t b0 = pack_f16_rn(pe[0] * s0, pe[2] * s2);     // k-slots 2tig, 2tig+1: tokens n = 0, 2
-            const uint32_t b1 = pack_f16_rn(pe[1] * s1, pe[3] * s3);     // k-slots 2tig+8, +9:   tokens n = 1, 3
-            const uint32_t we = vw[gd * 64 + kap * 32], wo = we >> 8;
+            const uint32_t b0 = gd < 2 ? own[gd][0] : got[gd - 2][0];
+            const uint32_t b1 = gd < 2 ? own[gd][1] : got[gd - 2][1];
+            const CodeRegs cr = code_regs(vw[gd * 64 + kap * 32]);
             uint32_t a[4];
-            a[0] = code_pair<0>(we); a[1] = code_pair<1>(we); a[2] = code_pair<0>(wo); a[3] = code_pair<1>(wo);
-            mma_f16(acc[2 * gd], a, b0, b1);
-            a[0] = code_pair<2>(we); a[1] = code_pair<3>(we); a[2] = code_pair<2>(wo); a[3] = code_pair<3>(wo);
-            mma_f16(acc[2 * gd + 1], a, b0, b1);
+            a[0] = cr.lo[0]; a[1] = cr.lo[1]; a[2] = cr.hi[0]; a[3] = cr.hi[1];          // channels 4*gid, 4*gid + 1 of the group
+            if (FIRST && kap == 0) mma_f16_first(acc[2 * gd], a, b0, b1);
+            else mma_f16(acc[2 * gd], a, b0, b1);
+            a[0] = cr.lo[2]; a[1] = cr.lo[3]; a[2] = cr.hi[2]; a[3] = cr.hi[3];
+            if (FIRST && kap == 0) mma_f16_first(acc[2 * gd + 1], a, b0, b1);
+            else mma_f16(acc[2 * gd + 1], a, b0, b1);
         }
     }
 }
@@ -287,16 +329,22 @@ __device__ __forceinline__ void pv_phase(
 // NG consecutive token groups of one pipeline stage, processed together: the
 // q.k and p.v phases of the groups are independent instruction streams, the
 // softmax update is done once for all NG*32 tokens.
+struct LaneView {
+    const float* qx;       // q_s + head*kD + 4*tig
+    const float* qzp;      // qx + 16*part
+    uint32_t part_mask;    // 0 on hi lanes, "keep 11 significant bits" on lo lanes
+    int part, gid, tig, lane;
+};
+
 template <int NG>
-__device__ __forceinline__ void process_groups(
-    const uint8_t* __restrict__ sb, int g0, const float* __restrict__ qreg, uint32_t part_mask,
-    int part, int gid, int tig, int lane, WarpState& st) {
+__device__ __forceinline__ void process_groups(const uint8_t* __restrict__ sb, const LaneView& v, WarpState& st) {
     float s[NG][4];
 #pragma unroll
     for (int g = 0; g < NG; ++g)
-        qk_phase(sb + (g0 + g) * 1024, reinterpret_cast<const float*>(sb + kGPS * 1024 + (g0 + g) * 512),
-                 reinterpret_cast<const float*>(sb + kGPS * 1536 + (g0 + g) * 512), qreg, part_mask, gid, tig, s[g]);
-    softmax_phase<NG>(s, gid, lane, st);
+        qk_phase(sb + g * 1024, reinterpret_cast<const float*>(sb + kGPS * 1024 + g * 512) + 4 * v.tig,
+                 reinterpret_cast<const float*>(sb + kGPS * 1536 + g * 512) + 4 * v.tig + 16 * v.part,
+                 v.qx, v.qzp, v.part_mask, v.gid, v.tig, s[g]);
+    softmax_phase<NG>(s, v.gid, v.lane, st);
     // The tensor core adds each product into its fp32 accumulator with
     // truncation; against an accumulator that has grown over thousands of tokens
     // that is a biased loss (all addends p*s*c are positive) which the later
@@ -304,16 +352,14 @@ __device__ __forceinline__ void process_groups(
     // into fresh accumulators and join the running sums through ordinary adds
     // (only the even columns are ever read).
     float acc[8][4];
+    pv_phase<true>(sb + kGPS * 2048, reinterpret_cast<const float*>(sb + kGPS * 3072),
+                   reinterpret_cast<const float*>(sb + kGPS * 3584), s[0], v.part, v.gid, v.tig, acc, st);
 #pragma unroll
-    for (int mt = 0; mt < 8; ++mt)
+    for (int g = 1; g < NG; ++g)
+        pv_phase<false>(sb + kGPS * 2048 + g * 1024, reinterpret_cast<const float*>(sb + kGPS * 3072 + g * 512),
+                        reinterpret_cast<const float*>(sb + kGPS * 3584 + g * 512), s[g], v.part, v.gid, v.tig, acc, st);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[mt][i] = 0.0f;
-#pragma unroll
-    for (int g = 0; g < NG; ++g)
-        pv_phase(sb + kGPS * 2048 + (g0 + g) * 1024, reinterpret_cast<const float*>(sb + kGPS * 3072 + (g0 + g) * 512),
-                 reinterpret_cast<const float*>(sb + kGPS * 3584 + (g0 + g) * 512), s[g], part, gid, tig, acc, st);
-#pragma unroll
-    for (int mt = 0; mt < 8; ++mt) { st.o[mt][0] += acc[mt][0]; st.o[mt][2] += acc[mt][2]; }
+    for (int mt = 0; mt < 8; ++mt) { st.o[mt][0] += acc[mt][0]; st.o[mt][1] += acc[mt][2]; }
 }
 
 // ---- residual ring: full-precision tokens ---------------------------------------
@@ -457,6 +503,12 @@ __device__ __forceinline__ void residual_part(
 // and overlap with the rest); CTA n_res_splits + i covers token groups
 // [i*gps, min((i+1)*gps, n_groups)).  Partial slots: quantized split i -> i,
 // residual part r -> nq_splits + r.
+//
+// Shared memory: [kWarps][kStages][kStageBytes] stage rings | q_s [4][128] fp32
+// (the unit's queries times sm_scale*log2(e), rows >= n_rep zero) | mbarriers |
+// (max, sum) of the warps.  When a warp is done, its ring doubles as the
+// [4][128] buffer its scaled output goes to; the CTA then adds the warps'
+// buffers in warp order (deterministic) and writes one partial.
 __global__ void __launch_bounds__(kWarps * 32, KIVI_MMA_MIN_CTAS)
 attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
                 const void* __restrict__ q, int q_dtype,
@@ -464,25 +516,92 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
                 float* __restrict__ part_o, float* __restrict__ part_ml) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* stage_mem = smem_raw;                                               // [kWarps][kStages][kStageBytes]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + kWarps * kStages * kStageBytes);  // [kWarps][kStages]
+    float* q_s = reinterpret_cast<float*>(smem_raw + kWarps * kStages * kStageBytes);   // [4][128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(q_s + 4 * kD);                  // [kWarps][kStages]
     float* ml_s = reinterpret_cast<float*>(bars + kWarps * kStages);             // [kWarps][4][2]
-    float* o_s = ml_s + kWarps * 4 * 2;                                          // [4][128]
+
+    // the kernel that folds the partials is queued with programmatic stream
+    // serialization: let it become resident now, it waits for this grid's end
+    cudaTriggerProgrammaticLaunchCompletion();
 
     const int u = blockIdx.y;
     const int n_splits_total = nq_splits + n_res_splits;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int gid = lane >> 2, tig = lane & 3;
+    uint8_t* wstage = stage_mem + warp * kStages * kStageBytes;
+    float* fo = reinterpret_cast<float*>(wstage);                               // [4][128] once the ring is idle
+    const bool is_res = (int)blockIdx.x < n_res_splits;
+    const int slot = is_res ? nq_splits + (int)blockIdx.x : (int)blockIdx.x - n_res_splits;
 
-    if ((int)blockIdx.x < n_res_splits) {
+    // ---- quantized split: start the copies before anything else ----------------
+    const int64_t n_groups = quant_len / kG;
+    const int64_t g_begin = is_res ? 0 : (int64_t)slot * gps;
+    int64_t g_end = is_res ? 0 : g_begin + gps;
+    if (g_end > n_groups) g_end = n_groups;
+    const int n_my_groups = (int)(g_end - g_begin);
+    const int n_chunks = (n_my_groups + kGPS - 1) / kGPS;
+    const int my_n = n_chunks > warp ? (n_chunks - warp + kWarps - 1) / kWarps : 0;
+    const uint32_t bar0 = smem_u32(bars + warp * kStages);
+    const uint32_t stage0 = smem_u32(wstage);
+    // The six pieces of a chunk (key codes, scales, zeros, value codes, scales,
+    // zeros) are contiguous runs of 1024 or 512 bytes per token group; lane i < 6
+    // owns piece i and issues its copy, so a chunk costs one copy's instructions.
+    // Chunk c of this warp starts at group g_begin + (warp + kWarps*c)*kGPS.
+    const uint8_t* my_src = nullptr;
+    uint32_t my_bytes = 0, my_dst = 0;
+    if (!is_res) {
+        const uint8_t* base = lane == 0 ? L.k_codes
+                            : lane == 1 ? reinterpret_cast<const uint8_t*>(L.k_scales)
+                            : lane == 2 ? reinterpret_cast<const uint8_t*>(L.k_zeros)
+                            : lane == 3 ? L.v_codes
+                            : lane == 4 ? reinterpret_cast<const uint8_t*>(L.v_scales)
+                                        : reinterpret_cast<const uint8_t*>(L.v_zeros);
+        my_bytes = (lane == 0 || lane == 3) ? 1024u : 512u;
+        my_dst = lane == 0 ? 0u : lane == 1 ? kGPS * 1024u : lane == 2 ? kGPS * 1536u
+               : lane == 3 ? kGPS * 2048u : lane == 4 ? kGPS * 3072u : kGPS * 3584u;
+        const int64_t gw0 = (int64_t)u * (L.max_tokens / kG) + g_begin + (int64_t)warp * kGPS;
+        my_src = base + gw0 * my_bytes;
+        if (lane == 0) {
+#pragma unroll
+            for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncwarp();
+    }
+    const uint64_t policy = l2_stream_policy();
+    auto issue = [&](int c) {                 // all lanes call it
+        const int goff = (warp + kWarps * c) * kGPS;             // groups from g_begin
+        const int ng = (n_my_groups - goff) < kGPS ? (n_my_groups - goff) : kGPS;
+        const int s = c % kStages;
+        const uint32_t bar = bar0 + 8 * s;
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)ng * kGroupBytes);
+        __syncwarp();
+        if (lane < 6)
+            bulk_g2s(stage0 + s * kStageBytes + my_dst, my_src + (int64_t)c * (kWarps * kGPS) * my_bytes,
+                     (uint32_t)ng * my_bytes, bar, policy);
+    };
+    for (int c = 0; c < kStages && c < my_n; ++c) issue(c);
+
+    // ---- queries -> shared memory, pre-scaled -----------------------------------
+    {
+        for (int i = threadIdx.x; i < kD; i += blockDim.x) {             // 128 float4 = [4][128]
+            const int hh = i >> 5, cc = (i & 31) * 4;
+            float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (hh < n_rep) {
+                const int64_t e = ((int64_t)u * n_rep + hh) * kD + cc;
+                if (q_dtype == KIVI_BF16) RowVec<__nv_bfloat16>::load4(reinterpret_cast<const __nv_bfloat16*>(q) + e, v);
+                else RowVec<float>::load4(reinterpret_cast<const float*>(q) + e, v);
+            }
+            *reinterpret_cast<float4*>(q_s + hh * kD + cc) =
+                make_float4(scale_log2 * v[0], scale_log2 * v[1], scale_log2 * v[2], scale_log2 * v[3]);
+        }
+    }
+    __syncthreads();
+
+    if (is_res) {
         // ---------------- residual ring ----------------
         const int rs = blockIdx.x;
-        float* q_s = reinterpret_cast<float*>(stage_mem);            // [4][128]
-        for (int i = threadIdx.x; i < 4 * kD; i += blockDim.x) {
-            const int h = i / kD;
-            q_s[i] = h < n_rep ? scale_log2 * load_as_float(q, q_dtype, (int64_t)u * n_rep * kD + i) : 0.0f;
-        }
-        for (int i = threadIdx.x; i < 4 * kD; i += blockDim.x) o_s[i] = 0.0f;
-        __syncthreads();
         const int t_begin = rs * res_chunk;
         const int t_end = t_begin + res_chunk < res_len ? t_begin + res_chunk : res_len;
         float m[4], l[4], o[4][4];
@@ -503,173 +622,104 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
             ml_s[(warp * 4 + lane) * 2] = mh; ml_s[(warp * 4 + lane) * 2 + 1] = lh;
         }
         __syncthreads();
-        for (int w2 = 0; w2 < kWarps; ++w2) {
-            if (warp == w2) {
 #pragma unroll
-                for (int h = 0; h < 4; ++h) {
-                    float M = -INFINITY;
-                    for (int w3 = 0; w3 < kWarps; ++w3) M = fmaxf(M, ml_s[(w3 * 4 + h) * 2]);
-                    const float f = (m[h] == -INFINITY) ? 0.0f : ex2(m[h] - M);
+        for (int h = 0; h < 4; ++h) {
+            float M = -INFINITY;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) o_s[h * kD + 4 * lane + i] += f * o[h][i];
-                }
-            }
-            __syncthreads();
+            for (int w2 = 0; w2 < kWarps; ++w2) M = fmaxf(M, ml_s[(w2 * 4 + h) * 2]);
+            const float f = (m[h] == -INFINITY) ? 0.0f : ex2(m[h] - M);
+            *reinterpret_cast<float4*>(fo + h * kD + 4 * lane) = make_float4(f * o[h][0], f * o[h][1], f * o[h][2], f * o[h][3]);
         }
-        const int64_t pbase = ((int64_t)u * n_splits_total + nq_splits + rs) * n_rep;
-        for (int i = threadIdx.x; i < n_rep * kD; i += blockDim.x) part_o[pbase * kD + i] = o_s[i];
-        if (threadIdx.x < n_rep) {
-            const int h = threadIdx.x;
-            float Mh = -INFINITY, ls = 0.0f;
-            for (int w2 = 0; w2 < kWarps; ++w2) Mh = fmaxf(Mh, ml_s[(w2 * 4 + h) * 2]);
-            for (int w2 = 0; w2 < kWarps; ++w2) {
-                const float mw = ml_s[(w2 * 4 + h) * 2];
-                if (mw != -INFINITY) ls += ml_s[(w2 * 4 + h) * 2 + 1] * ex2(mw - Mh);
-            }
-            part_ml[(pbase + h) * 2] = Mh;
-            part_ml[(pbase + h) * 2 + 1] = ls;
-        }
-        return;
-    }
-    const int split = (int)blockIdx.x - n_res_splits;
-    const int part = gid & 1, hB = gid >> 1;
-    const int64_t max_groups = L.max_tokens / kG;
-    const int64_t n_groups = quant_len / kG;
-    const int64_t g_begin = (int64_t)split * gps;
-    int64_t g_end = g_begin + gps;
-    if (g_end > n_groups) g_end = n_groups;
-    const int n_chunks = (int)((g_end - g_begin + kGPS - 1) / kGPS);
-    const int my_n = n_chunks > warp ? (n_chunks - warp + kWarps - 1) / kWarps : 0;
+    } else {
+        // ---------------- quantized history ----------------
+        LaneView v;
+        v.part = gid & 1; v.gid = gid; v.tig = tig; v.lane = lane;
+        v.qzp = q_s + (gid >> 1) * kD + 4 * tig + 16 * v.part;
+        v.qx = q_s + (gid >> 1) * kD + 4 * tig;
+        v.part_mask = v.part ? 0xffffe000u : 0u;   // keep 11 significant bits
 
-    uint8_t* wstage = stage_mem + warp * kStages * kStageBytes;
-    const uint32_t bar0 = smem_u32(bars + warp * kStages);
-    if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < kStages; ++s) mbar_init(bar0 + 8 * s, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    __syncwarp();
-
-    // chunk i of this warp starts at group g_begin + (warp + kWarps*i)*kGPS: base
-    // pointers of chunk 0, advanced by a constant per chunk
-    const int64_t gw0 = (int64_t)u * max_groups + g_begin + (int64_t)warp * kGPS;
-    const int64_t tw0 = (int64_t)u * L.max_tokens + (g_begin + (int64_t)warp * kGPS) * kG;
-    const uint8_t* pk_c = L.k_codes + gw0 * 1024;
-    const float* pk_s = L.k_scales + gw0 * kD;
-    const float* pk_z = L.k_zeros + gw0 * kD;
-    const uint8_t* pv_c = L.v_codes + tw0 * 32;
-    const float* pv_s = L.v_scales + tw0 * 4;
-    const float* pv_z = L.v_zeros + tw0 * 4;
-    const int n_my_groups = (int)(g_end - g_begin);
-    auto issue = [&](int i) {
-        const int goff = (warp + kWarps * i) * kGPS;             // groups from g_begin
-        const int ng = (n_my_groups - goff) < kGPS ? (n_my_groups - goff) : kGPS;
-        const int s = i % kStages;
-        const uint32_t bar = bar0 + 8 * s;
-        const uint32_t dst = smem_u32(wstage + s * kStageBytes);
-        const int64_t adv = (int64_t)i * kWarps * kGPS;          // groups past chunk 0
-        mbar_expect_tx(bar, (uint32_t)ng * kGroupBytes);
-        bulk_g2s(dst, pk_c + adv * 1024, ng * 1024, bar);
-        bulk_g2s(dst + kGPS * 1024, pk_s + adv * kD, ng * 512, bar);
-        bulk_g2s(dst + kGPS * 1536, pk_z + adv * kD, ng * 512, bar);
-        bulk_g2s(dst + kGPS * 2048, pv_c + adv * 1024, ng * 1024, bar);
-        bulk_g2s(dst + kGPS * 3072, pv_s + adv * 128, ng * 512, bar);
-        bulk_g2s(dst + kGPS * 3584, pv_z + adv * 128, ng * 512, bar);
-    };
-    if (lane == 0) {
-        for (int i = 0; i < kStages && i < my_n; ++i) issue(i);
-    }
-
-    // query registers: channel 64*qh + 16*m + 4*tig + i at index 16*qh + 4*m + i,
-    // head hB, pre-multiplied by sm_scale * log2(e)
-    __align__(16) float qreg[32];
-    {
-        const float f = scale_log2;
-#pragma unroll
-        for (int r = 0; r < 32; ++r) {
-            const int ch = 64 * (r >> 4) + 16 * ((r >> 2) & 3) + 4 * tig + (r & 3);
-            qreg[r] = hB < n_rep ? f * load_as_float(q, q_dtype, ((int64_t)u * n_rep + hB) * kD + ch) : 0.0f;
-        }
-    }
-    const uint32_t part_mask = part ? 0xffffe000u : 0u;   // keep 11 significant bits
-
-    WarpState st;
-    st.m = -INFINITY; st.l = 0.0f;
-#pragma unroll
-    for (int mt = 0; mt < 8; ++mt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) st.o[mt][i] = 0.0f;
-#pragma unroll
-    for (int gd = 0; gd < 4; ++gd) {
-        st.oz[gd] = 0.0f;
-    }
-
-    bool ok = true;
-    for (int i = 0; i < my_n; ++i) {
-        const int s = i % kStages;
-        if (!mbar_wait(bar0 + 8 * s, (uint32_t)(i / kStages) & 1u)) { ok = false; break; }
-        const int64_t g0 = g_begin + (int64_t)(warp + kWarps * i) * kGPS;
-        const int ng = (int)((g_end - g0) < kGPS ? (g_end - g0) : kGPS);
-        const uint8_t* sb = wstage + s * kStageBytes;
-#if KIVI_MMA_JOINT
-        static_assert(kGPS == 2, "joint processing is written for two groups per stage");
-        if (ng == 2) {
-            process_groups<2>(sb, 0, qreg, part_mask, part, gid, tig, lane, st);
-        } else {
-            process_groups<1>(sb, 0, qreg, part_mask, part, gid, tig, lane, st);
-        }
-#else
-        for (int gi = 0; gi < ng; ++gi)
-            process_groups<1>(sb, gi, qreg, part_mask, part, gid, tig, lane, st);
-#endif
-        __syncwarp();
-        if (lane == 0 && i + kStages < my_n) issue(i + kStages);
-    }
-    if (!ok) {
-        // copies still in flight target this CTA's shared memory: give them a
-        // bounded chance to land before the CTA may exit, then report empty.
-        if (lane == 0) atomicExch(&g_fault_word, 1);
-        for (int s = 0; s < kStages; ++s) mbar_wait(bar0 + 8 * s, 0);
+        WarpState st;
         st.m = -INFINITY; st.l = 0.0f;
-    }
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) { st.o[mt][0] = 0.0f; st.o[mt][1] = 0.0f; }
+        st.oz[0] = 0.0f; st.oz[1] = 0.0f;
 
-    // ---- fold the warp's lanes, then the CTA's warps ---------------------------
-    st.l += __shfl_xor_sync(0xffffffffu, st.l, 4);
-    st.l += __shfl_xor_sync(0xffffffffu, st.l, 8);
-    st.l += __shfl_xor_sync(0xffffffffu, st.l, 16);
-    float ozt[4];
-#pragma unroll
-    for (int gd = 0; gd < 4; ++gd) {
-        float z = st.oz[gd];
-        z += __shfl_xor_sync(0xffffffffu, z, 1);
-        z += __shfl_xor_sync(0xffffffffu, z, 2);
-        z += __shfl_xor_sync(0xffffffffu, z, 4);      // the other half of the tokens (lo lanes)
-        ozt[gd] = __shfl_sync(0xffffffffu, z, 8 * tig);   // head tig <- lanes with gid>>1 == tig
-    }
-    if (gid == 0) { ml_s[(warp * 4 + tig) * 2] = st.m; ml_s[(warp * 4 + tig) * 2 + 1] = st.l; }
-    for (int i = threadIdx.x; i < 4 * kD; i += blockDim.x) o_s[i] = 0.0f;
-    __syncthreads();
-    float M = -INFINITY;
-    for (int w2 = 0; w2 < kWarps; ++w2) M = fmaxf(M, ml_s[(w2 * 4 + tig) * 2]);
-    const float f = (st.m == -INFINITY) ? 0.0f : ex2(st.m - M);
-    for (int w2 = 0; w2 < kWarps; ++w2) {
-        if (warp == w2 && f != 0.0f) {
-#pragma unroll
-            for (int mt = 0; mt < 8; ++mt) {
-                const int gd = mt >> 1;
-                const int ch = 32 * gd + 4 * gid + 2 * (mt & 1);
-                // rows gid / gid+8 hold code index 2*(mt&1) / 2*(mt&1)+1 of their byte
-                const float r0 = (mt & 1) ? kRow2 : kRow0, r1 = (mt & 1) ? kRow3 : kRow1;
-                o_s[tig * kD + ch] += f * fmaf(st.o[mt][0], r0, ozt[gd]);       // odd columns unused
-                o_s[tig * kD + ch + 1] += f * fmaf(st.o[mt][2], r1, ozt[gd]);
-            }
+        bool ok = true;
+        int c = 0;
+        for (; c < my_n; ++c) {
+            const int s = c % kStages;
+            if (!mbar_wait(bar0 + 8 * s, (uint32_t)(c / kStages) & 1u)) { ok = false; break; }
+            const int goff = (warp + kWarps * c) * kGPS;
+            const uint8_t* sb = wstage + s * kStageBytes;
+#if KIVI_MMA_GPS == 2
+            if (n_my_groups - goff >= 2) process_groups<2>(sb, v, st);
+            else process_groups<1>(sb, v, st);
+#else
+            process_groups<1>(sb, v, st);
+#endif
+            __syncwarp();
+            if (c + kStages < my_n) issue(c + kStages);
         }
+        if (!ok) {
+            // A copy did not land within the bound.  The copies still in flight
+            // target this warp's ring: give each of them (chunks c .. c+kStages-1,
+            // those that were issued) a second bounded wait on its own phase
+            // before the ring is reused, then report an empty partial.
+            if (lane == 0) atomicExch(&g_fault_word, 1);
+            for (int k = c; k < c + kStages && k < my_n; ++k)
+                mbar_wait(bar0 + 8 * (k % kStages), (uint32_t)(k / kStages) & 1u);
+            st.m = -INFINITY; st.l = 0.0f;
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) { st.o[mt][0] = 0.0f; st.o[mt][1] = 0.0f; }
+            st.oz[0] = 0.0f; st.oz[1] = 0.0f;
+        }
+
+        // ---- fold the warp's lanes ----------------------------------------------
+        st.l += __shfl_xor_sync(0xffffffffu, st.l, 4);
+        st.l += __shfl_xor_sync(0xffffffffu, st.l, 8);
+        st.l += __shfl_xor_sync(0xffffffffu, st.l, 16);
+        // zero term: lanes (gid, *) hold head gid>>1, channel groups 2*(gid&1) + {0, 1}
+        float ozt[4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float z = st.oz[i];
+            z += __shfl_xor_sync(0xffffffffu, z, 1);
+            z += __shfl_xor_sync(0xffffffffu, z, 2);
+            ozt[i] = __shfl_sync(0xffffffffu, z, 8 * tig);          // head tig, group i     <- hi lanes of gid 2*tig
+            ozt[2 + i] = __shfl_sync(0xffffffffu, z, 8 * tig + 4);  // head tig, group 2 + i <- lo lanes
+        }
+        if (gid == 0) { ml_s[(warp * 4 + tig) * 2] = st.m; ml_s[(warp * 4 + tig) * 2 + 1] = st.l; }
         __syncthreads();
+        float M = -INFINITY;
+#pragma unroll
+        for (int w2 = 0; w2 < kWarps; ++w2) M = fmaxf(M, ml_s[(w2 * 4 + tig) * 2]);
+        const float f = (st.m == -INFINITY) ? 0.0f : ex2(st.m - M);
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+            const int gd = mt >> 1;
+            const int ch = 32 * gd + 4 * gid + 2 * (mt & 1);
+            // rows gid / gid+8 hold code index 2*(mt&1) / 2*(mt&1)+1 of their byte
+            const float r0 = (mt & 1) ? kRow2 : kRow0, r1 = (mt & 1) ? kRow3 : kRow1;
+            *reinterpret_cast<float2*>(fo + tig * kD + ch) =
+                make_float2(f * fmaf(st.o[mt][0], r0, ozt[gd]), f * fmaf(st.o[mt][1], r1, ozt[gd]));
+        }
     }
-    const int64_t pbase = ((int64_t)u * n_splits_total + split) * n_rep;
-    for (int i = threadIdx.x; i < n_rep * kD; i += blockDim.x)
-        part_o[pbase * kD + i] = o_s[i];
+    __syncthreads();
+
+    // ---- the CTA's partial: warps added in warp order ------------------------------
+    const int64_t pbase = ((int64_t)u * n_splits_total + slot) * n_rep;
+    for (int i = threadIdx.x; i < kD; i += blockDim.x) {
+        const int h = i >> 5, cc = (i & 31) * 4;
+        if (h < n_rep) {
+            float4 a = *reinterpret_cast<const float4*>(stage_mem + h * kD * 4 + cc * 4);
+#pragma unroll
+            for (int w2 = 1; w2 < kWarps; ++w2) {
+                const float4 b = *reinterpret_cast<const float4*>(stage_mem + w2 * kStages * kStageBytes + h * kD * 4 + cc * 4);
+                a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+            }
+            *reinterpret_cast<float4*>(part_o + (pbase + h) * kD + cc) = a;
+        }
+    }
     if (threadIdx.x < n_rep) {
         const int h = threadIdx.x;
         float Mh = -INFINITY, ls = 0.0f;
@@ -683,15 +733,16 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
     }
 }
 
-constexpr size_t kSmemBytes = (size_t)kWarps * kStages * kStageBytes + kWarps * kStages * 8 +
-                              kWarps * 4 * 2 * 4 + 4 * kD * 4;
+constexpr size_t kSmemBytes = (size_t)kWarps * kStages * kStageBytes + 4 * kD * 4 + kWarps * kStages * 8 +
+                              kWarps * 4 * 2 * 4;
+static_assert(kStages * kStageBytes >= 4 * kD * 4, "a warp's ring doubles as its [4][128] fold buffer");
+static_assert(kWarps * 32 >= 32, "at least one warp");
 
 }  // namespace
 
-bool attn_mma_supported(const kivi_layer* L, int n_rep, int q_dtype) {
-    (void)q_dtype;
+bool attn_mma_supported(const kivi_layer* L, int n_rep, const void* q) {
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-    return L->head_dim == kD && L->group_size == kG && n_rep >= 1 && n_rep <= 4 &&
+    return L->head_dim == kD && L->group_size == kG && n_rep >= 1 && n_rep <= 4 && al(q) &&
            al(L->k_res) && al(L->v_res) && al(L->k_codes) && al(L->k_scales) && al(L->k_zeros) && al(L->v_codes) && al(L->v_scales) && al(L->v_zeros);
 }
 
@@ -705,10 +756,8 @@ void attn_mma_residual_plan(int res_len, int* n_res_splits, int* res_chunk) {
     *res_chunk = chunk;
 }
 
-int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
-                 const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
-                 int n_res_splits, int res_chunk, float* part_o, float* part_ml, cudaStream_t st) {
-    // the opt-in shared-memory size is a per-device attribute of the kernel
+// the opt-in shared-memory size is a per-device attribute of the kernel
+static int ensure_smem_attr(int* dev_out) {
     static std::atomic<bool> attr_set[64];
     int dev = 0;
     KIVI_CUDA_OK(cudaGetDevice(&dev));
@@ -717,6 +766,29 @@ int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_
         KIVI_CUDA_OK(cudaFuncSetAttribute(attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         attr_set[dev].store(true, std::memory_order_release);
     }
+    if (dev_out) *dev_out = dev;
+    return KIVI_OK;
+}
+
+// CTAs of the kernel that one SM holds at a time (registers and shared memory
+// decide); asked from the runtime once per device.  0 = the query failed.
+int attn_mma_ctas_per_sm() {
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    if (ensure_smem_attr(&dev) != KIVI_OK) return 0;
+    int n = cached[dev].load(std::memory_order_acquire);
+    if (n == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_mma_kernel, kWarps * 32, kSmemBytes) != cudaSuccess || n <= 0)
+            return 0;
+        cached[dev].store(n, std::memory_order_release);
+    }
+    return n;
+}
+
+int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
+                 const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
+                 int n_res_splits, int res_chunk, float* part_o, float* part_ml, cudaStream_t st) {
+    if (int rc = ensure_smem_attr(nullptr)) return rc;
     dim3 grid((unsigned)(nq_splits + n_res_splits), (unsigned)L->num_units);
     attn_mma_kernel<<<grid, kWarps * 32, kSmemBytes, st>>>(*L, quant_len, res_start, res_len, q, q_dtype, scale_log2,
                                                          n_rep, gps, nq_splits, n_res_splits, res_chunk, part_o, part_ml);
@@ -726,6 +798,12 @@ int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_
 
 int attn_mma_fault_word(int* out) {
     KIVI_CUDA_OK(cudaMemcpyFromSymbol(out, g_fault_word, sizeof(int)));
+    return KIVI_OK;
+}
+
+int attn_mma_fault_clear() {
+    const int zero = 0;
+    KIVI_CUDA_OK(cudaMemcpyToSymbol(g_fault_word, &zero, sizeof(int)));
     return KIVI_OK;
 }
 

@@ -46,13 +46,16 @@ int validate_state(const kivi_layer* L, int64_t quant_len, int res_start, int re
 int run_attn_fp32(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
                   const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
                   int n_splits, float* part_o, float* part_ml, cudaStream_t st);
-bool attn_mma_supported(const kivi_layer* L, int n_rep, int q_dtype);
+bool attn_mma_supported(const kivi_layer* L, int n_rep, const void* q);
 void attn_mma_residual_plan(int res_len, int* n_res_splits, int* res_chunk);
+int attn_mma_ctas_per_sm();
 int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
                  const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
                  int n_res_splits, int res_chunk, float* part_o, float* part_ml, cudaStream_t st);
 int attn_mma_fault_word(int* out);
 int gather_fault_word(int* out);
+int attn_mma_fault_clear();
+int gather_fault_clear();
 int run_merge(const float* part_o, const float* part_ml, void* out, const kivi_peer_gather* gather, float* lse,
               int out_dtype, int num_units, int n_rep, int n_splits, int D, cudaStream_t st);
 
@@ -70,6 +73,11 @@ extern "C" int kivi_device_fault(int* word_out) {
     if (int rc = gather_fault_word(&peer_wait)) return rc;
     *word_out = (copy_wait ? 1 : 0) | (peer_wait ? 2 : 0);
     return KIVI_OK;
+}
+
+extern "C" int kivi_device_fault_clear(void) {
+    if (int rc = attn_mma_fault_clear()) return rc;
+    return gather_fault_clear();
 }
 
 static int check_values_args(int64_t num_tokens, int head_dim, int group_size) {
@@ -170,7 +178,9 @@ static int plan_splits_fp32(int num_units, int64_t n_groups, int requested) {
 static int plan_splits_mma(int num_units, int64_t n_groups, int requested, int n_res_splits) {
     if (n_groups <= 0) return 0;
     if (requested > 0) return clamp_splits(requested, n_groups);
-    const double slots = 3.0 * num_sms();
+    int per_sm = attn_mma_ctas_per_sm();
+    if (per_sm <= 0) per_sm = 3;
+    const double slots = (double)per_sm * num_sms();
     const double c0 = 10.0, c1 = 0.425, t_ring = 7.0;
     const int64_t s_wave = (int64_t)(slots / num_units);                    // quantized CTAs alone fill one wave
     if (s_wave >= 1 && (double)(s_wave * num_units) >= 0.9 * slots) {
@@ -207,15 +217,15 @@ static int decode_attention_impl(const kivi_layer* L, int64_t quant_len, int res
     const int64_t n_groups = quant_len / G;
     bool use_mma = false;
     if (path == KIVI_ATTN_MMA) {
-        if (!attn_mma_supported(L, n_rep, q_dtype)) {
-            set_error("tensor-core path needs head_dim 128, group_size 32, n_rep <= 4 (got %d, %d, %d)", D, G, n_rep);
+        if (!attn_mma_supported(L, n_rep, q)) {
+            set_error("tensor-core path needs head_dim 128, group_size 32, n_rep <= 4 (got %d, %d, %d) and 16-byte aligned arrays", D, G, n_rep);
             return KIVI_ERR_UNSUPPORTED;
         }
         use_mma = true;
     } else if (path == KIVI_ATTN_AUTO) {
         // fp32 queries keep the all-fp32 kernel (1e-5 tolerance); bf16 queries take
         // the tensor-core kernel when the shape allows it
-        use_mma = q_dtype == KIVI_BF16 && attn_mma_supported(L, n_rep, q_dtype);
+        use_mma = q_dtype == KIVI_BF16 && attn_mma_supported(L, n_rep, q);
     }
     int n_res_splits = res_len > 0 ? 1 : 0, res_chunk = res_len;
     if (use_mma) attn_mma_residual_plan(res_len, &n_res_splits, &res_chunk);
@@ -226,6 +236,7 @@ static int decode_attention_impl(const kivi_layer* L, int64_t quant_len, int res
     const size_t need = (size_t)L->num_units * n_splits * n_rep * (D + 2) * sizeof(float);
     KIVI_REQUIRE(workspace != nullptr && workspace_bytes >= need,
                  "workspace too small: %zu bytes given, %zu needed", workspace_bytes, need);
+    KIVI_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15u) == 0, "workspace must be 16-byte aligned");
     float* part_o = reinterpret_cast<float*>(workspace);
     float* part_ml = part_o + (size_t)L->num_units * n_splits * n_rep * D;
     if (sm_scale <= 0.0f) sm_scale = 1.0f / sqrtf((float)D);

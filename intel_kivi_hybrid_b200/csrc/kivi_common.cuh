@@ -107,7 +107,7 @@ __device__ __forceinline__ float code_of(float x, float mn, float scale, float r
     return __fsub_rn(code_magic<HALF_EVEN>(x, mn, scale, rcp), 8388608.0f);
 }
 
-// byte q0 | q1<<2 | q2<<4 | q3<<6 (pack_kernels.cpp:20-24) from four code_magic
+// byte q0 | q1<<2 | q2<<4 | q3<<6 (quant_tile.hpp:61-68) from four code_magic
 // values: the 2^23 offsets only reach bits 8 and up of the integer sum.
 __device__ __forceinline__ uint32_t pack4_magic(float m0, float m1, float m2, float m3) {
     const uint32_t b = ((__float_as_uint(m3) * 4u + __float_as_uint(m2)) * 4u + __float_as_uint(m1)) * 4u + __float_as_uint(m0);

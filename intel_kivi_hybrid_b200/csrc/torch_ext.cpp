@@ -28,6 +28,14 @@ void check_tensor(const torch::Tensor& t, const char* name, torch::ScalarType ex
     TORCH_CHECK(t.is_cuda(), name, " must be on cuda but got ", t.device().str());
 }
 
+// Every operand of one operator must live on the same GPU: the kernel runs on
+// the first operand's device and would otherwise dereference another GPU's
+// pointers.  Checked before anything is launched.
+void check_same_device(const torch::Tensor& first, const char* first_name, const torch::Tensor& t, const char* name) {
+    TORCH_CHECK(t.device() == first.device(), name, " is on ", t.device().str(), " but ", first_name, " is on ",
+                first.device().str(), ": all tensors of one call must be on the same device");
+}
+
 // input of quantize / round trip: float32 (reference) or bfloat16 (extension)
 int check_input(const torch::Tensor& t) {
     TORCH_CHECK(t.is_contiguous(), "input must be contiguous");
@@ -61,6 +69,9 @@ int64_t validate_quant_keys(const torch::Tensor& input, const torch::Tensor& out
     check_tensor(output, "output", torch::kUInt8);
     check_tensor(scales, "scales", torch::kFloat32);
     check_tensor(zeros, "zeros", torch::kFloat32);
+    check_same_device(input, "input", output, "output");
+    check_same_device(input, "input", scales, "scales");
+    check_same_device(input, "input", zeros, "zeros");
     TORCH_CHECK(group_size > 0 && group_size % 4 == 0, "group_size must be positive and divisible by 4, got ", group_size);
     const int64_t n = scales.numel();
     TORCH_CHECK(n > 0, "scales must be non-empty");
@@ -78,6 +89,9 @@ int64_t validate_quant_values(const torch::Tensor& input, const torch::Tensor& o
     check_tensor(output, "output", torch::kUInt8);
     check_tensor(scales, "scales", torch::kFloat32);
     check_tensor(zeros, "zeros", torch::kFloat32);
+    check_same_device(input, "input", output, "output");
+    check_same_device(input, "input", scales, "scales");
+    check_same_device(input, "input", zeros, "zeros");
     TORCH_CHECK(group_size > 0 && group_size % 4 == 0, "group_size must be positive and divisible by 4");
     TORCH_CHECK(head_dim > 0 && head_dim % group_size == 0, "head_dim must be positive and divisible by group_size");
     TORCH_CHECK(input.numel() % head_dim == 0, "input.numel() (", input.numel(), ") must be divisible by head_dim (",
@@ -98,6 +112,9 @@ int64_t validate_dequant(const torch::Tensor& input, const torch::Tensor& scales
     check_tensor(scales, "scales", torch::kFloat32);
     check_tensor(zeros, "zeros", torch::kFloat32);
     check_tensor(output, "output", torch::kFloat32);
+    check_same_device(input, "input", scales, "scales");
+    check_same_device(input, "input", zeros, "zeros");
+    check_same_device(input, "input", output, "output");
     TORCH_CHECK(group_size > 0 && group_size % 4 == 0, "group_size must be positive and divisible by 4, got ", group_size);
     const int64_t n = scales.numel();
     TORCH_CHECK(n > 0, "scales must be non-empty");
@@ -112,6 +129,7 @@ int64_t validate_dequant(const torch::Tensor& input, const torch::Tensor& scales
 int64_t validate_roundtrip_keys(const torch::Tensor& input, const torch::Tensor& output, int group_size) {
     check_input(input);
     check_tensor(output, "output", torch::kFloat32);
+    check_same_device(input, "input", output, "output");
     TORCH_CHECK(group_size > 0 && group_size % 4 == 0, "group_size must be positive and divisible by 4, got ", group_size);
     TORCH_CHECK(input.numel() % group_size == 0, "input.numel() (", input.numel(), ") must be divisible by group_size (", group_size, ")");
     TORCH_CHECK(output.numel() == input.numel(), "output size (", output.numel(), ") must equal input size (", input.numel(),
@@ -124,6 +142,7 @@ int64_t validate_roundtrip_keys(const torch::Tensor& input, const torch::Tensor&
 int64_t validate_roundtrip_values(const torch::Tensor& input, const torch::Tensor& output, int head_dim, int group_size) {
     check_input(input);
     check_tensor(output, "output", torch::kFloat32);
+    check_same_device(input, "input", output, "output");
     TORCH_CHECK(group_size > 0 && group_size % 4 == 0, "group_size must be positive and divisible by 4");
     TORCH_CHECK(head_dim > 0 && head_dim % group_size == 0, "head_dim must be positive and divisible by group_size");
     TORCH_CHECK(input.numel() % head_dim == 0, "input.numel() (", input.numel(), ") must be divisible by head_dim (", head_dim, ")");
@@ -189,7 +208,16 @@ void* enqueue_roundtrip_values(torch::Tensor& input, torch::Tensor& output, int 
     return st;
 }
 
-void block_on(void* st) { C10_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)st)); }
+// the blocking operators wait with the GIL released, so other Python threads run
+// while the kernel does (the reference holds it, bindings/pybind_module.cpp:18-49)
+void block_on(void* st) {
+    cudaError_t e;
+    {
+        py::gil_scoped_release nogil;
+        e = cudaStreamSynchronize((cudaStream_t)st);
+    }
+    C10_CUDA_CHECK(e);
+}
 
 
 
@@ -215,6 +243,13 @@ kivi_layer layer_of(const torch::Tensor& k_packed, const torch::Tensor& k_scales
                 "k_res must be Float or BFloat16 but got ", torch::toString(k_res.scalar_type()));
     check_tensor(k_res, "k_res", k_res.scalar_type());
     check_tensor(v_res, "v_res", k_res.scalar_type());
+    check_same_device(k_res, "k_res", v_res, "v_res");
+    check_same_device(k_res, "k_res", k_packed, "k_packed");
+    check_same_device(k_res, "k_res", k_scales, "k_scales");
+    check_same_device(k_res, "k_res", k_zeros, "k_zeros");
+    check_same_device(k_res, "k_res", v_packed, "v_packed");
+    check_same_device(k_res, "k_res", v_scales, "v_scales");
+    check_same_device(k_res, "k_res", v_zeros, "v_zeros");
     const int64_t units = k_res.size(0), R = k_res.size(1), D = k_res.size(2);
     const int G = group_size;
     TORCH_CHECK(G > 0 && G % 4 == 0, "group_size must be positive and divisible by 4, got ", G);
@@ -315,10 +350,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("append_and_flush",
           [](T new_k, T new_v, T k_packed, T k_scales, T k_zeros, T v_packed, T v_scales, T v_zeros, T k_res, T v_res,
              int64_t quant_len, int res_start, int res_len, int group_size, int rounding) {
-              c10::cuda::CUDAGuard guard(k_res.device());
               kivi_layer L = layer_of(k_packed, k_scales, k_zeros, v_packed, v_scales, v_zeros, k_res, v_res, group_size);
               const int dt = dtype_code(new_k, "new_k");
               TORCH_CHECK(new_v.scalar_type() == new_k.scalar_type() && new_v.is_cuda(), "new_v must match new_k's dtype and device");
+              check_same_device(k_res, "k_res", new_k, "new_k");
+              check_same_device(k_res, "k_res", new_v, "new_v");
+              c10::cuda::CUDAGuard guard(k_res.device());
               TORCH_CHECK(new_k.dim() == 3 && new_k.sizes() == new_v.sizes() && new_k.size(0) == L.num_units && new_k.size(2) == L.head_dim,
                           "new_k / new_v must be [units, n_new, head_dim]");
               TORCH_CHECK(new_k.stride(2) == 1 && new_v.stride(2) == 1, "the last dimension of new_k / new_v must be contiguous");
@@ -338,19 +375,22 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           [](T q, T k_packed, T k_scales, T k_zeros, T v_packed, T v_scales, T v_zeros, T k_res, T v_res,
              int64_t quant_len, int res_start, int res_len, T out, int group_size, c10::optional<T> workspace,
              double sm_scale, int num_splits, int path) {
-              c10::cuda::CUDAGuard guard(k_res.device());
               kivi_layer L = layer_of(k_packed, k_scales, k_zeros, v_packed, v_scales, v_zeros, k_res, v_res, group_size);
               const int qd = dtype_code(q, "q"), od = dtype_code(out, "out");
+              check_same_device(k_res, "k_res", q, "q");
+              check_same_device(k_res, "k_res", out, "out");
+              if (workspace.has_value()) check_same_device(k_res, "k_res", *workspace, "workspace");
+              c10::cuda::CUDAGuard guard(k_res.device());
               TORCH_CHECK(q.is_contiguous() && out.is_contiguous(), "q and out must be contiguous");
               TORCH_CHECK(q.numel() == out.numel() && q.numel() % ((int64_t)L.num_units * L.head_dim) == 0 && q.numel() > 0,
                           "q and out must both hold units * n_rep * head_dim elements");
               const int n_rep = (int)(q.numel() / ((int64_t)L.num_units * L.head_dim));
               const size_t need = kivi_decode_attention_workspace(L.num_units, n_rep, L.head_dim, num_splits);
               T ws = workspace.has_value() ? *workspace
-                                           : torch::empty({(int64_t)need}, torch::TensorOptions().dtype(torch::kUInt8).device(q.device()));
+                                           : torch::empty({(int64_t)need}, torch::TensorOptions().dtype(torch::kUInt8).device(k_res.device()));
               check_tensor(ws, "workspace", torch::kUInt8);
               check(kivi_decode_attention(&L, quant_len, res_start, res_len, q.data_ptr(), qd, out.data_ptr(), od, n_rep,
-                                          (float)sm_scale, ws.data_ptr(), (size_t)ws.numel(), num_splits, path, stream_of(q)));
+                                          (float)sm_scale, ws.data_ptr(), (size_t)ws.numel(), num_splits, path, stream_of(k_res)));
           },
           "Fused decode attention over a layer's packed cache: out = softmax(q K^T * sm_scale) V over [quantized history || "
           "residual ring] (the math of tests/integration/test_attention_fix.py:40-43), no dequantized cache is built.  "

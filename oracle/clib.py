@@ -16,9 +16,20 @@ _f32 = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 _u8 = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
 
 
+def reference_dir():
+    """Where the reference project's tree is: $KIVI_REFERENCE_DIR, else a
+    checkout named ``reference`` next to this repository; None when neither
+    exists (the reference-derived checker is then not rebuilt)."""
+    cand = os.environ.get("KIVI_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isdir(cand) else None
+
+
 def build(reference=None):
-    reference = reference or os.environ.get("KIVI_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
-    subprocess.run(["make", "-s", "-C", _HERE, f"REFERENCE={reference}"], check=True)
+    reference = reference or reference_dir()
+    cmd = ["make", "-s", "-C", _HERE]
+    if reference:
+        cmd.append(f"REFERENCE={reference}")
+    subprocess.run(cmd, check=True)
 
 
 def c_port():

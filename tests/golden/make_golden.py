@@ -26,8 +26,12 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("KIVI_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
 sys.path.insert(0, REPO)
+from oracle import clib  # noqa: E402
+
+REF = sys.argv[1] if len(sys.argv) > 1 else clib.reference_dir()
+if not REF:
+    sys.exit("usage: make_golden.py <reference tree>  (or set KIVI_REFERENCE_DIR)")
 
 
 def _load(path, name):
@@ -38,7 +42,6 @@ def _load(path, name):
 
 
 def main():
-    from oracle import clib
     clib.build(REF)
     cpu_sim = _load(os.path.join(REF, "examples", "cpu_sim.py"), "ref_cpu_sim")
     sys.path.insert(0, os.path.join(REF, "src"))

@@ -1,8 +1,11 @@
 """GPU parity of the device-resident cache and the fused decode attention,
 through the C ABI, against the oracle and the reference-made golden vectors.
 
-Tolerances (relative = max|out-ref| / max|ref| per (unit, head) row):
-fp32 activations 1e-5; bf16 activations 2e-3."""
+Tolerances: fp32 activations 1e-5; bf16 activations 2e-3, on the error of a
+(unit, head) output row relative to the row's largest reference element,
+max|out-ref| / max|ref| (`rel_err`).  The tests also print the element-wise
+figure max |out-ref| / max(|ref|, 1e-3 * max|ref| of the row) (`elem_err`),
+which weighs the same absolute error against each element's own magnitude."""
 import os
 
 import numpy as np
@@ -28,6 +31,12 @@ def rel_err(out, ref):
     num = (out - ref).abs().amax(dim=-1)
     den = ref.abs().amax(dim=-1).clamp_min(1e-30)
     return float((num / den).max())
+
+
+def elem_err(out, ref):
+    out, ref = out.float().cpu(), ref.float().cpu()
+    floor = 1e-3 * ref.abs().amax(dim=-1, keepdim=True).clamp_min(1e-30)
+    return float(((out - ref).abs() / torch.maximum(ref.abs(), floor)).max())
 
 
 def units(x):            # [B,H,T,D] -> [B*H,T,D]
@@ -255,9 +264,10 @@ def test_attention_errors(cabi):
     (3968, 128, 4, 0), (32, 0, 4, 0), (64, 5, 4, 1), (96, 128, 4, 3), (2048 + 32, 100, 4, 5),
     (992, 128, 1, 0), (992, 128, 2, 2), (992, 128, 3, 0), (13 * 32, 96, 4, 13)])
 def test_attention_mma_bf16(cabi, n_quant, n_res, n_rep, splits):
-    err, _, _, _ = _attention_case(cabi, 2, 4, n_rep, 128, 32, 128, n_quant, n_res, torch.bfloat16, 17,
-                                   cabi.ATTN_MMA, num_splits=splits)
-    print(f"[attn mma bf16 q={n_quant} r={n_res} rep={n_rep} splits={splits}] rel err {err:.2e}")
+    err, _, out, ref64 = _attention_case(cabi, 2, 4, n_rep, 128, 32, 128, n_quant, n_res, torch.bfloat16, 17,
+                                         cabi.ATTN_MMA, num_splits=splits)
+    print(f"[attn mma bf16 q={n_quant} r={n_res} rep={n_rep} splits={splits}] rel err {err:.2e}, "
+          f"element-wise {elem_err(out, ref64.float()):.2e}")
     assert err < TOL_BF16
     assert cabi.device_fault() == 0
 
@@ -267,7 +277,9 @@ def test_attention_mma_matches_fp32_kernel_and_auto_dispatch(cabi):
     e_auto, _, o_auto, _ = _attention_case(cabi, 2, 8, 4, 128, 32, 128, 3968, 128, torch.bfloat16, 13, cabi.ATTN_AUTO)
     e_f32, _, o_f32, _ = _attention_case(cabi, 2, 8, 4, 128, 32, 128, 3968, 128, torch.bfloat16, 13, cabi.ATTN_FP32)
     assert torch.equal(o_mma, o_auto)                 # bf16 queries dispatch to the tensor-core kernel
-    print(f"[attn cfg1 slice] mma {e_mma:.2e}  fp32 kernel {e_f32:.2e}  mma vs fp32 kernel {rel_err(o_mma, o_f32):.2e}")
+    _, _, _, ref64 = _attention_case(cabi, 2, 8, 4, 128, 32, 128, 3968, 128, torch.bfloat16, 13, cabi.ATTN_FP32)
+    print(f"[attn cfg1 slice] mma {e_mma:.2e}  fp32 kernel {e_f32:.2e}  mma vs fp32 kernel {rel_err(o_mma, o_f32):.2e}; "
+          f"element-wise: mma {elem_err(o_mma, ref64.float()):.2e}  fp32 kernel {elem_err(o_f32, ref64.float()):.2e}")
     assert e_mma < TOL_BF16 and rel_err(o_mma, o_f32) < TOL_BF16
 
 
@@ -339,7 +351,47 @@ def test_full_size_config2_properties(cabi):
     # oracle on the first KV head of the first batch row
     kk, vv = k[:1].cpu().reshape(1, 1, T, D), v[:1].cpu().reshape(1, 1, T, D)
     ref = ko.kivi_decode_attention(q[:1].cpu().reshape(1, n_rep, D), kk, vv, n_quant, G, "half_away", dtype=torch.float64)
-    assert rel_err(o_auto[:1], ref.float().reshape(1, n_rep, D)) < TOL_BF16
+    r0 = ref.float().reshape(1, n_rep, D)
+    print(f"[cfg2 full size] unit 0 vs oracle: rel err {rel_err(o_auto[:1], r0):.2e}, element-wise {elem_err(o_auto[:1], r0):.2e}")
+    assert rel_err(o_auto[:1], r0) < TOL_BF16
+
+
+def test_full_size_config3_long_context(cabi):
+    """The long-context shape: 32 units x (131072 quantized + 128 ring) tokens,
+    bf16, split count chosen by the library (few units, so every unit is cut into
+    many pieces).  One unit against the CPU oracle in fp64, agreement of the
+    tensor-core and the fp32 kernel on two units, no bounded wait expired."""
+    B, Hkv, n_rep, D, G, R, n_quant, n_res = 4, 8, 4, 128, 32, 128, 131072, 128
+    U, T = B * Hkv, n_quant + n_res
+    g = torch.Generator(device="cuda").manual_seed(321)
+    k = torch.randn(U, T, D, device="cuda", generator=g)
+    k[:, :, 17] *= 10.0
+    k[:, :, 99] *= 10.0
+    k = k.to(torch.bfloat16)
+    v = torch.randn(U, T, D, device="cuda", generator=g)
+    v *= 1.0 + 7.0 * (torch.rand(U, T, 1, device="cuda", generator=g) < 0.02)
+    v = v.to(torch.bfloat16)
+    st = cabi.LayerStore(U, D, G, R, n_quant, torch.bfloat16, "cuda")
+    cabi.load_state(st, k, v, n_quant)
+    q = torch.randn(U, n_rep, D, device="cuda", generator=g).to(torch.bfloat16)
+    o_auto = st.attention(q, n_rep=n_rep, path=cabi.ATTN_MMA, out_dtype=torch.float32)
+    o_s28 = st.attention(q, n_rep=n_rep, path=cabi.ATTN_MMA, num_splits=28, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert cabi.device_fault() == 0 and torch.isfinite(o_auto).all()
+    assert rel_err(o_s28, o_auto) < TOL_BF16
+    sub = slice(U - 2, U)
+    st2 = cabi.LayerStore(2, D, G, R, n_quant, torch.bfloat16, "cuda")
+    cabi.load_state(st2, k[sub], v[sub], n_quant)
+    o_f32 = st2.attention(q[sub].contiguous(), n_rep=n_rep, path=cabi.ATTN_FP32, out_dtype=torch.float32)
+    print(f"[cfg3 full size] tensor-core vs fp32 kernel {rel_err(o_auto[sub], o_f32):.2e}")
+    assert rel_err(o_auto[sub], o_f32) < TOL_BF16
+    u = 5
+    kk, vv = k[u:u + 1].cpu().reshape(1, 1, T, D), v[u:u + 1].cpu().reshape(1, 1, T, D)
+    ref = ko.kivi_decode_attention(q[u:u + 1].cpu().reshape(1, n_rep, D), kk, vv, n_quant, G, "half_away",
+                                   dtype=torch.float64).float().reshape(1, n_rep, D)
+    e_row, e_el = rel_err(o_auto[u:u + 1], ref), elem_err(o_auto[u:u + 1], ref)
+    print(f"[cfg3 full size] unit {u} vs oracle: rel err {e_row:.2e}, element-wise {e_el:.2e}")
+    assert e_row < TOL_BF16
 
 
 def test_full_size_config4_prefill_properties(cabi):

@@ -94,3 +94,63 @@ def test_generate_with_fused_attention_runs_through_flushes():
     a = generate(model, tok, short, max_new_tokens=20, residual_length=128, device="cuda", fused_attention=True)
     b = generate(model, tok, short, max_new_tokens=20, residual_length=128, device="cuda")
     assert a == b
+
+
+def test_fused_attention_hook_matches_oracle_after_flushes():
+    """With a 32-token window the hook flushes every 32 tokens.  Every decode
+    step's attention output (each layer) is compared with the CPU oracle fed the
+    very K/V tensors the model produced: the tokens before the step's
+    quantized length round-tripped group by group, the rest exact."""
+    from kivi_sycl import KiviCache
+    from intel_kivi_hybrid_b200.generation.hf_attention import attached
+    from oracle import kivi_oracle as ko
+    model = _model("cuda")
+    G = R = 32
+    cache = KiviCache.from_model(model, device="cuda", group_size=G, residual_length=R)
+    seen_k = [[] for _ in range(cache.num_layers)]
+    seen_v = [[] for _ in range(cache.num_layers)]
+    calls = []
+    ingest, attend = cache.ingest_layer, cache.decode_attention
+
+    def rec_ingest(layer, k, v):
+        seen_k[layer].append(k.detach().float().cpu()); seen_v[layer].append(v.detach().float().cpu())
+        return ingest(layer, k, v)
+
+    def rec_attend(layer, q, **kw):
+        out = attend(layer, q, **kw)
+        calls.append((layer, q.detach().float().cpu(), out.detach().float().cpu(), cache._quant_token_count[layer]))
+        return out
+
+    cache.ingest_layer, cache.decode_attention = rec_ingest, rec_attend
+    ids = torch.tensor([[3 + i % 90 for i in range(40)]], device="cuda")
+    with torch.no_grad(), attached(model, cache) as pkv:
+        model(ids, past_key_values=pkv, use_cache=True)
+        for i in range(60):
+            model(torch.tensor([[5 + i % 80]], device="cuda"), past_key_values=pkv, use_cache=True)
+    assert len(calls) == 60 * cache.num_layers and cache.total_flushes == 3 * cache.num_layers
+    worst, flushed_steps = 0.0, 0
+    for n, (layer, q, out, n_quant) in enumerate(calls):
+        T = 40 + n // cache.num_layers + 1                      # tokens the cache held when this step attended
+        K = torch.cat(seen_k[layer], dim=2)[:, :, :T]
+        V = torch.cat(seen_v[layer], dim=2)[:, :, :T]
+        assert n_quant % G == 0 and 0 <= T - n_quant < R
+        ref = ko.kivi_decode_attention(q, K, V, n_quant, G, "half_away", dtype=torch.float64).float()
+        err = float(((out - ref).abs().amax(-1) / ref.abs().amax(-1)).max())
+        worst = max(worst, err)
+        flushed_steps += n_quant > 32
+    print(f"[fused hook, {flushed_steps} steps after the second flush] worst rel err vs oracle {worst:.2e}")
+    assert flushed_steps > 0 and worst < 1e-5
+
+
+def test_fused_attention_hook_refuses_chunked_prefill():
+    """Several query tokens on a cache that already holds tokens would ignore the
+    packed history: the hook must raise, not attend over the new tokens alone."""
+    from kivi_sycl import KiviCache
+    from intel_kivi_hybrid_b200.generation.hf_attention import attached
+    model = _model("cuda")
+    ids = torch.tensor([[3 + i % 90 for i in range(24)]], device="cuda")
+    cache = KiviCache.from_model(model, device="cuda", group_size=32, residual_length=128)
+    with torch.no_grad(), attached(model, cache) as pkv:
+        model(ids[:, :12], past_key_values=pkv, use_cache=True)
+        with pytest.raises(RuntimeError, match="chunked prefill"):
+            model(ids[:, 12:], past_key_values=pkv, use_cache=True)

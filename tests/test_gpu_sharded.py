@@ -101,3 +101,54 @@ def test_peer_gather_kernel_world_of_one(tmp_path):
     p = subprocess.run([sys.executable, str(script), ROOT], env=env, stdout=subprocess.PIPE,
                        stderr=subprocess.STDOUT, text=True, timeout=240)
     assert p.returncode == 0 and "ok" in p.stdout, p.stdout
+
+
+def test_peer_wait_that_runs_out_is_reported_and_can_be_cleared():
+    """A bounded device-side wait seen to expire, without any fault: the gather
+    descriptor names a second rank whose buffer and flag array are plain local
+    allocations that nobody ever writes, and the wait is limited to about a
+    millisecond.  The kernel must return, bit 1 of the fault word must be set,
+    this rank's rows must be in both buffers, KiviCache must report the fault,
+    and the word must be clearable."""
+    import time
+    from intel_kivi_hybrid_b200 import cabi
+    from kivi_cuda import KiviCache
+    from oracle import kivi_oracle as ko
+    B, Hkv, n_rep, D, T, nq = 1, 4, 4, 128, 300, 256
+    U = B * Hkv
+    K = ko.make_keys(B, Hkv, T, D, 9).to(torch.bfloat16).reshape(U, T, D).cuda()
+    V = ko.make_values(B, Hkv, T, D, 9).to(torch.bfloat16).reshape(U, T, D).cuda()
+    q = ko.make_queries(B, Hkv * n_rep, D, 9).to(torch.bfloat16).reshape(U, n_rep, D).cuda()
+    st = cabi.LayerStore(U, D, 32, 128, nq, torch.bfloat16, "cuda")
+    cabi.load_state(st, K, V, nq)
+    ref = st.attention(q, n_rep=n_rep, num_splits=2, out_dtype=torch.float32)
+    bufs = [torch.zeros(2 * U, n_rep, D, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(cabi.PEER_MAX_WORLD, dtype=torch.int32, device="cuda") for _ in range(2)]
+    torch.cuda.synchronize()
+    assert cabi.device_fault() == 0
+
+    def expire(epoch):
+        d = cabi.PeerGatherDesc()
+        d.rank, d.world, d.unit_offset, d.epoch, d.wait, d.spin_limit = 0, 2, 0, epoch, 1, 5000
+        for r in range(2):
+            d.out_ptrs[r], d.flag_ptrs[r] = bufs[r].data_ptr(), flags[r].data_ptr()
+        t0 = time.time()
+        st.attention_gather(q, d, torch.float32, n_rep, num_splits=2)
+        torch.cuda.synchronize()
+        return time.time() - t0
+
+    took = expire(1)
+    assert took < 1.0, f"the bounded wait took {took:.2f} s"
+    assert cabi.device_fault() == 2
+    for b in bufs:                                   # this rank's rows reached both ranks' buffers
+        assert torch.equal(b[:U], ref) and not b[U:].any()
+    assert flags[0].tolist()[:2] == [1, 0] and flags[1].tolist()[:2] == [1, 0]
+    cabi.device_fault_clear()
+    assert cabi.device_fault() == 0
+    expire(2)
+    cache = KiviCache(num_layers=1, head_dim=D)
+    with pytest.raises(RuntimeError, match="peer rank did not publish"):
+        cache.check_device_fault()
+    assert cabi.device_fault() == 0                  # reported once, then cleared
+    out = st.attention(q, n_rep=n_rep, num_splits=2, out_dtype=torch.float32)
+    assert torch.equal(out, ref)                     # the context is as usable as before

@@ -212,3 +212,38 @@ def test_merge_token_shards_equals_attention_over_the_whole_sequence():
         lses.append(torch.logsumexp(s[..., a:b], -1))
     got = merge_token_shards(torch.stack(outs).float(), torch.stack(lses).float())
     assert got.dtype == torch.float32 and torch.allclose(got.double(), whole, atol=1e-6)
+
+
+def test_operands_on_different_devices_are_refused_before_any_launch():
+    """A kernel runs on one GPU and must not be handed another GPU's pointers:
+    the binding compares the devices of all tensors of a call on the host.
+    Stand-ins with a .device are enough: nothing is launched."""
+    from intel_kivi_hybrid_b200 import cabi
+
+    class T:
+        is_cuda = True
+
+        def __init__(self, device):
+            self.device = torch.device(device)
+
+        def is_contiguous(self):
+            return True
+
+    cabi._dev(T("cuda:0"), T("cuda:0"))
+    with pytest.raises(RuntimeError, match="same device"):
+        cabi._dev(T("cuda:0"), T("cuda:0"), T("cuda:1"))
+    with pytest.raises(RuntimeError, match="same device"):
+        cabi.quantize_keys(T("cuda:0"), T("cuda:1"), T("cuda:0"), T("cuda:0"), 32)
+
+
+def test_peer_gather_descriptor_layout_matches_the_header():
+    """struct kivi_peer_gather as ctypes sees it: the C compiler's layout of the
+    header's fields (two ints, 2 x 8 pointers, int64, four 32-bit words)."""
+    from intel_kivi_hybrid_b200 import cabi
+    d = cabi.PeerGatherDesc
+    assert d.out_ptrs.offset == 8 and d.flag_ptrs.offset == 8 + 8 * cabi.PEER_MAX_WORLD
+    assert d.unit_offset.offset == 8 + 16 * cabi.PEER_MAX_WORLD
+    assert (d.epoch.offset, d.wait.offset, d.spin_limit.offset) == (d.unit_offset.offset + 8, d.unit_offset.offset + 12,
+                                                                    d.unit_offset.offset + 16)
+    import ctypes
+    assert ctypes.sizeof(d) == d.unit_offset.offset + 24

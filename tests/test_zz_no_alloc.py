@@ -40,10 +40,9 @@ def test_noalloc_entry_point_matches_workspace_entry_point():
         st.attention_noalloc(q, out2, n_rep, path=path)
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before           # nothing went through torch's allocator
-        tol = 1e-6                                               # same kernels, same split plan
+        # same kernels, same split plan, same order of additions: identical bits
         assert torch.isfinite(out1).all() and torch.isfinite(out2).all()
-        assert (out1 - ref).abs().max() <= tol * ref.abs().max()
-        assert (out2 - ref).abs().max() <= tol * ref.abs().max()
+        assert torch.equal(out1, ref) and torch.equal(out2, ref)
     assert cabi.device_fault() == 0
 
 
