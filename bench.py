@@ -3,13 +3,16 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload cfg2|cfg1|cfg3|small] [--path auto|fp32|mma]
+                    [--scaling strong|weak] [--gather auto|peer|nccl]
 
 One "step" = one layer-step of fused decode attention over the packed cache of
 the workload (B*Hkv units, Sq quantized + Sr residual tokens each); on one GPU
 the steps are replayed from a CUDA graph (one pass over the rotating layer
-buffers per replay), so small workloads are not bound by host launch overhead.  At N GPUs
-every rank holds the workload's units (weak scaling: global batch = N * B) and
-the per-layer outputs are all-gathered over NCCL.  Prints ONE JSON line.
+buffers per replay), so small workloads are not bound by host launch overhead.
+At N GPUs the (batch, kv_head) units are sharded over the ranks and the
+per-layer outputs all-gathered: --scaling strong (default) keeps the workload's
+global batch and gives every rank 1/N of its units, --scaling weak gives every
+rank the whole workload (global batch = N * B).  Prints ONE JSON line.
 
 metric: 2-bit KV decode-attention HBM GB/s = algorithmic bytes / time, where
 algorithmic bytes = units*[Sq*(D/2 + 16*D/G) + Sr*2*D*T] + 2*B*Hq*D*T.
@@ -29,9 +32,9 @@ sys.path.insert(0, ROOT)
 
 WORKLOADS = {
     # name: (B, Hkv, n_rep, D, G, R, n_quant, n_res)
-    "cfg2": (64, 8, 4, 128, 32, 128, 32640, 128),    # BASELINE configs[2]: B=64, 32k context
-    "cfg1": (16, 8, 4, 128, 32, 128, 3968, 128),     # configs[1]: B=16, 4096 context
-    "cfg3": (4, 8, 4, 128, 32, 128, 131072, 128),    # configs[3]: B=4, 128k context
+    "cfg2": (64, 8, 4, 128, 32, 128, 32640, 128),    # Llama-3-8B shape, batch 64, 32k context: the headline workload
+    "cfg1": (16, 8, 4, 128, 32, 128, 3968, 128),     # same shape, batch 16, 4096-token context
+    "cfg3": (4, 8, 4, 128, 32, 128, 131072, 128),    # same shape, batch 4, 128k-token context
     "small": (2, 8, 4, 128, 32, 128, 992, 128),
     "long": (2, 8, 4, 128, 32, 128, 65536, 128),     # few units, long history: profiling case
     "mid": (16, 8, 4, 128, 32, 128, 16384, 128),
@@ -42,6 +45,24 @@ LAYERS = 32          # Llama-3-8B depth, for the tokens/s figure
 
 def alg_bytes(B, Hkv, n_rep, D, G, n_quant, n_res, tbytes=2):
     return B * Hkv * (n_quant * (D // 2 + 16 * D // G) + n_res * 2 * D * tbytes) + 2 * B * Hkv * n_rep * D * tbytes
+
+
+NOMINAL_HBM_GBS = 8000.0          # the ~8 TB/s the target is quoted on
+MIN_TIMED_SECONDS = 0.25          # the timed region is repeated until it is at least this long
+
+
+def traffic_factor():
+    """DRAM bytes of the attention kernel per algorithmic byte, as measured with
+    ncu: read from the line `dram_traffic_over_algorithmic: <x>` of the kernel's
+    profile summary, so the number is stated in one place only."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "attn_mma_kernel_prof.md")) as f:
+            for line in f:
+                if line.startswith("dram_traffic_over_algorithmic:"):
+                    return float(line.split(":")[1].split()[0])
+    except Exception:
+        pass
+    return None
 
 
 def peaks():
@@ -100,11 +121,10 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def make_unit_tensors(B, Hkv, T, D, seed, device, dtype):
-    """Seeded synthetic K/V [B*Hkv, T, D] generated on the device: N(0,1); keys
+def make_unit_tensors(U, T, D, seed, device, dtype):
+    """Seeded synthetic K/V [U, T, D] generated on the device: N(0,1); keys
     with 4 outlier channels per head x10, values with 2% of tokens x8."""
     g = torch.Generator(device=device).manual_seed(seed)
-    U = B * Hkv
     k = torch.empty(U, T, D, device=device, dtype=dtype)
     v = torch.empty(U, T, D, device=device, dtype=dtype)
     step = max(1, (1 << 28) // (T * D))
@@ -120,6 +140,11 @@ def make_unit_tensors(B, Hkv, T, D, seed, device, dtype):
         v[u0:u1] = (vv * tokm[:, :, None]).to(dtype)
         del kk, vv
     return k, v
+
+
+def unit_bytes(U, n_rep, D, G, n_quant, n_res, tbytes=2):
+    """alg_bytes() for U (batch, kv_head) units."""
+    return U * (n_quant * (D // 2 + 16 * D // G) + n_res * 2 * D * tbytes) + 2 * U * n_rep * D * tbytes
 
 
 def cpu_attention_sample(B_s, Hkv, n_rep, D, G, n_quant, n_res, iters, threads):
@@ -168,7 +193,8 @@ def run_reference(args, wl):
     sample = f"B={B_s} of {B} batch rows (Hkv={Hkv}, {n_quant}+{n_res} tokens), scaled by bytes"
     line = {"impl": "reference", "metric": "kivi_2bit_decode_attention_hbm_gbs", "value": gbs, "unit": "GB/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": t * 1e3 * (B / B_s), "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": t * 1e3 * (B / B_s), "higher_is_better": True,
+            "scaling": "strong" if args.gpus > 1 and args.scaling == "strong" else "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "B_per_gpu": B, "Hkv": Hkv, "Hq": Hkv * n_rep, "D": D, "G": G,
                        "n_quant": n_quant, "n_res": n_res,
@@ -180,6 +206,7 @@ def run_reference(args, wl):
 
 def run_ours(args, wl):
     from intel_kivi_hybrid_b200 import cabi
+    from intel_kivi_hybrid_b200.parallel import unit_partition
     import torch.distributed as dist
     B, Hkv, n_rep, D, G, R, n_quant, n_res = wl
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -193,12 +220,20 @@ def run_ours(args, wl):
     sampler = ClockSampler(local) if rank == 0 else None     # started early: nvidia-smi needs a moment to come up
     dtype = torch.bfloat16
     path = {"auto": cabi.ATTN_AUTO, "fp32": cabi.ATTN_FP32, "mma": cabi.ATTN_MMA}[args.path]
-    U = B * Hkv
+    strong = world > 1 and args.scaling == "strong"
+    # strong: the workload's B*Hkv units are split over the ranks; weak: every rank holds all of them
+    U_total = B * Hkv if (strong or world == 1) else world * B * Hkv
+    u0, u1 = unit_partition(U_total, rank, world)
+    U = u1 - u0
+    assert U > 0, f"{U_total} units cannot be spread over {world} ranks"
     T = n_quant + n_res
-    # two layer-sized stores are rotated so no step finds its inputs in L2
-    n_buf = 2 if alg_bytes(*wl[:5], n_quant, n_res) > (1 << 29) else 8
+    by_rank = unit_bytes(U, n_rep, D, G, n_quant, n_res)
+    by_total = unit_bytes(U_total, n_rep, D, G, n_quant, n_res)
+    # layer-sized stores are rotated so no step finds its inputs in L2
+    n_buf = 2 if by_rank > (1 << 29) else 8
     stores = []
-    k, v = make_unit_tensors(B, Hkv, T, D, 1000 + rank, dev, dtype)
+    k, v = make_unit_tensors(U, T, D, 1000 + rank, dev, dtype)
+    k0, v0 = k[:1].cpu(), v[:1].cpu()             # this rank's first unit, kept for the oracle check
     for i in range(n_buf):
         st = cabi.LayerStore(U, D, G, R, n_quant, dtype, dev)
         if i == 0:
@@ -210,61 +245,81 @@ def run_ours(args, wl):
         stores.append(st)
     del k, v
     torch.cuda.empty_cache()
-    q = torch.randn(U, n_rep, D, device=dev, generator=torch.Generator(device=dev).manual_seed(7)).to(dtype)
+    q = torch.randn(U, n_rep, D, device=dev, generator=torch.Generator(device=dev).manual_seed(7 + rank)).to(dtype)
     out = torch.empty_like(q)
-    gathered = torch.empty(world * U, n_rep, D, device=dev, dtype=dtype) if world > 1 else None
+    gathered = torch.empty(U_total, n_rep, D, device=dev, dtype=dtype) if world > 1 else None
+    equal_shards = U * world == U_total
     # the exchange of a step: an NCCL all-gather after the kernels, or the
     # attention's last kernel storing its rows into every rank's buffer itself
-    pg = None
+    pg, gather_note = None, None
+    wait_stats = torch.zeros(2, dtype=torch.int64, device=dev)
     if world > 1 and args.gather in ("peer", "auto"):
         from intel_kivi_hybrid_b200.parallel import PeerGather
         try:                                   # raises on every rank or on none
-            pg = PeerGather(world * U, n_rep, D, dtype, rank, world)
+            pg = PeerGather(U_total, n_rep, D, dtype, rank, world)
         except RuntimeError as exc:
-            if rank == 0:
-                print(f"[bench] {exc}; falling back to the NCCL all-gather", file=sys.stderr)
-        if pg is not None:
-            # self-check before anything is timed: two fused steps (both halves of the
-            # double buffer) must reproduce the NCCL all-gather bit for bit on every
-            # rank with no wait having run out; otherwise all ranks use NCCL
-            ok = 1
-            try:
-                stores[0].attention(q, out=out, n_rep=n_rep, path=path, num_splits=args.splits)
-                dist.all_gather_into_tensor(gathered, out)
-                for _ in range(2):
-                    stores[0].attention_gather(q, pg.descriptor(), dtype, n_rep, path=path, num_splits=args.splits)
-                    torch.cuda.synchronize()
-                    ok &= int(torch.equal(pg.gathered(), gathered))
-                ok &= int(cabi.device_fault() == 0)
-            except RuntimeError as exc:
-                print(f"[bench] rank {rank}: fused gather failed its self-check: {exc}", file=sys.stderr)
-                ok = 0
-            t_ok = torch.tensor([ok], device=dev)
-            dist.all_reduce(t_ok, op=dist.ReduceOp.MIN)
-            if int(t_ok.item()) == 0:
-                if rank == 0:
-                    print("[bench] fused gather failed its self-check; using the NCCL all-gather", file=sys.stderr)
-                pg.close()
-                pg = None
+            gather_note = f"peer-gather setup failed ({exc}); NCCL all-gather used"
+    if world > 1 and not equal_shards and pg is None:
+        raise SystemExit("ragged unit shards need --gather peer/auto (the NCCL path uses all_gather_into_tensor)")
 
-    def attend(store, q=q):
+    def attend(store, q=q, stats=None):
         if pg is not None:
-            store.attention_gather(q, pg.descriptor(), dtype, n_rep, path=path, num_splits=args.splits)
-            return pg.gathered()[rank * U:(rank + 1) * U]
+            store.attention_gather(q, pg.descriptor(wait_stats=stats), dtype, n_rep, path=path, num_splits=args.splits)
+            return pg.gathered()
         store.attention(q, out=out, n_rep=n_rep, path=path, num_splits=args.splits)
         if world > 1:
             dist.all_gather_into_tensor(gathered, out)
+            return gathered
         return out
-
-    def step(i):
-        attend(stores[i % n_buf])
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
+    # ---- parity, before anything is timed ------------------------------------------
+    # (1) this rank's first unit against the CPU oracle in fp64 (rank 0's figure is
+    #     reported); (2) at N > 1 the gathered rows of every rank must be bit for bit
+    #     what that rank computes alone, for the exchange in use and, with the fused
+    #     exchange, on both halves of its double buffer.  A fused exchange that fails
+    #     (2) is replaced by the NCCL all-gather on every rank, and the line says so.
+    from oracle import kivi_oracle as ko            # the checker, never the thing measured
+    alone = stores[0].attention(q, n_rep=n_rep, path=path, num_splits=args.splits).clone()
+    ref = ko.kivi_decode_attention(q[:1].cpu().reshape(1, n_rep, D), k0.reshape(1, 1, T, D), v0.reshape(1, 1, T, D),
+                                   n_quant, G, "half_away", dtype=torch.float64).float().reshape(n_rep, D)
+    rel = lambda got: float(((got.float().cpu() - ref).abs().amax(-1) / ref.abs().amax(-1)).max())
+    # the kernel's own error (fp32 output) and what the bf16 output of the timed steps adds (half an ulp: 2e-3)
+    oracle_err = rel(stores[0].attention(q, n_rep=n_rep, path=path, num_splits=args.splits, out_dtype=torch.float32)[0])
+    oracle_err_bf16_out = rel(alone[0])
+    gather_ok = None
+    if world > 1:
+        def gathered_equals_alone():
+            ok = 1
+            for _ in range(2):
+                g = attend(stores[0])
+                torch.cuda.synchronize()
+                ok &= int(torch.equal(g[u0:u1], alone))
+            ok &= int(cabi.device_fault() == 0)
+            t_ok = torch.tensor([ok], device=dev)
+            dist.all_reduce(t_ok, op=dist.ReduceOp.MIN)
+            return bool(t_ok.item())
+        try:
+            gather_ok = gathered_equals_alone()
+        except RuntimeError as exc:
+            print(f"[bench] rank {rank}: exchange failed its self-check: {exc}", file=sys.stderr)
+            gather_ok = False
+        if not gather_ok and pg is not None and equal_shards:
+            gather_note = "fused exchange failed its bitwise self-check; NCCL all-gather used"
+            pg.close()
+            pg = None
+            cabi.device_fault_clear()
+            gather_ok = gathered_equals_alone()
+    del k0, v0
+
+    def step(i, stats=None):
+        attend(stores[i % n_buf], stats=stats)
+
+    for i in range(max(3, args.warmup)):
         step(i)
     launches_per_step = cabi.lib.kivi_last_launch_count()
     barrier()
@@ -291,36 +346,71 @@ def run_ours(args, wl):
             print(f"[bench] CUDA graph capture failed ({exc}); timing plain launches", file=sys.stderr)
             graph = None
             torch.cuda.synchronize()
+
+    def timed(n_steps, use_graph, stats=None, fn=None):
+        """(total ms, sorted per-step ms) of n_steps steps, CUDA events on the launching stream."""
+        fn = fn or (lambda i: step(i, stats))
+        if use_graph:
+            reps = max(1, (n_steps + n_buf - 1) // n_buf)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+            ev[0].record()
+            for i in range(reps):
+                graph.replay()
+                ev[i + 1].record()
+            barrier()
+            per = sorted(ev[i].elapsed_time(ev[i + 1]) / n_buf for i in range(reps))
+            return ev[0].elapsed_time(ev[-1]) * n_steps / (reps * n_buf), per
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(n_steps + 1)]
+        ev[0].record()
+        for i in range(n_steps):
+            fn(i)
+            ev[i + 1].record()
+        barrier()
+        return ev[0].elapsed_time(ev[-1]), sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(n_steps))
+
+    # the timed region: exactly --steps steps, repeated until it lasts MIN_TIMED_SECONDS
+    # (the same number of repeats on every rank)
+    est_ms, _ = timed(args.steps, graph is not None)
+    rep = torch.tensor([max(1, int(MIN_TIMED_SECONDS * 1e3 / max(est_ms, 1e-3)) + 1)], device=dev)
+    if world > 1:
+        dist.all_reduce(rep, op=dist.ReduceOp.MAX)
+    n_timed = args.steps * int(rep.item())
     windows = []
+    barrier()
     w0 = time.time()
-    if graph is not None:
-        n_rep_g = max(1, (args.steps + n_buf - 1) // n_buf)          # replays; each = n_buf steps
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(n_rep_g + 1)]
-        ev[0].record()
-        for i in range(n_rep_g):
-            graph.replay()
-            ev[i + 1].record()
-        barrier()
-        windows.append((w0, time.time()))
-        total_ms = ev[0].elapsed_time(ev[-1]) * args.steps / (n_rep_g * n_buf)
-        per = sorted(ev[i].elapsed_time(ev[i + 1]) / n_buf for i in range(n_rep_g))
-    else:
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-        ev[0].record()
-        for i in range(args.steps):
-            step(i)
-            ev[i + 1].record()
-        barrier()
-        windows.append((w0, time.time()))
-        total_ms = ev[0].elapsed_time(ev[-1])
-        per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
+    total_ms, per = timed(n_timed, graph is not None, stats=wait_stats if pg is not None else None)
+    windows.append((w0, time.time()))
     if world > 1:
         t = torch.tensor([total_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t.item())
-    ms_step = total_ms / args.steps
-    by = alg_bytes(B, Hkv, n_rep, D, G, n_quant, n_res)
-    value = world * by / (ms_step * 1e-3) / 1e9
+    ms_step = total_ms / n_timed
+    value = by_total / (ms_step * 1e-3) / 1e9
+
+    extra = {}
+    if world == 1 and graph is not None:
+        ng_ms, ng_per = timed(args.steps, False)
+        extra["ms_per_step_no_graph"] = statistics.median(ng_per)
+    if world > 1:
+        # the same steps without the exchange: what every rank needs for its own units
+        lo_ms, lo_per = timed(args.steps, False, fn=lambda i: stores[i % n_buf].attention(q, out=out, n_rep=n_rep, path=path,
+                                                                                          num_splits=args.splits))
+        t = torch.tensor([statistics.median(lo_per), -statistics.median(lo_per)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ws = wait_stats.clone().double()
+        wait_us = float(ws[0] / max(float(ws[1]), 1.0)) / 1e3
+        tw = torch.tensor([wait_us, -wait_us], device=dev)
+        dist.all_reduce(tw, op=dist.ReduceOp.MAX)
+        slowest, fastest = float(t[0]), -float(t[1])
+        exchange = statistics.median(per) - slowest
+        extra["per_rank"] = {
+            "ms_local_attention_slowest": slowest, "ms_local_attention_fastest": fastest,
+            "ms_step_minus_slowest_local": exchange,
+            "us_wait_for_peers_in_kernel_max": float(tw[0]) if pg is not None else None,
+            "us_wait_for_peers_in_kernel_min": -float(tw[1]) if pg is not None else None,
+            "limiter": ("skew between ranks" if slowest - fastest > max(exchange, 0.0) else
+                        "exchange (peer stores, flags, wait)" if exchange > 0.02 * slowest else "the attention kernel itself"),
+            "note": "local = the same attention without the exchange, launched from Python like the timed steps"}
 
     # ---- end to end: host q + host new K/V token in, host out, every step ----
     # one pinned staging buffer [q | new K token | new V token] and one copy per step
@@ -331,7 +421,7 @@ def run_ours(args, wl):
     d_in = torch.empty(nq + 2 * U * D, device=dev, dtype=dtype)
     q_e2e = d_in[:nq].view(U, n_rep, D)
     d_kv = d_in[nq:].view(2, U, 1, D)
-    h_out = torch.empty(U, n_rep, D, dtype=dtype).pin_memory()
+    h_out = torch.empty(U_total, n_rep, D, dtype=dtype).pin_memory()
     e2e_store = stores[-1]
     # start from "n_quant quantized + (R - G) in the ring" so flushes happen at the real rate (1 step in G)
     e2e_store.quant_len, e2e_store.res_start, e2e_store.res_len = n_quant - G, 0, R - G
@@ -361,15 +451,17 @@ def run_ours(args, wl):
         t = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
-    e2e_val = world * by / (e2e_ms * 1e-3) / 1e9
+    e2e_val = by_total / (e2e_ms * 1e-3) / 1e9
 
     # the timed region can be shorter than one polling period of nvidia-smi: every
     # rank keeps the same step loop running (untimed) for about 1.2 s more -- the
     # same number of steps everywhere, because a step holds a collective
     clocks = None
-    n_extra = int(min(20000, max(args.steps, 1.2e3 / max(ms_step, 1e-3))))
+    n_extra = torch.tensor([int(min(20000, max(args.steps, 1.2e3 / max(ms_step, 1e-3))))], device=dev)
+    if world > 1:
+        dist.all_reduce(n_extra, op=dist.ReduceOp.MAX)
     w0 = time.time()
-    for i in range(n_extra):
+    for i in range(int(n_extra.item())):
         step(i)
         if i % 200 == 199:
             torch.cuda.synchronize()
@@ -381,7 +473,8 @@ def run_ours(args, wl):
         clocks["sampled"] = "timed region plus ~1.2 s of the same step loop right after it"
     if rank == 0:
         peak, which = peaks()
-        achieved = by / (statistics.median(per) * 1e-3) / 1e9
+        achieved = by_rank / (statistics.median(per) * 1e-3) / 1e9
+        tf = traffic_factor()
         cpu = None
         if world == 1 and not args.no_cpu:
             threads = os.cpu_count() or 1
@@ -390,31 +483,40 @@ def run_ours(args, wl):
                    "cores": threads, "kind": "port",
                    "sample": f"B=1 of {B} batch rows, 3 timed passes of the reference CPU path (fp32 attention over "
                              f"the served cache + 1/G flush round trip), median"}
+        exchange_txt = ("" if world == 1 else " by NCCL" if pg is None else
+                        " inside the merge kernel (peer stores over NVLink)")
         line = {"metric": "kivi_2bit_decode_attention_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": args.workload, "B_per_gpu": B, "Hkv": Hkv, "Hq": Hkv * n_rep, "D": D, "G": G,
-                           "n_quant": n_quant, "n_res": n_res, "path": args.path, "layer_buffers_rotated": n_buf,
-                           "cuda_graph": graph is not None,
+                "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": args.workload, "B_global": U_total // Hkv, "units_per_gpu": U, "Hkv": Hkv,
+                           "Hq": Hkv * n_rep, "D": D, "G": G, "n_quant": n_quant, "n_res": n_res, "path": args.path,
+                           "layer_buffers_rotated": n_buf, "cuda_graph": graph is not None,
                            "l2": "inputs larger than L2 (layer buffers rotated)",
-                           "parallelism": f"(batch,kv_head) units x{world}, all-gather of outputs"
-                                          + ("" if world == 1 else " by NCCL" if pg is None else
-                                             " inside the merge kernel (peer stores over NVLink)")},
+                           "parallelism": f"(batch,kv_head) units over {world} GPU(s), all-gather of outputs" + exchange_txt},
+                "timed_steps": n_timed,
                 "ms_per_step_median": statistics.median(per), "ms_per_step_p10": per[len(per) // 10],
                 "ms_per_step_p90": per[min(len(per) - 1, (9 * len(per)) // 10)],
-                "decode_tokens_per_s": world * B / (LAYERS * ms_step * 1e-3),
+                "decode_tokens_per_s": (U_total // Hkv) / (LAYERS * ms_step * 1e-3),
+                "parity": {"oracle_rel_err": oracle_err, "oracle_rel_err_bf16_output": oracle_err_bf16_out,
+                           "oracle_sample": "rank 0, first unit against the fp64 CPU oracle, error of an output row over "
+                                            "the row's largest reference element; bar 2e-3 for the fp32 output",
+                           "gather_bitwise": gather_ok, "gather_note": gather_note},
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                             "peak_source": which, "traffic": by * 1.026,
-                             "note": "achieved = algorithmic bytes / median per-step CUDA-event time (attention kernel + split merge); "
-                                     "traffic = ncu dram bytes of attn_mma_kernel on the 235 MB prof workload (1.026x its "
-                                     "algorithmic bytes), scaled to this launch"},
+                             "peak_source": which, "frac_nominal": achieved / NOMINAL_HBM_GBS,
+                             "nominal_peak": NOMINAL_HBM_GBS,
+                             "traffic": by_rank * tf if tf else None,
+                             "note": "per GPU: achieved = this rank's algorithmic bytes / median per-step CUDA-event time "
+                                     "(attention kernel + split merge); traffic = ncu dram bytes of attn_mma_kernel per "
+                                     "algorithmic byte on the profiling workload (profiles/attn_mma_kernel_prof.md), "
+                                     "scaled to this launch"},
                 "cpu_baseline": cpu,
                 "e2e": {"value": e2e_val, "unit": "GB/s", "ms_per_step": e2e_ms,
-                        "h2d_bytes_per_step": h_in.numel() * 2, "d2h_bytes_per_step": h_out.numel() * 2,
+                        "h2d_bytes_per_step": world * h_in.numel() * 2, "d2h_bytes_per_step": world * h_out.numel() * 2,
                         "note": "host q + new K/V token -> cache update (flush every G steps) -> attention -> host out"},
-                "gpu_launches": args.steps * launches_per_step,
+                "gpu_launches": n_timed * launches_per_step,
                 "device_fault": fault,
                 "clocks": clocks}
+        line.update(extra)
         print(json.dumps(line))
     if pg is not None:
         pg.close()
@@ -423,7 +525,7 @@ def run_ours(args, wl):
 
 
 def run_quantize(args):
-    """--workload cfg4: bulk prefill flush (BASELINE configs[4]): B=8, 32 KV heads,
+    """--workload cfg4: bulk prefill flush (Llama-2-7B MHA shapes): B=8, 32 KV heads,
     D=128, 8192 tokens quantized in one kivi_cache_update call per layer (keys per
     channel over 32-token groups, values per token over 32-channel groups)."""
     from intel_kivi_hybrid_b200 import cabi
@@ -432,7 +534,7 @@ def run_quantize(args):
     U, S, D, G, R = 8 * 32, 8192, 128, 32, 128
     res = {}
     for name, dtype, eb in (("f32", torch.float32, 4), ("bf16", torch.bfloat16, 2)):
-        k, v = make_unit_tensors(8, 32, S, D, 77, dev, dtype)
+        k, v = make_unit_tensors(8 * 32, S, D, 77, dev, dtype)
         st = cabi.LayerStore(U, D, G, R, S, dtype, dev)
         n_flush, ql, rl = cabi.cache_plan(0, 0, S, G, R)
         by = 2 * U * (ql * D * eb + ql * D // 4 + (ql * D // G) * 8) + 2 * U * rl * D * eb * 2
@@ -504,7 +606,7 @@ def run_operators(args):
         del x, out
         torch.cuda.empty_cache()
     U, T, D, G, R = 64, 8192 + 96, 128, 32, 128
-    k, v = make_unit_tensors(8, 8, T, D, 9, dev, torch.bfloat16)
+    k, v = make_unit_tensors(8 * 8, T, D, 9, dev, torch.bfloat16)
     st = cabi.LayerStore(U, D, G, R, T, torch.bfloat16, dev)
     st.update(k, v)
     ko_, vo_ = st.materialize()
@@ -535,6 +637,9 @@ def main():
     ap.add_argument("--gather", default="auto", choices=["auto", "nccl", "peer"],
                     help="N>1: how the attention outputs are all-gathered: by NCCL after the kernels, or by the "
                          "attention's last kernel through peer memory (auto = the latter if it passes a self-check)")
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="N>1: strong = the workload's global batch sharded over the GPUs (the configuration the "
+                         "workloads are defined on), weak = every GPU holds the whole workload")
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["cfg4", "ops"])
     ap.add_argument("--path", default="auto", choices=["auto", "fp32", "mma"])
     ap.add_argument("--splits", type=int, default=0)

@@ -197,6 +197,18 @@ int kivi_cache_import_keys(const kivi_layer* layer, const uint8_t* packed,
 size_t kivi_decode_attention_workspace(int num_units, int n_rep, int head_dim, int num_splits);
 int kivi_decode_attention_max_splits(void);
 
+/* The plan kivi_decode_attention follows for a problem of this shape (host
+ * arithmetic only, nothing is launched): whether the tensor-core kernel runs,
+ * into how many pieces every unit's quantized history is cut (num_splits > 0 is
+ * taken as given, 0 lets the library choose from the number of CTAs the GPU
+ * holds at a time) and how many CTAs per unit take the residual ring.
+ * sms / ctas_per_sm: the SM count and the tensor-core kernel's resident CTAs per
+ * SM to plan for; <= 0 asks the current device (148 and 3 without one).
+ * No counterpart in the reference. */
+int kivi_decode_attention_plan(int num_units, int64_t quant_len, int res_len, int head_dim, int group_size,
+                               int n_rep, int q_dtype, int num_splits, int path, int sms, int ctas_per_sm,
+                               int* tensor_cores_out, int* quant_splits_out, int* residual_parts_out);
+
 int kivi_decode_attention(const kivi_layer* layer, int64_t quant_len, int res_start,
                           int res_len, const void* q, int q_dtype, void* out, int out_dtype,
                           int n_rep, float sm_scale, void* workspace, size_t workspace_bytes,
@@ -282,6 +294,8 @@ typedef struct kivi_peer_gather {
     int wait;
     uint32_t spin_limit; /* polls (about 200 ns each) the wait may take; 0 = about a second */
     uint32_t reserved;
+    uint64_t* wait_stats; /* optional device uint64[2]: the kernel adds the nanoseconds it spent waiting
+                             for the other ranks to [0] and 1 to [1]; NULL = not recorded */
 } kivi_peer_gather;
 
 int kivi_peer_alloc(size_t bytes, void** ptr_out, unsigned char handle_out[64]);
@@ -302,6 +316,23 @@ int kivi_decode_attention_gather(const kivi_layer* layer, int64_t quant_len, int
  * until kivi_device_fault_clear() resets it (current device; synchronises). */
 int kivi_device_fault(int* word_out);
 int kivi_device_fault_clear(void);
+
+/* ------------------------------------------------------------------------
+ * Next-token choice on the device.
+ *
+ * replaces sample_token, src/kivi_sycl/generation/sampling.py:10-25 (torch on
+ * the host there): ids_out[b] = argmax of row b, or with do_sample != 0 one draw
+ * from softmax(logits / max(temperature, 1e-8)) restricted to the entries not
+ * below the top_k-th largest (top_k = 0: no cut; ties with the k-th are kept).
+ * logits: device [batch][row_stride >= vocab] of dtype; ids_out: device int64[batch].
+ * The draw of row b is the inverse CDF, in index order, at the uniform number
+ * (w + 0.5) / 2^32, w = first output word of Philox4x32-10 with key `seed` and
+ * counter (step, b): the same (seed, step) gives the same ids, and a host
+ * restatement can reproduce them.  Ties of the argmax go to the lowest index.
+ * ---------------------------------------------------------------------- */
+int kivi_sample_tokens(const void* logits, int dtype, int batch, int vocab, int64_t row_stride,
+                       float temperature, int top_k, int do_sample, uint64_t seed, uint64_t step,
+                       int64_t* ids_out, void* stream);
 
 /* number of kernels the last successful call on this thread launched */
 int kivi_last_launch_count(void);

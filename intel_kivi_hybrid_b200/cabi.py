@@ -36,7 +36,7 @@ class PeerGatherDesc(_c.Structure):
     """struct kivi_peer_gather of include/kivi_cuda.h."""
     _fields_ = [("rank", _c.c_int32), ("world", _c.c_int32), ("out_ptrs", _vp * PEER_MAX_WORLD),
                 ("flag_ptrs", _vp * PEER_MAX_WORLD), ("unit_offset", _c.c_int64), ("epoch", _c.c_uint32),
-                ("wait", _c.c_int32), ("spin_limit", _c.c_uint32), ("reserved", _c.c_uint32)]
+                ("wait", _c.c_int32), ("spin_limit", _c.c_uint32), ("reserved", _c.c_uint32), ("wait_stats", _vp)]
 
 
 SIGNATURES = {
@@ -58,6 +58,8 @@ SIGNATURES = {
     "kivi_cache_import_keys": (_int, [_c.POINTER(Layer), _vp, _vp, _vp, _i64, _vp]),
     "kivi_decode_attention_workspace": (_c.c_size_t, [_int, _int, _int, _int]),
     "kivi_decode_attention_max_splits": (_int, []),
+    "kivi_decode_attention_plan": (_int, [_int, _i64, _int, _int, _int, _int, _int, _int, _int, _int, _int,
+                                          _c.POINTER(_int), _c.POINTER(_int), _c.POINTER(_int)]),
     "kivi_decode_attention_noalloc": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _int, _vp, _int, _int, _f,
                                              _int, _int, _vp]),
     "kivi_decode_attention": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _int, _vp, _int, _int, _f,
@@ -66,6 +68,7 @@ SIGNATURES = {
                                          _vp, _c.c_size_t, _int, _int, _vp]),
     "kivi_decode_attention_gather": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _int, _c.POINTER(PeerGatherDesc),
                                             _int, _int, _f, _vp, _c.c_size_t, _int, _int, _vp]),
+    "kivi_sample_tokens": (_int, [_vp, _int, _int, _int, _i64, _f, _int, _int, _c.c_uint64, _c.c_uint64, _vp, _vp]),
     "kivi_peer_alloc": (_int, [_c.c_size_t, _c.POINTER(_vp), _c.c_char_p]),
     "kivi_peer_open": (_int, [_c.c_char_p, _c.POINTER(_vp)]),
     "kivi_peer_close": (_int, [_vp]),
@@ -174,6 +177,17 @@ def cache_plan(quant_len, res_len, n_new, G, R):
     f, ql, rl = _int(), _i64(), _int()
     _check(lib.kivi_cache_plan(quant_len, res_len, n_new, G, R, _c.byref(f), _c.byref(ql), _c.byref(rl)))
     return f.value, ql.value, rl.value
+
+
+def attention_plan(num_units, quant_len, res_len, head_dim=128, group_size=32, n_rep=4, q_dtype=BF16, num_splits=0,
+                   path=ATTN_AUTO, sms=0, ctas_per_sm=0):
+    """kivi_decode_attention_plan: (uses the tensor-core kernel, pieces per unit,
+    residual-ring CTAs per unit) for a problem of this shape; sms / ctas_per_sm
+    <= 0 ask the current device."""
+    tc, sp, rp = _int(), _int(), _int()
+    _check(lib.kivi_decode_attention_plan(num_units, quant_len, res_len, head_dim, group_size, n_rep, q_dtype,
+                                          num_splits, path, sms, ctas_per_sm, _c.byref(tc), _c.byref(sp), _c.byref(rp)))
+    return bool(tc.value), sp.value, rp.value
 
 
 class LayerStore:
@@ -286,6 +300,23 @@ class LayerStore:
                                                  q.data_ptr(), _dt(q), out.data_ptr(), _dt(out), n_rep,
                                                  float(sm_scale), num_splits, path, _stream()))
         return out
+
+
+def sample_tokens(logits, temperature=1.0, top_k=0, do_sample=False, seed=0, step=0, out=None):
+    """kivi_sample_tokens: [batch, vocab] fp32 / bf16 device logits (last dim
+    contiguous) -> int64 [batch] device ids, without a host round trip."""
+    assert logits.dim() == 2 and logits.stride(1) == 1
+    if not logits.is_cuda:
+        raise RuntimeError("tensor must be on a CUDA device")
+    if out is None:
+        out = torch.empty(logits.shape[0], dtype=torch.int64, device=logits.device)
+    _dev(out)
+    if out.device != logits.device:
+        raise RuntimeError(f"all tensors of one call must be on the same device, got {logits.device} and {out.device}")
+    _check(lib.kivi_sample_tokens(logits.data_ptr(), _dt(logits), logits.shape[0], logits.shape[1], logits.stride(0),
+                                  float(temperature), int(top_k or 0), int(bool(do_sample)), int(seed) & (2**64 - 1),
+                                  int(step) & (2**64 - 1), out.data_ptr(), _stream()))
+    return out
 
 
 def peer_alloc(nbytes: int):

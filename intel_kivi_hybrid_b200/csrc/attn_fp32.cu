@@ -362,12 +362,21 @@ merge_gather_kernel(const float* __restrict__ part_o, const float* __restrict__ 
     if (!g.wait) return;
     const uint32_t* mine = g.flag_ptrs[g.rank];
     const uint32_t limit = g.spin_limit ? g.spin_limit : kPeerSpinLimit;
-    for (int r = 0; r < g.world; ++r) {
+    uint64_t t0 = 0;
+    if (g.wait_stats) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    bool expired = false;
+    for (int r = 0; r < g.world && !expired; ++r) {
         uint32_t it = 0;
         while ((int32_t)(ld_acquire_sys(mine + r) - g.epoch) < 0) {
-            if (++it > limit) { atomicOr(&g_gather_fault, 2); return; }
+            if (++it > limit) { atomicOr(&g_gather_fault, 2); expired = true; break; }
             __nanosleep(200);
         }
+    }
+    if (g.wait_stats) {
+        uint64_t t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        g.wait_stats[0] += t1 - t0;        // one thread of one CTA per launch, launches are stream-ordered
+        g.wait_stats[1] += 1;
     }
 }
 

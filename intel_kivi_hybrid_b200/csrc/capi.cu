@@ -52,6 +52,8 @@ int attn_mma_ctas_per_sm();
 int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
                  const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
                  int n_res_splits, int res_chunk, float* part_o, float* part_ml, cudaStream_t st);
+int run_sample(const void* logits, int dtype, int batch, int vocab, int64_t row_stride, float temperature, int top_k,
+               int do_sample, uint64_t seed, uint64_t step, int64_t* ids, cudaStream_t st);
 int attn_mma_fault_word(int* out);
 int gather_fault_word(int* out);
 int attn_mma_fault_clear();
@@ -161,41 +163,63 @@ static int plan_splits_fp32(int num_units, int64_t n_groups, int requested) {
     return clamp_splits(s, n_groups);
 }
 
-// Tensor-core kernel: 3 CTAs per SM are resident.  Measured on B200, a CTA
-// costs about c0 = 10 us of fixed time (cold instruction fetch, first bulk
-// copy, the merge of its warps) plus c1 = 0.47 us per token group, so with
-// `slots` resident CTAs the time of s splits per unit is about
-//   units*s*c0/slots + units*n_groups*c1/slots + (c0 + n_groups*c1/s)/2,
-// minimal at s = sqrt(n_groups*c1*slots / (2*units*c0)).
-// One exactly filled wave beats that whenever it exists: if the quantized CTAs
-// of all units fill at least 90 % of the slots without exceeding them, every
-// CTA starts at once and they all end together.  The ring CTAs come first in
-// the grid and last about t_ring = 7 us; if they push the total past one wave,
-// the quantized CTAs that had to wait start that much later, which is weighed
-// against the longer CTAs of one split less (measured at 128k tokens, 32 units:
-// 13 splits 144 us, 12 splits 149 us, 14 splits 179 us, the formula's 36: 150-157 us;
-// at 64k tokens, 16 units: 26 splits 48 us, 27 splits 51 us).
-static int plan_splits_mma(int num_units, int64_t n_groups, int requested, int n_res_splits) {
+// Tensor-core kernel: how many pieces to cut every unit's quantized history into.
+// Evaluates a small cost model for every candidate count and keeps the cheapest
+// (ties: fewer pieces).  `slots` CTAs are resident at a time (SMs x CTAs per SM).
+// Constants in microseconds, fitted to CUDA-event times on B200 at about 1.9 GHz
+// (units x tokens from 16 x 1k to 512 x 32k and 4 x 128k): a CTA costs c0 of
+// fixed time (first copy, query staging, the fold of its warps) plus c1 per token
+// group, a residual-ring CTA t_ring, starting a CTA c_start, folding one more
+// partial per unit c_fold.
+//   * everything resident at once: the time of one CTA;
+//   * the quantized CTAs alone fit, the ring CTAs (first in the grid, short) push
+//     the total past the slots: the CTAs that had to wait start t_ring late;
+//   * several waves: total CTA time over the slots, plus a ragged end of about
+//     a third of a CTA.
+static int plan_splits_mma(int num_units, int64_t n_groups, int requested, int n_res_splits, int sms, int ctas_per_sm) {
     if (n_groups <= 0) return 0;
     if (requested > 0) return clamp_splits(requested, n_groups);
-    int per_sm = attn_mma_ctas_per_sm();
-    if (per_sm <= 0) per_sm = 3;
-    const double slots = (double)per_sm * num_sms();
-    const double c0 = 10.0, c1 = 0.425, t_ring = 7.0;
-    const int64_t s_wave = (int64_t)(slots / num_units);                    // quantized CTAs alone fill one wave
-    if (s_wave >= 1 && (double)(s_wave * num_units) >= 0.9 * slots) {
-        const int64_t s_all = s_wave - n_res_splits;                        // ring CTAs fit into the wave as well
-        auto cta_us = [&](int64_t sp) { return c0 + (double)((n_groups + sp - 1) / sp) * c1; };
-        const double t_wave = cta_us(s_wave) + (n_res_splits > 0 ? t_ring : 0.0);
-        if (s_all >= 1 && cta_us(s_all) <= t_wave) return clamp_splits(s_all, n_groups);
-        return clamp_splits(s_wave, n_groups);
+    const double slots = (double)(ctas_per_sm > 0 ? ctas_per_sm : 3) * (sms > 0 ? sms : 148);
+    const double c0 = 6.0, c1 = 0.36, t_ring = 7.0, c_start = 0.015, c_fold = 0.03, ragged = 0.3;
+    const int64_t s_max = n_groups < kMaxSplitsC ? n_groups : kMaxSplitsC;
+    int best = 1;
+    double best_t = 0.0;
+    for (int64_t s = 1; s <= s_max; ++s) {
+        const double t_cta = c0 + c1 * (double)((n_groups + s - 1) / s);
+        const double quant = (double)num_units * (double)s, ring = (double)num_units * n_res_splits;
+        double t;
+        if (quant + ring <= slots) t = t_cta + c_start * (quant + ring);
+        else if (quant <= slots) t = t_cta + t_ring + c_start * (quant + ring);
+        else t = (quant * t_cta + ring * t_ring) / slots + ragged * t_cta;
+        t += c_fold * (double)s;
+        if (s == 1 || t < best_t - 1e-9) { best = (int)s; best_t = t; }
     }
-    int64_t s = (int64_t)llround(sqrt(0.5 * (double)n_groups * (0.47 / c0) * slots / num_units));
-    if (s < 1) s = 1;
-    const int64_t s_fill = s_wave - n_res_splits;                           // most splits that still fit one wave
-    const double waves = (double)num_units * (double)(s + n_res_splits) / slots;
-    if (waves < 2.0 && s_fill >= 1) s = s_fill;
-    return clamp_splits(s, n_groups);
+    return best;
+}
+
+extern "C" int kivi_decode_attention_plan(int num_units, int64_t quant_len, int res_len, int head_dim, int group_size,
+                                          int n_rep, int q_dtype, int num_splits, int path, int sms, int ctas_per_sm,
+                                          int* tensor_cores_out, int* quant_splits_out, int* residual_parts_out) {
+    KIVI_REQUIRE(num_units > 0 && head_dim > 0 && group_size > 0 && quant_len >= 0 && quant_len % group_size == 0 && res_len >= 0,
+                 "invalid shape");
+    KIVI_REQUIRE(num_splits >= 0 && num_splits <= kMaxSplitsC, "num_splits (%d) outside 0..%d", num_splits, kMaxSplitsC);
+    KIVI_REQUIRE(tensor_cores_out && quant_splits_out && residual_parts_out, "output pointers must be given");
+    const bool shape_ok = head_dim == 128 && group_size == 32 && n_rep >= 1 && n_rep <= 4;
+    const bool use_mma = path == KIVI_ATTN_MMA ? shape_ok : path == KIVI_ATTN_AUTO ? (shape_ok && q_dtype == KIVI_BF16) : false;
+    if (path == KIVI_ATTN_MMA && !shape_ok) {
+        set_error("tensor-core path needs head_dim 128, group_size 32, n_rep <= 4 (got %d, %d, %d)", head_dim, group_size, n_rep);
+        return KIVI_ERR_UNSUPPORTED;
+    }
+    int n_res = res_len > 0 ? 1 : 0, chunk = res_len;
+    if (use_mma) attn_mma_residual_plan(res_len, &n_res, &chunk);
+    const int64_t n_groups = quant_len / group_size;
+    if (sms <= 0) sms = num_sms();
+    if (ctas_per_sm <= 0) ctas_per_sm = attn_mma_ctas_per_sm();
+    *tensor_cores_out = use_mma ? 1 : 0;
+    *quant_splits_out = use_mma ? plan_splits_mma(num_units, n_groups, num_splits, n_res, sms, ctas_per_sm)
+                                : plan_splits_fp32(num_units, n_groups, num_splits);
+    *residual_parts_out = n_res;
+    return KIVI_OK;
 }
 
 static int decode_attention_impl(const kivi_layer* L, int64_t quant_len, int res_start,
@@ -229,7 +253,7 @@ static int decode_attention_impl(const kivi_layer* L, int64_t quant_len, int res
     }
     int n_res_splits = res_len > 0 ? 1 : 0, res_chunk = res_len;
     if (use_mma) attn_mma_residual_plan(res_len, &n_res_splits, &res_chunk);
-    const int nq_splits = use_mma ? plan_splits_mma(L->num_units, n_groups, num_splits, n_res_splits)
+    const int nq_splits = use_mma ? plan_splits_mma(L->num_units, n_groups, num_splits, n_res_splits, num_sms(), attn_mma_ctas_per_sm())
                                   : plan_splits_fp32(L->num_units, n_groups, num_splits);
     const int gps = nq_splits > 0 ? (int)((n_groups + nq_splits - 1) / nq_splits) : 0;
     const int n_splits = nq_splits + n_res_splits;
@@ -370,4 +394,16 @@ extern "C" int kivi_decode_attention_noalloc(const kivi_layer* L, int64_t quant_
                   (unsigned)KIVI_NOALLOC_SCRATCH_BYTES, detail);
     }
     return rc;
+}
+
+// ---- next-token choice -----------------------------------------------------------
+extern "C" int kivi_sample_tokens(const void* logits, int dtype, int batch, int vocab, int64_t row_stride,
+                                  float temperature, int top_k, int do_sample, uint64_t seed, uint64_t step,
+                                  int64_t* ids_out, void* stream) {
+    KIVI_REQUIRE(logits != nullptr && ids_out != nullptr, "logits / ids_out are null");
+    KIVI_REQUIRE(dtype == KIVI_F32 || dtype == KIVI_BF16, "logits dtype must be KIVI_F32 or KIVI_BF16");
+    KIVI_REQUIRE(batch > 0 && vocab > 0 && row_stride >= vocab, "batch (%d), vocab (%d) and row_stride must be positive, row_stride >= vocab", batch, vocab);
+    KIVI_REQUIRE(top_k >= 0, "top_k (%d) is negative; 0 means no cut", top_k);
+    return run_sample(logits, dtype, batch, vocab, row_stride, temperature, top_k, do_sample, seed, step, ids_out,
+                      (cudaStream_t)stream);
 }

@@ -112,15 +112,17 @@ class PeerGather:
         self.epoch = 0
         dist.barrier(group=group)
 
-    def descriptor(self, wait: bool = True, spin_limit: int = 0):
+    def descriptor(self, wait: bool = True, spin_limit: int = 0, wait_stats: torch.Tensor = None):
         """The kivi_peer_gather of the next call (advances the epoch).
         ``spin_limit``: bound of the wait for the other ranks in polls of about
-        200 ns (0 = the library's default, about a second)."""
+        200 ns (0 = the library's default, about a second).  ``wait_stats``: an
+        int64[2] device tensor the kernel adds its waiting time (ns) and 1 to."""
         c = self._cabi
         self.epoch += 1
         d = c.PeerGatherDesc()
         d.rank, d.world, d.unit_offset, d.epoch, d.wait = self.rank, self.world, self.u0, self.epoch, int(wait)
         d.spin_limit = int(spin_limit)
+        d.wait_stats = wait_stats.data_ptr() if wait_stats is not None else None
         half = (self.epoch & 1) * self._buf_bytes
         for r in range(self.world):
             d.out_ptrs[r] = self._ptrs[r] + half

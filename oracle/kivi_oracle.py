@@ -379,3 +379,42 @@ def algorithmic_bytes_attention(B, Hkv, Hq, D, G, n_quant, n_res, t_bytes) -> in
     the full-precision residual window, q in and out."""
     per_tok = D // 2 + 16 * D // G
     return B * Hkv * (n_quant * per_tok + n_res * 2 * D * t_bytes) + 2 * B * Hq * D * t_bytes
+
+
+# --------------------------------------------------------------------------
+# Next-token choice (src/kivi_sycl/generation/sampling.py:10-25) with the
+# counter-based draw of include/kivi_cuda.h: kivi_sample_tokens
+# --------------------------------------------------------------------------
+
+def philox4x32_first_word(seed: int, step: int, row: int) -> int:
+    """First output word of Philox4x32-10 (Salmon et al. 2011) with key = the two
+    halves of ``seed`` and counter = (step lo, step hi, row, 0)."""
+    M = 0xFFFFFFFF
+    c = [step & M, (step >> 32) & M, row & M, 0]
+    k = [seed & M, (seed >> 32) & M]
+    for _ in range(10):
+        p0, p1 = 0xD2511F53 * c[0], 0xCD9E8D57 * c[2]
+        c = [(p1 >> 32) ^ c[1] ^ k[0], p1 & M, (p0 >> 32) ^ c[3] ^ k[1], p0 & M]
+        k = [(k[0] + 0x9E3779B9) & M, (k[1] + 0xBB67AE85) & M]
+    return c[0]
+
+
+def sample_tokens(logits: torch.Tensor, temperature: float, top_k: Optional[int], do_sample: bool,
+                  seed: int = 0, step: int = 0) -> torch.Tensor:
+    """The reference's sample_token with its multinomial draw replaced by the
+    inverse CDF (index order) at u = (w + 0.5) / 2^32, w = philox word of
+    (seed, step, row).  logits [B, V] -> int64 [B]."""
+    x = logits.float()
+    if not do_sample:
+        return x.argmax(dim=-1)
+    x = x / max(temperature, 1e-8)
+    if top_k:
+        kth = x.topk(top_k, dim=-1).values[:, -1:]
+        x = x.masked_fill(x < kth, float("-inf"))
+    w = torch.exp((x - x.amax(dim=-1, keepdim=True)).double())
+    cdf = w.cumsum(dim=-1)
+    out = torch.empty(x.shape[0], dtype=torch.int64)
+    for b in range(x.shape[0]):
+        u = (philox4x32_first_word(seed, step, b) + 0.5) / 4294967296.0
+        out[b] = int(torch.searchsorted(cdf[b], torch.tensor(u * float(cdf[b, -1]), dtype=torch.float64), right=True))
+    return out.clamp_max(x.shape[1] - 1)

@@ -154,3 +154,23 @@ def test_fused_attention_hook_refuses_chunked_prefill():
         model(ids[:, :12], past_key_values=pkv, use_cache=True)
         with pytest.raises(RuntimeError, match="chunked prefill"):
             model(ids[:, 12:], past_key_values=pkv, use_cache=True)
+
+
+def test_generate_stops_at_eos_like_the_reference_loop():
+    """EOS is looked for every few steps on the device-resident ids; the text
+    must still end with the first EOS, as the reference's per-step test gives."""
+    from kivi_sycl import generate
+    model, tok = _model("cuda"), _Tok()
+    prompt = " ".join(str(i % 97) for i in range(3, 23))
+    ids = tok(prompt).input_ids.cuda()
+    with torch.no_grad():
+        plain = model.generate(ids, max_new_tokens=40, do_sample=False, pad_token_id=0)[0].tolist()
+    new = plain[20:]
+    for pos in (0, 5, 11, 17):                      # an EOS at the first token, inside and at the edge of a check window
+        eos = _Tok()
+        eos.eos_token_id = new[pos]
+        first = new.index(new[pos])
+        want = " ".join(str(t) for t in plain[:20 + first + 1])
+        for fused in (False, True):
+            got = generate(model, eos, prompt, max_new_tokens=40, residual_length=128, device="cuda", fused_attention=fused)
+            assert got == want, (pos, fused)

@@ -246,4 +246,23 @@ def test_peer_gather_descriptor_layout_matches_the_header():
     assert (d.epoch.offset, d.wait.offset, d.spin_limit.offset) == (d.unit_offset.offset + 8, d.unit_offset.offset + 12,
                                                                     d.unit_offset.offset + 16)
     import ctypes
-    assert ctypes.sizeof(d) == d.unit_offset.offset + 24
+    assert d.wait_stats.offset == d.unit_offset.offset + 24 and ctypes.sizeof(d) == d.unit_offset.offset + 32
+
+
+def test_attention_split_plan_is_pinned():
+    """kivi_decode_attention_plan is host arithmetic: pin what it chooses for the
+    benchmark shapes on a 148-SM GPU holding 3 CTAs of the tensor-core kernel per
+    SM (units, quantized tokens, ring tokens) -> (tensor cores, pieces, ring CTAs)."""
+    from intel_kivi_hybrid_b200 import cabi
+    plan = lambda *a, **k: cabi.attention_plan(*a, sms=148, ctas_per_sm=3, **k)
+    assert plan(512, 32640, 128) == (True, 4, 1)          # batch 64, 32k context: several waves of ~250-group CTAs
+    assert plan(128, 3968, 128) == (True, 4, 1)           # batch 16, 4k context
+    assert plan(32, 131072, 128) == (True, 13, 1)         # batch 4, 128k context: 13*32 CTAs fill the 444 slots once
+    assert plan(64, 32640, 128) == (True, 12, 1)          # 1/8 of the batch-64 workload (8-GPU shard)
+    assert plan(16, 65536, 128) == (True, 26, 1)
+    assert plan(512, 32640, 128, num_splits=7) == (True, 7, 1)            # a caller-fixed count is taken as given
+    assert plan(512, 32640, 0)[2] == 0 and plan(512, 32640, 1000)[2] == 8  # ring CTAs: none / capped at 8
+    assert plan(4, 64, 0, n_rep=8) == (False, 1, 0)       # n_rep 8: CUDA-core kernel, two groups: one piece
+    assert plan(12, 512, 96, head_dim=64, q_dtype=cabi.F32)[0] is False
+    with pytest.raises(RuntimeError, match="tensor-core path"):
+        plan(12, 512, 96, head_dim=64, path=cabi.ATTN_MMA)
