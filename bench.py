@@ -413,24 +413,28 @@ def run_ours(args, wl):
             "note": "local = the same attention without the exchange, launched from Python like the timed steps"}
 
     # ---- end to end: host q + host new K/V token in, host out, every step ----
-    # one pinned staging buffer [q | new K token | new V token] and one copy per step
-    nq = q.numel()
-    h_in = torch.empty(nq + 2 * U * D, dtype=dtype).pin_memory()
-    h_in[:nq] = q.cpu().reshape(-1)
-    h_in[nq:] = torch.randn(2 * U * D).to(dtype)
-    d_in = torch.empty(nq + 2 * U * D, device=dev, dtype=dtype)
-    q_e2e = d_in[:nq].view(U, n_rep, D)
-    d_kv = d_in[nq:].view(2, U, 1, D)
+    # through the library's host-to-host decode step (one foreign call per step; the
+    # units go in two chunks on separate streams so copies overlap the kernels)
+    h_q = q.cpu().pin_memory()
+    h_k = torch.randn(U, D).to(dtype).pin_memory()
+    h_v = torch.randn(U, D).to(dtype).pin_memory()
     h_out = torch.empty(U_total, n_rep, D, dtype=dtype).pin_memory()
     e2e_store = stores[-1]
     # start from "n_quant quantized + (R - G) in the ring" so flushes happen at the real rate (1 step in G)
     e2e_store.quant_len, e2e_store.res_start, e2e_store.res_len = n_quant - G, 0, R - G
     n_e2e = max(args.steps, G)
+    d_q, d_k, d_v = q.clone(), torch.empty(U, 1, D, device=dev, dtype=dtype), torch.empty(U, 1, D, device=dev, dtype=dtype)
 
     def e2e_step():
-        d_in.copy_(h_in, non_blocking=True)
-        e2e_store.update(d_kv[0], d_kv[1])
-        h_out.copy_(attend(e2e_store, q_e2e), non_blocking=True)
+        if world > 1 and pg is None:                 # NCCL exchange: the collective is issued from Python
+            d_q.copy_(h_q, non_blocking=True); d_k[:, 0].copy_(h_k, non_blocking=True); d_v[:, 0].copy_(h_v, non_blocking=True)
+            e2e_store.update(d_k, d_v)
+            h_out.copy_(attend(e2e_store, d_q), non_blocking=True)
+        elif pg is not None:
+            e2e_store.decode_step_host(h_q, h_k, h_v, h_out, n_rep, num_splits=args.splits, path=path, chunks=1,
+                                       gather=pg.descriptor(), gather_units=U_total)
+        else:
+            e2e_store.decode_step_host(h_q, h_k, h_v, h_out, n_rep, num_splits=args.splits, path=path, chunks=args.e2e_chunks)
         torch.cuda.current_stream().synchronize()
 
     for _ in range(3):
@@ -511,8 +515,11 @@ def run_ours(args, wl):
                                      "scaled to this launch"},
                 "cpu_baseline": cpu,
                 "e2e": {"value": e2e_val, "unit": "GB/s", "ms_per_step": e2e_ms,
-                        "h2d_bytes_per_step": world * h_in.numel() * 2, "d2h_bytes_per_step": world * h_out.numel() * 2,
-                        "note": "host q + new K/V token -> cache update (flush every G steps) -> attention -> host out"},
+                        "h2d_bytes_per_step": world * (h_q.numel() + h_k.numel() + h_v.numel()) * 2,
+                        "d2h_bytes_per_step": world * h_out.numel() * 2,
+                        "note": "pinned host q + new K/V token -> cache update (flush every G steps) -> attention -> "
+                                "pinned host out, one kivi_decode_step_host call per step"
+                                + (f", units in {args.e2e_chunks} chunks on separate streams" if world == 1 else "")},
                 "gpu_launches": n_timed * launches_per_step,
                 "device_fault": fault,
                 "clocks": clocks}
@@ -643,6 +650,7 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["cfg4", "ops"])
     ap.add_argument("--path", default="auto", choices=["auto", "fp32", "mma"])
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--e2e-chunks", type=int, default=2, help="chunks of units the end-to-end step overlaps copies and kernels over")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", dest="graph", action="store_false",
                     help="launch every step from Python instead of replaying a CUDA graph (single GPU only)")

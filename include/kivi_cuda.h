@@ -318,6 +318,34 @@ int kivi_device_fault(int* word_out);
 int kivi_device_fault_clear(void);
 
 /* ------------------------------------------------------------------------
+ * One decode layer-step from and to pinned host memory.
+ *
+ * replaces the cache side of one iteration of the reference's decode loop --
+ * add_tokens() of the step's new token, then serving the cache to the attention
+ * (generation/generate.py:72-77, cache/manager.py:162-290) -- for a host that
+ * holds q and the new K/V token in pinned memory and wants the attention output
+ * back there.  In stream order on `stream`: copy in, kivi_cache_update with one
+ * new token per unit (counters are read from and written back to *quant_len,
+ * *res_start, *res_len), kivi_decode_attention, copy out.  Nothing is
+ * synchronised: wait for `stream` before reading h_out.
+ * h_q, h_out: [num_units][n_rep][D]; h_new_k, h_new_v: [num_units][D]; dtype
+ * applies to q / new K / new V, out_dtype to h_out.  d_stage: device scratch of
+ * kivi_decode_step_stage_bytes().  chunks (1..4): the units are cut into that
+ * many runs handled on separate streams of the library, so one run's copies
+ * overlap another's kernels; every run gets its share of `workspace`
+ * (kivi_decode_attention_workspace of the whole layer is enough).
+ * gather != NULL: the attention is kivi_decode_attention_gather (chunks = 1) and
+ * h_out receives the first gather_units rows of this rank's gathered buffer.
+ * ---------------------------------------------------------------------- */
+size_t kivi_decode_step_stage_bytes(int num_units, int n_rep, int head_dim);
+int kivi_decode_step_host(const kivi_layer* layer, int64_t* quant_len, int* res_start, int* res_len,
+                          const void* h_q, const void* h_new_k, const void* h_new_v, void* h_out,
+                          int dtype, int out_dtype, int n_rep, float sm_scale,
+                          void* d_stage, size_t d_stage_bytes, void* workspace, size_t workspace_bytes,
+                          int num_splits, int path, int rounding, int chunks,
+                          const kivi_peer_gather* gather, int64_t gather_units, void* stream);
+
+/* ------------------------------------------------------------------------
  * Next-token choice on the device.
  *
  * replaces sample_token, src/kivi_sycl/generation/sampling.py:10-25 (torch on

@@ -68,6 +68,10 @@ SIGNATURES = {
                                          _vp, _c.c_size_t, _int, _int, _vp]),
     "kivi_decode_attention_gather": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _int, _c.POINTER(PeerGatherDesc),
                                             _int, _int, _f, _vp, _c.c_size_t, _int, _int, _vp]),
+    "kivi_decode_step_stage_bytes": (_c.c_size_t, [_int, _int, _int]),
+    "kivi_decode_step_host": (_int, [_c.POINTER(Layer), _c.POINTER(_i64), _c.POINTER(_int), _c.POINTER(_int),
+                                     _vp, _vp, _vp, _vp, _int, _int, _int, _f, _vp, _c.c_size_t, _vp, _c.c_size_t,
+                                     _int, _int, _int, _int, _c.POINTER(PeerGatherDesc), _i64, _vp]),
     "kivi_sample_tokens": (_int, [_vp, _int, _int, _int, _i64, _f, _int, _int, _c.c_uint64, _c.c_uint64, _vp, _vp]),
     "kivi_peer_alloc": (_int, [_c.c_size_t, _c.POINTER(_vp), _c.c_char_p]),
     "kivi_peer_open": (_int, [_c.c_char_p, _c.POINTER(_vp)]),
@@ -289,6 +293,29 @@ class LayerStore:
         _check(lib.kivi_decode_attention_gather(_c.byref(self.c), self.quant_len, self.res_start, self.res_len,
                                                 q.data_ptr(), _dt(q), _c.byref(desc), odt, n_rep, float(sm_scale),
                                                 ws.data_ptr(), ws.numel(), num_splits, path, _stream()))
+
+    def decode_step_host(self, h_q, h_new_k, h_new_v, h_out, n_rep, sm_scale=0.0, num_splits=0, path=ATTN_AUTO,
+                         rounding=ROUND_HALF_AWAY, chunks=2, gather=None, gather_units=0):
+        """kivi_decode_step_host: one decode layer-step from pinned host tensors
+        (q [units, n_rep, D], the new K and V token [units, D]) to a pinned host
+        output, stream-ordered on the current stream and not synchronised; the
+        store's counters advance as in update()."""
+        for t in (h_q, h_new_k, h_new_v, h_out):
+            if t.is_cuda or not t.is_pinned() or not t.is_contiguous():
+                raise RuntimeError("decode_step_host needs contiguous pinned host tensors")
+        need = lib.kivi_decode_step_stage_bytes(self.num_units, n_rep, self.D)
+        if getattr(self, "_stage", None) is None or self._stage.numel() < need:
+            self._stage = torch.empty(need, dtype=torch.uint8, device=self.device)
+        ws = self.workspace(n_rep, num_splits)
+        ql, rs, rl = _i64(self.quant_len), _int(self.res_start), _int(self.res_len)
+        _check(lib.kivi_decode_step_host(_c.byref(self.c), _c.byref(ql), _c.byref(rs), _c.byref(rl),
+                                         h_q.data_ptr(), h_new_k.data_ptr(), h_new_v.data_ptr(), h_out.data_ptr(),
+                                         _dt(h_q), _dt(h_out), n_rep, float(sm_scale), self._stage.data_ptr(),
+                                         self._stage.numel(), ws.data_ptr(), ws.numel(), num_splits, path, rounding,
+                                         chunks, _c.byref(gather) if gather is not None else None, gather_units,
+                                         _stream()))
+        self.quant_len, self.res_start, self.res_len = ql.value, rs.value, rl.value
+        return h_out
 
     def attention_noalloc(self, q, out, n_rep, sm_scale=0.0, num_splits=0, path=ATTN_AUTO):
         """kivi_decode_attention_noalloc: same result as attention(), with the

@@ -34,12 +34,12 @@ class DeviceSampler:
             logits = logits.float()
         if logits.stride(-1) != 1:
             logits = logits.contiguous()
-        seed = self.seed
-        if seed is None:
-            seed = int(torch.randint(0, 2 ** 62, (1,)).item()) if do_sample else 0
-        ids = cabi.sample_tokens(logits, temperature, top_k or 0, do_sample, seed, self.step)
-        self.step += 1
-        return ids.unsqueeze(1)
+        if self.seed is None:       # a fresh key per call: the counter stays at 0
+            seed, step = (int(torch.randint(0, 2 ** 62, (1,)).item()) if do_sample else 0), 0
+        else:
+            seed, step = self.seed, self.step
+            self.step += 1
+        return cabi.sample_tokens(logits, temperature, top_k or 0, do_sample, seed, step).unsqueeze(1)
 
 
 _default = None

@@ -483,3 +483,46 @@ def test_attention_lse_combines_token_shards(cabi, dtype, path):
     assert rel_err(merged, ref) < tol
     with pytest.raises(RuntimeError, match="empty cache"):
         cabi.LayerStore(U, D, G, R, 64, dtype, "cuda").attention_lse(qd, n_rep=n_rep)
+
+
+@pytest.mark.parametrize("chunks", [1, 2, 3])
+def test_decode_step_from_host_equals_update_then_attention(cabi, chunks):
+    """kivi_decode_step_host: pinned host q / new token in, pinned host output back.
+    Over 40 steps (one flush inside) the counters, the packed store and the ring
+    must end up bit-identical to update() + attention() called separately; the
+    outputs are bit-identical with one chunk (same split plan) and within the
+    tolerance of the oracle with several."""
+    B, Hkv, n_rep, D, G, R = 2, 4, 4, 128, 32, 128
+    U, T0, steps = B * Hkv, 700, 40
+    K = ko.make_keys(B, Hkv, T0 + steps, D, seed=31).to(torch.bfloat16)
+    V = ko.make_values(B, Hkv, T0 + steps, D, seed=31).to(torch.bfloat16)
+    Kc, Vc = units(K).cuda(), units(V).cuda()
+    a = cabi.LayerStore(U, D, G, R, 1024, torch.bfloat16, "cuda")
+    b = cabi.LayerStore(U, D, G, R, 1024, torch.bfloat16, "cuda")
+    a.update(Kc[:, :T0], Vc[:, :T0]); b.update(Kc[:, :T0], Vc[:, :T0])
+    h_q = torch.empty(U, n_rep, D, dtype=torch.bfloat16).pin_memory()
+    h_k = torch.empty(U, D, dtype=torch.bfloat16).pin_memory()
+    h_v = torch.empty(U, D, dtype=torch.bfloat16).pin_memory()
+    h_out = torch.empty(U, n_rep, D, dtype=torch.float32).pin_memory()
+    worst = 0.0
+    for t in range(T0, T0 + steps):
+        q = ko.make_queries(B, Hkv * n_rep, D, seed=t).to(torch.bfloat16)
+        h_q.copy_(q.reshape(U, n_rep, D)); h_k.copy_(units(K)[:, t]); h_v.copy_(units(V)[:, t])
+        a.decode_step_host(h_q, h_k, h_v, h_out, n_rep, chunks=chunks)
+        b.update(Kc[:, t:t + 1], Vc[:, t:t + 1])
+        ref_out = b.attention(q.reshape(U, n_rep, D).cuda(), n_rep=n_rep, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        assert (a.quant_len, a.res_start, a.res_len) == (b.quant_len, b.res_start, b.res_len)
+        if chunks == 1:
+            assert torch.equal(h_out, ref_out.cpu())
+        else:
+            assert rel_err(h_out, ref_out) < TOL_BF16
+        if t % 13 == 0:
+            ref = ko.kivi_decode_attention(q, K[:, :, :t + 1], V[:, :, :t + 1], a.quant_len, G, "half_away", dtype=torch.float64)
+            worst = max(worst, rel_err(h_out, ref.float().reshape(U, n_rep, D)))
+    assert a.quant_len == 640 and worst < TOL_BF16
+    for name in ("k_codes", "k_scales", "k_zeros", "v_codes", "v_scales", "v_zeros", "k_res", "v_res"):
+        assert torch.equal(getattr(a, name), getattr(b, name)), name
+    assert cabi.device_fault() == 0
+    with pytest.raises(RuntimeError, match="pinned"):
+        a.decode_step_host(h_q.clone(), h_k, h_v, h_out, n_rep)
