@@ -431,10 +431,11 @@ def run_ours(args, wl):
             e2e_store.update(d_k, d_v)
             h_out.copy_(attend(e2e_store, d_q), non_blocking=True)
         elif pg is not None:
-            e2e_store.decode_step_host(h_q, h_k, h_v, h_out, n_rep, num_splits=args.splits, path=path, chunks=1,
-                                       gather=pg.descriptor(), gather_units=U_total)
+            e2e_store.decode_step_host(h_q, h_k, h_v, h_out, n_rep, num_splits=args.splits, path=path,
+                                       direct=not args.e2e_staged, gather=pg.descriptor(), gather_units=U_total)
         else:
-            e2e_store.decode_step_host(h_q, h_k, h_v, h_out, n_rep, num_splits=args.splits, path=path, chunks=args.e2e_chunks)
+            e2e_store.decode_step_host(h_q, h_k, h_v, h_out, n_rep, num_splits=args.splits, path=path,
+                                       chunks=args.e2e_chunks, direct=not args.e2e_staged)
         torch.cuda.current_stream().synchronize()
 
     for _ in range(3):
@@ -519,7 +520,8 @@ def run_ours(args, wl):
                         "d2h_bytes_per_step": world * h_out.numel() * 2,
                         "note": "pinned host q + new K/V token -> cache update (flush every G steps) -> attention -> "
                                 "pinned host out, one kivi_decode_step_host call per step"
-                                + (f", units in {args.e2e_chunks} chunks on separate streams" if world == 1 else "")},
+                                + (f", staged copies in {args.e2e_chunks} chunk(s)" if args.e2e_staged else
+                                   ", kernels reading and writing the pinned buffers directly")},
                 "gpu_launches": n_timed * launches_per_step,
                 "device_fault": fault,
                 "clocks": clocks}
@@ -650,7 +652,9 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["cfg4", "ops"])
     ap.add_argument("--path", default="auto", choices=["auto", "fp32", "mma"])
     ap.add_argument("--splits", type=int, default=0)
-    ap.add_argument("--e2e-chunks", type=int, default=2, help="chunks of units the end-to-end step overlaps copies and kernels over")
+    ap.add_argument("--e2e-staged", action="store_true",
+                    help="end-to-end step through explicit staging copies instead of kernels accessing the pinned host buffers")
+    ap.add_argument("--e2e-chunks", type=int, default=1, help="with --e2e-staged: chunks of units whose copies and kernels overlap")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", dest="graph", action="store_false",
                     help="launch every step from Python instead of replaying a CUDA graph (single GPU only)")

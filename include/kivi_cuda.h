@@ -225,6 +225,15 @@ int kivi_decode_attention_lse(const kivi_layer* layer, int64_t quant_len, int re
                               float* lse_out, int n_rep, float sm_scale, void* workspace,
                               size_t workspace_bytes, int num_splits, int path, void* stream);
 
+/* Folds attention results computed over disjoint token ranges of the same
+ * sequences (a history sharded over GPUs by token groups): parts is device
+ * [n_shards][rows][head_dim + 1] fp32, a row = the shard's output followed by its
+ * log-sum-exp as written by kivi_decode_attention_lse (-inf for a shard that
+ * held no token of the row).  out: device [rows][head_dim] of out_dtype;
+ * lse_out (optional): the combined log-sum-exp.  No counterpart in the reference. */
+int kivi_merge_token_shards(const float* parts, int n_shards, int64_t rows, int head_dim, void* out,
+                            int out_dtype, float* lse_out, void* stream);
+
 /* Decode attention for callers that cannot allocate device memory.
  *
  * No counterpart in the reference.  Some hosts of this library may not call
@@ -329,11 +338,13 @@ int kivi_device_fault_clear(void);
  * *res_start, *res_len), kivi_decode_attention, copy out.  Nothing is
  * synchronised: wait for `stream` before reading h_out.
  * h_q, h_out: [num_units][n_rep][D]; h_new_k, h_new_v: [num_units][D]; dtype
- * applies to q / new K / new V, out_dtype to h_out.  d_stage: device scratch of
- * kivi_decode_step_stage_bytes().  chunks (1..4): the units are cut into that
- * many runs handled on separate streams of the library, so one run's copies
- * overlap another's kernels; every run gets its share of `workspace`
- * (kivi_decode_attention_workspace of the whole layer is enough).
+ * applies to q / new K / new V, out_dtype to h_out.
+ * direct != 0: the kernels read and write the pinned host buffers themselves
+ * (no copy operation; d_stage may be NULL).  direct == 0: explicit copies through
+ * d_stage, device scratch of kivi_decode_step_stage_bytes(); chunks (1..4) then
+ * cuts the units into that many runs handled on separate streams of the library,
+ * so one run's copies overlap another's kernels; every run gets its share of
+ * `workspace` (kivi_decode_attention_workspace of the whole layer is enough).
  * gather != NULL: the attention is kivi_decode_attention_gather (chunks = 1) and
  * h_out receives the first gather_units rows of this rank's gathered buffer.
  * ---------------------------------------------------------------------- */
@@ -342,7 +353,7 @@ int kivi_decode_step_host(const kivi_layer* layer, int64_t* quant_len, int* res_
                           const void* h_q, const void* h_new_k, const void* h_new_v, void* h_out,
                           int dtype, int out_dtype, int n_rep, float sm_scale,
                           void* d_stage, size_t d_stage_bytes, void* workspace, size_t workspace_bytes,
-                          int num_splits, int path, int rounding, int chunks,
+                          int num_splits, int path, int rounding, int chunks, int direct,
                           const kivi_peer_gather* gather, int64_t gather_units, void* stream);
 
 /* ------------------------------------------------------------------------

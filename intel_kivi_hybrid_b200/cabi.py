@@ -68,10 +68,11 @@ SIGNATURES = {
                                          _vp, _c.c_size_t, _int, _int, _vp]),
     "kivi_decode_attention_gather": (_int, [_c.POINTER(Layer), _i64, _int, _int, _vp, _int, _c.POINTER(PeerGatherDesc),
                                             _int, _int, _f, _vp, _c.c_size_t, _int, _int, _vp]),
+    "kivi_merge_token_shards": (_int, [_vp, _int, _i64, _int, _vp, _int, _vp, _vp]),
     "kivi_decode_step_stage_bytes": (_c.c_size_t, [_int, _int, _int]),
     "kivi_decode_step_host": (_int, [_c.POINTER(Layer), _c.POINTER(_i64), _c.POINTER(_int), _c.POINTER(_int),
                                      _vp, _vp, _vp, _vp, _int, _int, _int, _f, _vp, _c.c_size_t, _vp, _c.c_size_t,
-                                     _int, _int, _int, _int, _c.POINTER(PeerGatherDesc), _i64, _vp]),
+                                     _int, _int, _int, _int, _int, _c.POINTER(PeerGatherDesc), _i64, _vp]),
     "kivi_sample_tokens": (_int, [_vp, _int, _int, _int, _i64, _f, _int, _int, _c.c_uint64, _c.c_uint64, _vp, _vp]),
     "kivi_peer_alloc": (_int, [_c.c_size_t, _c.POINTER(_vp), _c.c_char_p]),
     "kivi_peer_open": (_int, [_c.c_char_p, _c.POINTER(_vp)]),
@@ -271,15 +272,17 @@ class LayerStore:
                                          ws.data_ptr(), ws.numel(), num_splits, path, _stream()))
         return out
 
-    def attention_lse(self, q, n_rep=None, sm_scale=0.0, num_splits=0, path=ATTN_AUTO, out_dtype=None):
+    def attention_lse(self, q, n_rep=None, sm_scale=0.0, num_splits=0, path=ATTN_AUTO, out_dtype=None, use_ring=True):
         """attention() plus the natural-log sum of exponentials per (unit, head):
-        returns (out [like q], lse [num_units, n_rep] fp32)."""
+        returns (out [like q], lse [num_units, n_rep] fp32).  use_ring=False
+        attends to the quantized store only (a rank of a sequence-sharded cache
+        that leaves the replicated ring to another rank)."""
         _dev(q)
         n_rep = n_rep or q.numel() // (self.num_units * self.D)
         out = torch.empty(q.shape, dtype=out_dtype or q.dtype, device=q.device)
         lse = torch.empty(self.num_units, n_rep, dtype=torch.float32, device=q.device)
         ws = self.workspace(n_rep, num_splits)
-        _check(lib.kivi_decode_attention_lse(_c.byref(self.c), self.quant_len, self.res_start, self.res_len,
+        _check(lib.kivi_decode_attention_lse(_c.byref(self.c), self.quant_len, self.res_start, self.res_len if use_ring else 0,
                                              q.data_ptr(), _dt(q), out.data_ptr(), _dt(out), lse.data_ptr(), n_rep,
                                              float(sm_scale), ws.data_ptr(), ws.numel(), num_splits, path, _stream()))
         return out, lse
@@ -295,11 +298,12 @@ class LayerStore:
                                                 ws.data_ptr(), ws.numel(), num_splits, path, _stream()))
 
     def decode_step_host(self, h_q, h_new_k, h_new_v, h_out, n_rep, sm_scale=0.0, num_splits=0, path=ATTN_AUTO,
-                         rounding=ROUND_HALF_AWAY, chunks=2, gather=None, gather_units=0):
+                         rounding=ROUND_HALF_AWAY, chunks=1, direct=True, gather=None, gather_units=0):
         """kivi_decode_step_host: one decode layer-step from pinned host tensors
         (q [units, n_rep, D], the new K and V token [units, D]) to a pinned host
         output, stream-ordered on the current stream and not synchronised; the
-        store's counters advance as in update()."""
+        store's counters advance as in update().  direct: the kernels access the
+        host buffers themselves; otherwise staged copies in `chunks` runs."""
         for t in (h_q, h_new_k, h_new_v, h_out):
             if t.is_cuda or not t.is_pinned() or not t.is_contiguous():
                 raise RuntimeError("decode_step_host needs contiguous pinned host tensors")
@@ -312,7 +316,7 @@ class LayerStore:
                                          h_q.data_ptr(), h_new_k.data_ptr(), h_new_v.data_ptr(), h_out.data_ptr(),
                                          _dt(h_q), _dt(h_out), n_rep, float(sm_scale), self._stage.data_ptr(),
                                          self._stage.numel(), ws.data_ptr(), ws.numel(), num_splits, path, rounding,
-                                         chunks, _c.byref(gather) if gather is not None else None, gather_units,
+                                         chunks, int(bool(direct)), _c.byref(gather) if gather is not None else None, gather_units,
                                          _stream()))
         self.quant_len, self.res_start, self.res_len = ql.value, rs.value, rl.value
         return h_out
@@ -327,6 +331,18 @@ class LayerStore:
                                                  q.data_ptr(), _dt(q), out.data_ptr(), _dt(out), n_rep,
                                                  float(sm_scale), num_splits, path, _stream()))
         return out
+
+
+def merge_token_shards(parts, out_dtype=torch.float32):
+    """kivi_merge_token_shards: parts [n_shards, ..., D + 1] fp32 (output rows
+    followed by their log-sum-exp) -> [..., D] of out_dtype."""
+    _dev(parts)
+    assert parts.dtype == torch.float32 and parts.dim() >= 3
+    n, D = parts.shape[0], parts.shape[-1] - 1
+    rows = parts[0].numel() // (D + 1)
+    out = torch.empty(parts.shape[1:-1] + (D,), dtype=out_dtype, device=parts.device)
+    _check(lib.kivi_merge_token_shards(parts.data_ptr(), n, rows, D, out.data_ptr(), _dt(out), None, _stream()))
+    return out
 
 
 def sample_tokens(logits, temperature=1.0, top_k=0, do_sample=False, seed=0, step=0, out=None):
@@ -344,6 +360,42 @@ def sample_tokens(logits, temperature=1.0, top_k=0, do_sample=False, seed=0, ste
                                   float(temperature), int(top_k or 0), int(bool(do_sample)), int(seed) & (2**64 - 1),
                                   int(step) & (2**64 - 1), out.data_ptr(), _stream()))
     return out
+
+
+def quantize_groups_at(store: "LayerStore", k, v, at_group: int, rounding=ROUND_HALF_AWAY):
+    """Quantize whole groups of tokens k, v [num_units, n*G, D] straight into the
+    packed store of ``store`` at groups at_group .. at_group + n - 1, without
+    touching its ring or counters (a view of the layer whose window is one group
+    long, so every token is flushed)."""
+    G = store.G
+    n_tok = k.shape[1]
+    assert n_tok % G == 0 and at_group * G + n_tok <= store.max_tokens
+    if n_tok == 0:
+        return
+    shadow = Layer.from_buffer_copy(store.c)
+    shadow.residual_cap = G
+    ql, rs, rl = _i64(), _int(), _int()
+    _check(lib.kivi_cache_update(_c.byref(shadow), at_group * G, 0, 0, k.data_ptr(), v.data_ptr(), _dt(k),
+                                 k.stride(0), k.stride(1), v.stride(0), v.stride(1), n_tok, rounding,
+                                 _c.byref(ql), _c.byref(rs), _c.byref(rl), _stream()))
+    assert ql.value == at_group * G + n_tok and rl.value == 0
+
+
+def update_discarding_flush(store: "LayerStore", scratch: "LayerStore", new_k, new_v, rounding=ROUND_HALF_AWAY):
+    """store.update() for a rank that does not keep the groups this update
+    flushes: the ring of ``store`` advances exactly as usual, the flushed groups
+    are written to ``scratch``'s packed arrays (group 0 onwards) instead of the
+    store's, and store.quant_len stays as it is."""
+    shadow = Layer.from_buffer_copy(store.c)
+    for name in ("k_codes", "k_scales", "k_zeros", "v_codes", "v_scales", "v_zeros"):
+        setattr(shadow, name, getattr(scratch, name).data_ptr())
+    shadow.max_tokens = scratch.max_tokens
+    ql, rs, rl = _i64(), _int(), _int()
+    _check(lib.kivi_cache_update(_c.byref(shadow), 0, store.res_start, store.res_len, new_k.data_ptr(), new_v.data_ptr(),
+                                 _dt(new_k), new_k.stride(0), new_k.stride(1), new_v.stride(0), new_v.stride(1),
+                                 new_k.shape[1], rounding, _c.byref(ql), _c.byref(rs), _c.byref(rl), _stream()))
+    store.res_start, store.res_len = rs.value, rl.value
+    return ql.value // store.G
 
 
 def peer_alloc(nbytes: int):

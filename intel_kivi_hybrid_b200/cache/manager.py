@@ -19,6 +19,14 @@ With ``shard=(rank, world)`` a process keeps only its contiguous slice of the
 ``gather="nccl"`` with a collective after the kernel, ``gather="peer"`` inside
 the kernel (its last stage stores every row into all ranks' buffers over
 NVLink, ``parallel.PeerGather``).
+
+With ``shard_mode="tokens"`` the *sequence* is sharded instead (fewer units than
+GPUs, or one very long context): every rank holds all units and the replicated
+residual ring, but only its share of each unit's quantized token groups
+(``parallel.TokenShardPlan``); every rank is fed the same new tokens.
+``decode_attention`` attends to the local groups (rank 0 also to the ring),
+all-gathers one (output, log-sum-exp) row per query head and folds the rows
+with ``kivi_merge_token_shards``.
 """
 from typing import List, Optional, Tuple
 
@@ -26,7 +34,7 @@ import torch
 
 from .. import cabi
 from ..config.model_config import detect_model_config
-from ..parallel import PeerGather, all_gather_units, unit_partition
+from ..parallel import PeerGather, TokenShardPlan, all_gather_units, unit_partition
 
 __all__ = ["KiviCache"]
 
@@ -60,8 +68,9 @@ class KiviCache:
     def __init__(self, num_layers: int, head_dim: int, num_kv_heads: Optional[int] = None,
                  device: str = "cuda", group_size: int = 32, residual_length: int = 128,
                  max_tokens: int = 4096, rounding: str = "half_away",
-                 shard: Optional[Tuple[int, int]] = None, gather: str = "nccl"):
+                 shard: Optional[Tuple[int, int]] = None, gather: str = "nccl", shard_mode: str = "units"):
         assert gather in ("nccl", "peer")
+        assert shard_mode in ("units", "tokens")
         assert head_dim % group_size == 0, \
             f"head_dim ({head_dim}) must be divisible by group_size ({group_size})"
         assert group_size >= 4 and group_size % 4 == 0, \
@@ -81,6 +90,12 @@ class KiviCache:
         self.rounding = cabi.ROUND_HALF_AWAY if rounding == "half_away" else cabi.ROUND_HALF_EVEN
         self.shard = shard
         self.gather = gather
+        self.shard_mode = shard_mode
+        # sequence sharding: the plan, the global quantized length per layer and a
+        # one-group scratch store per layer for flushes another rank keeps
+        self._tokens = TokenShardPlan(*shard) if (shard and shard_mode == "tokens" and shard[1] > 1) else None
+        self._global_quant: List[int] = [0] * num_layers
+        self._scratch: List[Optional[cabi.LayerStore]] = [None] * num_layers
         self._peer: dict = {}                              # (n_units, n_rep, dtype) -> PeerGather
         self._capacity = max(max_tokens, group_size)
         self._stores: List[Optional[cabi.LayerStore]] = [None] * num_layers
@@ -101,6 +116,8 @@ class KiviCache:
     # ------------------------------------------------------------------ state views
     @property
     def _quant_token_count(self) -> List[int]:
+        if self._tokens is not None:             # over all ranks, not only the groups kept here
+            return list(self._global_quant)
         return [0 if s is None else s.quant_len for s in self._stores]
 
     def _window(self, i: int, which: str) -> Optional[torch.Tensor]:
@@ -158,8 +175,9 @@ class KiviCache:
             self._latch_shapes(k, i)
             st = self._stores[i]
             new_start = 0
-            if st is not None and st.quant_len + st.res_len > 0:
-                new_start = st.quant_len + st.res_len
+            held = 0 if st is None else (self._global_quant[i] if self._tokens is not None else st.quant_len) + st.res_len
+            if held > 0:
+                new_start = held
                 assert k.shape[2] >= new_start, (
                     f"KiviCache desync at layer {i}: expected past length {new_start} but got {k.shape[2]}. "
                     f"add_tokens() must be called exactly once per forward pass, seeded by get_full_cache().")
@@ -177,12 +195,13 @@ class KiviCache:
             self.num_kv_heads = k.shape[1]
             self._serve_device, self._serve_dtype = k.device, k.dtype
             n_units = self.batch_size * self.num_kv_heads
-            if self.shard:
+            if self.shard and self._tokens is None and self.shard[1] > 1:
                 # a rank without units would never launch, and its peers would wait for it
                 assert n_units >= self.shard[1], (
                     f"{n_units} (batch, kv_head) units cannot be sharded over {self.shard[1]} ranks: "
                     f"every rank must hold at least one unit")
-            self._units = unit_partition(n_units, *self.shard) if self.shard else (0, n_units)
+            self._units = (unit_partition(n_units, *self.shard) if (self.shard and self._tokens is None)
+                           else (0, n_units))
         else:
             assert k.shape[0] == self.batch_size, (
                 f"KiviCache batch size changed mid-session ({self.batch_size} -> {k.shape[0]}) at layer {layer}. "
@@ -199,6 +218,11 @@ class KiviCache:
         u0, u1 = self._units
         nk = new_k.flatten(0, 1)[u0:u1].to(device=self.device, dtype=dtype)
         nv = new_v.flatten(0, 1)[u0:u1].to(device=self.device, dtype=dtype)
+        if self._tokens is not None:
+            flushed = self._ingest_token_sharded(layer, nk, nv, dtype)
+            if flushed:
+                self._flush_count[layer] += flushed
+            return
         st = self._ensure_capacity(layer, n_new, dtype, u1 - u0)
         before = st.quant_len
         st.update(nk, nv, self.rounding)
@@ -208,6 +232,83 @@ class KiviCache:
             # flushed tokens are now served at 2-bit fidelity: the persistent
             # view no longer matches (manager.py:244-249)
             self._cache_view_valid = False
+
+    def _ingest_token_sharded(self, layer: int, nk: torch.Tensor, nv: torch.Tensor, dtype) -> int:
+        """ingest_layer() of a sequence-sharded cache: nk, nv [units, n_new, D], the
+        same on every rank.  Returns the number of groups flushed (globally)."""
+        G, R, plan = self.G, self.R, self._tokens
+        n_units, n_new = nk.shape[0], nk.shape[1]
+        st = self._stores[layer]
+        if st is None:
+            st = self._stores[layer] = self._new_store(n_units, self._capacity, dtype)
+            self._scratch[layer] = self._new_store(n_units, 2 * G, dtype)
+        res_len0 = st.res_len
+        f, gq, rl = cabi.cache_plan(self._global_quant[layer], res_len0, n_new, G, R)
+        if self._global_quant[layer] == 0 and res_len0 == 0 and f > 1:
+            # bulk flush of an empty cache (prefill): contiguous runs of the f groups
+            g0, g1 = plan.bulk_run(f)
+            self._grow_token_store(layer, (g1 - g0) * G, dtype)
+            st = self._stores[layer]
+            cabi.quantize_groups_at(st, nk[:, g0 * G:g1 * G], nv[:, g0 * G:g1 * G], 0, self.rounding)
+            st.quant_len = (g1 - g0) * G
+            st.k_res[:, :rl] = nk[:, f * G:].to(st.dtype)
+            st.v_res[:, :rl] = nv[:, f * G:].to(st.dtype)
+            st.res_start, st.res_len = 0, rl
+            self._global_quant[layer] = gq
+            return f
+        # otherwise feed the tokens in pieces that flush at most one group each
+        flushed, t = 0, 0
+        while t < n_new:
+            piece = min(n_new - t, max(1, R - st.res_len))
+            pk, pv = nk[:, t:t + piece], nv[:, t:t + piece]
+            f1, _, _ = cabi.cache_plan(self._global_quant[layer], st.res_len, piece, G, R)
+            assert f1 <= 1
+            if f1 == 0 or plan.owns(self._global_quant[layer] // G):
+                self._grow_token_store(layer, f1 * G, dtype)
+                st = self._stores[layer]
+                st.update(pk, pv, self.rounding)
+            else:
+                cabi.update_discarding_flush(st, self._scratch[layer], pk, pv, self.rounding)
+            self._global_quant[layer] += f1 * G
+            flushed += f1
+            t += piece
+        return flushed
+
+    def _grow_token_store(self, layer: int, extra_tokens: int, dtype) -> None:
+        """Make room for extra_tokens more locally kept quantized tokens."""
+        st = self._stores[layer]
+        need = st.quant_len + extra_tokens
+        if need <= st.max_tokens:
+            return
+        cap = st.max_tokens
+        while cap < need:
+            cap *= 2
+        big = self._new_store(st.num_units, cap, dtype)
+        ng, nt = st.quant_len // self.G, st.quant_len
+        for name, n in (("k_codes", ng), ("k_scales", ng), ("k_zeros", ng), ("v_codes", nt), ("v_scales", nt), ("v_zeros", nt)):
+            getattr(big, name)[:, :n].copy_(getattr(st, name)[:, :n])
+        big.k_res.copy_(st.k_res); big.v_res.copy_(st.v_res)
+        big.quant_len, big.res_start, big.res_len = st.quant_len, st.res_start, st.res_len
+        self._stores[layer] = big
+
+    def token_shard_partial(self, layer: int, q_units: torch.Tensor, n_rep: int, num_splits: int = 0,
+                            sm_scale: float = 0.0) -> torch.Tensor:
+        """This rank's share of a sequence-sharded attention: [units, n_rep, D + 1]
+        fp32, the output over the token groups kept here (rank 0: and the ring)
+        followed by its log-sum-exp; -inf marks "no token of this row here"."""
+        st = self._stores[layer]
+        use_ring = self._tokens.serves_ring
+        U, D = st.num_units, self.head_dim
+        part = torch.empty(U, n_rep, D + 1, dtype=torch.float32, device=q_units.device)
+        if st.quant_len + (st.res_len if use_ring else 0) == 0:
+            part[..., :D] = 0.0
+            part[..., D] = float("-inf")
+            return part
+        out, lse = st.attention_lse(q_units, n_rep=n_rep, out_dtype=torch.float32, num_splits=num_splits,
+                                    sm_scale=sm_scale, use_ring=use_ring)
+        part[..., :D] = out
+        part[..., D] = lse
+        return part
 
     def decode_attention(self, layer: int, q: torch.Tensor, out_dtype=None, num_splits: int = 0,
                          sm_scale: float = 0.0) -> torch.Tensor:
@@ -226,6 +327,12 @@ class KiviCache:
         n_rep = Hq // self.num_kv_heads
         u0, u1 = self._units
         q_units = q.reshape(B * self.num_kv_heads, n_rep, D)[u0:u1].contiguous()
+        if self._tokens is not None:
+            import torch.distributed as dist
+            part = self.token_shard_partial(layer, q_units, n_rep, num_splits, sm_scale)
+            parts = torch.empty((self._tokens.world,) + tuple(part.shape), dtype=torch.float32, device=part.device)
+            dist.all_gather_into_tensor(parts, part)
+            return cabi.merge_token_shards(parts, out_dtype or q.dtype).reshape(B, Hq, D)
         if self.shard and self.shard[1] > 1 and self.gather == "peer":
             # collective on first use (buffers are exchanged once); the result is a
             # view of this rank's gathered buffer, overwritten two calls later
@@ -236,7 +343,7 @@ class KiviCache:
             st.attention_gather(q_units, pg.descriptor(), pg.dtype, n_rep, sm_scale=sm_scale, num_splits=num_splits)
             return pg.gathered().reshape(B, Hq, D)
         out = st.attention(q_units, n_rep=n_rep, out_dtype=out_dtype, num_splits=num_splits, sm_scale=sm_scale)
-        if self.shard and self.shard[1] > 1:
+        if self.shard and self.shard[1] > 1 and self._tokens is None:
             out = all_gather_units(out, B * self.num_kv_heads, self.shard[0], self.shard[1])
         return out.reshape(B, Hq, D)
 
@@ -294,6 +401,8 @@ class KiviCache:
             self.check_device_fault()
         self._flush_count = [0] * self.num_layers
         self._stores = [None] * self.num_layers
+        self._scratch = [None] * self.num_layers
+        self._global_quant = [0] * self.num_layers
         self.batch_size = None
         self._cache_view = None
         self._cache_view_valid = False

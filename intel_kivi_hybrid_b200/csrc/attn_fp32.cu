@@ -417,6 +417,42 @@ int run_merge(const float* part_o, const float* part_ml, void* out, const kivi_p
     return KIVI_OK;
 }
 
+// ---- token shards: combine attention computed over disjoint token ranges -----------
+// parts [n_shards][rows][D + 1] fp32: D outputs then the natural-log sum of
+// exponentials of the shard (-inf for a shard that attended to nothing).
+// out[row] = sum_i out_i * exp(lse_i - LSE) / sum_i exp(lse_i - LSE); one warp per row.
+__global__ void __launch_bounds__(128)
+merge_token_shards_kernel(const float* __restrict__ parts, int n_shards, int64_t rows, int D,
+                          void* __restrict__ out, int out_dtype, float* __restrict__ lse_out) {
+    const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const int64_t stride = rows * (D + 1);
+    float M = -INFINITY;
+    for (int i = 0; i < n_shards; ++i) M = fmaxf(M, parts[i * stride + row * (D + 1) + D]);
+    float den = 0.0f;
+    for (int i = 0; i < n_shards; ++i) {
+        const float l = parts[i * stride + row * (D + 1) + D];
+        den += (l == -INFINITY) ? 0.0f : expf(l - M);
+    }
+    for (int d = lane; d < D; d += 32) {
+        float acc = 0.0f;
+        for (int i = 0; i < n_shards; ++i) {
+            const float l = parts[i * stride + row * (D + 1) + D];
+            if (l != -INFINITY) acc = fmaf(parts[i * stride + row * (D + 1) + d], expf(l - M), acc);
+        }
+        store_from_float(out, out_dtype, row * D + d, acc / den);
+    }
+    if (lse_out != nullptr && lane == 0) lse_out[row] = M + logf(den);
+}
+
+int run_merge_token_shards(const float* parts, int n_shards, int64_t rows, int D, void* out, int out_dtype,
+                           float* lse_out, cudaStream_t st) {
+    merge_token_shards_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(parts, n_shards, rows, D, out, out_dtype, lse_out);
+    KIVI_LAUNCH_OK();
+    return KIVI_OK;
+}
+
 template <int NREP>
 static int launch_fp32(const kivi_layer* L, int64_t quant_len, int res_start, int res_len,
                        const void* q, int q_dtype, float scale_log2, int nq_splits, int gps,

@@ -54,6 +54,8 @@ int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_
                  int n_res_splits, int res_chunk, float* part_o, float* part_ml, cudaStream_t st);
 int run_sample(const void* logits, int dtype, int batch, int vocab, int64_t row_stride, float temperature, int top_k,
                int do_sample, uint64_t seed, uint64_t step, int64_t* ids, cudaStream_t st);
+int run_merge_token_shards(const float* parts, int n_shards, int64_t rows, int D, void* out, int out_dtype,
+                           float* lse_out, cudaStream_t st);
 int attn_mma_fault_word(int* out);
 int gather_fault_word(int* out);
 int attn_mma_fault_clear();
@@ -406,4 +408,16 @@ extern "C" int kivi_sample_tokens(const void* logits, int dtype, int batch, int 
     KIVI_REQUIRE(top_k >= 0, "top_k (%d) is negative; 0 means no cut", top_k);
     return run_sample(logits, dtype, batch, vocab, row_stride, temperature, top_k, do_sample, seed, step, ids_out,
                       (cudaStream_t)stream);
+}
+
+// ---- sequence sharding: fold per-shard (output, log-sum-exp) rows ----------------------
+extern "C" int kivi_merge_token_shards(const float* parts, int n_shards, int64_t rows, int head_dim, void* out,
+                                       int out_dtype, float* lse_out, void* stream) {
+    KIVI_REQUIRE(parts != nullptr && out != nullptr, "parts / out are null");
+    KIVI_REQUIRE(n_shards >= 1 && rows >= 1 && head_dim >= 1, "n_shards, rows and head_dim must be positive");
+    KIVI_REQUIRE(out_dtype == KIVI_F32 || out_dtype == KIVI_BF16, "out dtype must be KIVI_F32 or KIVI_BF16");
+    KIVI_REQUIRE(rows < ((int64_t)1 << 33), "too many rows");
+    if (int rc = run_merge_token_shards(parts, n_shards, rows, head_dim, out, out_dtype, lse_out, (cudaStream_t)stream)) return rc;
+    note_launches(1);
+    return KIVI_OK;
 }

@@ -1,11 +1,15 @@
 // One decode layer-step fed from and returning to pinned host memory:
-//   host q + the step's new K/V token -> staging copy -> ring append (+ flush on
-//   one step in G) -> fused attention -> copy of the outputs back to the host,
+//   host q + the step's new K/V token -> ring append (+ flush on one step in G)
+//   -> fused attention -> outputs in host memory,
 // as ONE call of the C ABI, so a host loop pays one foreign call per step instead
-// of five, and with the units cut into chunks that run on separate streams, so
-// the copies of one chunk overlap the attention of the other (the copies move
-// about 1.3 MB per step at batch 64 -- tens of microseconds on PCIe that would
-// otherwise be serial with a 0.45 ms kernel).
+// of five.  Two ways to move the data (about 1.3 MB per step at batch 64):
+//   direct  the kernels read q and the new token from, and write the outputs to,
+//           the pinned host buffers themselves (pinned memory is addressable from
+//           the device): no copy operations at all, the bytes cross PCIe while
+//           the kernels run;
+//   staged  explicit copies into a device staging buffer and back, with the units
+//           optionally cut into chunks on separate streams so that one chunk's
+//           copies overlap another's kernels.
 //
 // What it replaces in the reference: the body of one generate() iteration around
 // the model forward -- get_full_cache() + add_tokens() (generation/generate.py:
@@ -78,17 +82,43 @@ extern "C" int kivi_decode_step_host(const kivi_layer* L, int64_t* quant_len, in
                                      const void* h_q, const void* h_new_k, const void* h_new_v, void* h_out,
                                      int dtype, int out_dtype, int n_rep, float sm_scale,
                                      void* d_stage, size_t d_stage_bytes, void* workspace, size_t workspace_bytes,
-                                     int num_splits, int path, int rounding, int chunks,
+                                     int num_splits, int path, int rounding, int chunks, int direct,
                                      const kivi_peer_gather* gather, int64_t gather_units, void* stream) {
     KIVI_REQUIRE(L && quant_len && res_start && res_len, "layer and counters must be given");
-    KIVI_REQUIRE(h_q && h_new_k && h_new_v && h_out && d_stage && workspace, "host, staging and workspace buffers must be given");
+    KIVI_REQUIRE(h_q && h_new_k && h_new_v && h_out && workspace, "host and workspace buffers must be given");
+    KIVI_REQUIRE(direct || d_stage, "a staging buffer is needed unless direct access is asked for");
     KIVI_REQUIRE(dtype == KIVI_F32 || dtype == KIVI_BF16, "dtype must be KIVI_F32 or KIVI_BF16");
     KIVI_REQUIRE(out_dtype == KIVI_F32 || out_dtype == KIVI_BF16, "out dtype must be KIVI_F32 or KIVI_BF16");
     KIVI_REQUIRE(n_rep >= 1 && n_rep <= 8, "n_rep (%d) outside 1..8", n_rep);
     const int U = L->num_units, D = L->head_dim;
     KIVI_REQUIRE(U > 0 && D > 0, "empty layer");
-    KIVI_REQUIRE(d_stage_bytes >= kivi_decode_step_stage_bytes(U, n_rep, D), "staging buffer too small: %zu bytes given, %zu needed",
+    KIVI_REQUIRE(direct || d_stage_bytes >= kivi_decode_step_stage_bytes(U, n_rep, D), "staging buffer too small: %zu bytes given, %zu needed",
                  d_stage_bytes, kivi_decode_step_stage_bytes(U, n_rep, D));
+    if (direct) {
+        // device-side addresses of the pinned host buffers
+        void *dq = nullptr, *dk = nullptr, *dv = nullptr, *dout = nullptr;
+        KIVI_CUDA_OK(cudaHostGetDevicePointer(&dq, const_cast<void*>(h_q), 0));
+        KIVI_CUDA_OK(cudaHostGetDevicePointer(&dk, const_cast<void*>(h_new_k), 0));
+        KIVI_CUDA_OK(cudaHostGetDevicePointer(&dv, const_cast<void*>(h_new_v), 0));
+        KIVI_CUDA_OK(cudaHostGetDevicePointer(&dout, h_out, 0));
+        int64_t ql_d = 0; int rs_d = 0, rl_d = 0;
+        if (int rc = kivi_cache_update(L, *quant_len, *res_start, *res_len, dk, dv, dtype, D, D, D, D, 1, rounding,
+                                       &ql_d, &rs_d, &rl_d, stream)) return rc;
+        int n_launch = kivi_last_launch_count();
+        if (gather) {
+            if (int rc = kivi_decode_attention_gather(L, ql_d, rs_d, rl_d, dq, dtype, gather, out_dtype, n_rep, sm_scale,
+                                                      workspace, workspace_bytes, num_splits, path, stream)) return rc;
+            KIVI_CUDA_OK(cudaMemcpyAsync(h_out, gather->out_ptrs[gather->rank], (size_t)gather_units * n_rep * D * elem_size(out_dtype),
+                                         cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+        } else {
+            if (int rc = kivi_decode_attention(L, ql_d, rs_d, rl_d, dq, dtype, dout, out_dtype, n_rep, sm_scale,
+                                               workspace, workspace_bytes, num_splits, path, stream)) return rc;
+        }
+        n_launch += kivi_last_launch_count();
+        *quant_len = ql_d; *res_start = rs_d; *res_len = rl_d;
+        note_launches(n_launch);
+        return KIVI_OK;
+    }
     if (chunks < 1) chunks = 1;
     if (chunks > kMaxChunks) chunks = kMaxChunks;
     if (chunks > U) chunks = U;

@@ -15,7 +15,7 @@ from typing import Tuple
 
 import torch
 
-__all__ = ["unit_partition", "all_gather_units", "PeerGather", "merge_token_shards"]
+__all__ = ["unit_partition", "all_gather_units", "PeerGather", "merge_token_shards", "TokenShardPlan"]
 
 
 def unit_partition(n_units: int, rank: int, world: int) -> Tuple[int, int]:
@@ -46,6 +46,44 @@ def all_gather_units(local: torch.Tensor, n_units: int, rank: int, world: int, g
     buf = torch.empty((world * biggest,) + tuple(tail), dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(buf, padded, group=group)
     return torch.cat([buf[r * biggest: r * biggest + (b - a)] for r, (a, b) in enumerate(sizes)], dim=0)
+
+
+class TokenShardPlan:
+    """Which rank keeps which token group when the *sequence* is sharded (every
+    rank holds all units but only its share of each unit's quantized groups; the
+    residual ring is replicated).  Attention is a sum over tokens, so any
+    assignment that gives every group to exactly one rank is correct; this one
+    keeps the ranks balanced as the sequence grows:
+
+    * a bulk flush of ``f`` groups at once (prefill) is cut into ``world``
+      contiguous runs, rank r taking run r (``unit_partition`` of the f groups);
+    * groups flushed one at a time (decode) go round robin, group number g to
+      rank ``g % world``.
+
+    Pure arithmetic on the global group count: every rank computes the same plan
+    without talking to the others (the reference has no counterpart: it is
+    single-device and keeps the whole history dequantized,
+    cache/manager.py:100-117)."""
+
+    def __init__(self, rank: int, world: int):
+        assert 0 <= rank < world
+        self.rank, self.world = rank, world
+
+    def bulk_run(self, n_groups: int) -> Tuple[int, int]:
+        """[g0, g1) of a bulk flush of n_groups groups that this rank keeps."""
+        return unit_partition(n_groups, self.rank, self.world)
+
+    def owner(self, global_group: int) -> int:
+        """Rank that keeps a group flushed on its own (decode)."""
+        return global_group % self.world
+
+    def owns(self, global_group: int) -> bool:
+        return self.owner(global_group) == self.rank
+
+    @property
+    def serves_ring(self) -> bool:
+        """The replicated ring is attended by one rank only (rank 0)."""
+        return self.rank == 0
 
 
 def merge_token_shards(outs: torch.Tensor, lses: torch.Tensor) -> torch.Tensor:

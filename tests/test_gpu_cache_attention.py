@@ -485,8 +485,8 @@ def test_attention_lse_combines_token_shards(cabi, dtype, path):
         cabi.LayerStore(U, D, G, R, 64, dtype, "cuda").attention_lse(qd, n_rep=n_rep)
 
 
-@pytest.mark.parametrize("chunks", [1, 2, 3])
-def test_decode_step_from_host_equals_update_then_attention(cabi, chunks):
+@pytest.mark.parametrize("chunks,direct", [(1, True), (1, False), (2, False), (3, False)])
+def test_decode_step_from_host_equals_update_then_attention(cabi, chunks, direct):
     """kivi_decode_step_host: pinned host q / new token in, pinned host output back.
     Over 40 steps (one flush inside) the counters, the packed store and the ring
     must end up bit-identical to update() + attention() called separately; the
@@ -508,7 +508,7 @@ def test_decode_step_from_host_equals_update_then_attention(cabi, chunks):
     for t in range(T0, T0 + steps):
         q = ko.make_queries(B, Hkv * n_rep, D, seed=t).to(torch.bfloat16)
         h_q.copy_(q.reshape(U, n_rep, D)); h_k.copy_(units(K)[:, t]); h_v.copy_(units(V)[:, t])
-        a.decode_step_host(h_q, h_k, h_v, h_out, n_rep, chunks=chunks)
+        a.decode_step_host(h_q, h_k, h_v, h_out, n_rep, chunks=chunks, direct=direct)
         b.update(Kc[:, t:t + 1], Vc[:, t:t + 1])
         ref_out = b.attention(q.reshape(U, n_rep, D).cuda(), n_rep=n_rep, out_dtype=torch.float32)
         torch.cuda.synchronize()

@@ -66,6 +66,16 @@ else:
         torch.cuda.synchronize()
         assert torch.equal(out_p, out_1), "peer-gather output differs from the single-GPU output"
     peer.close()
+if world > 1:
+    # the sequence sharded instead of the units: every rank holds all units and its share of the token groups
+    seq = KiviCache(num_layers=1, head_dim=D, device=dev, shard=(rank, world), shard_mode="tokens")
+    seq.add_tokens(((K[:, :, :T - 3].to(dev), V[:, :, :T - 3].to(dev)),))
+    seq.add_tokens(((K.to(dev), V.to(dev)),))
+    assert seq._quant_token_count[0] == single._quant_token_count[0] and seq._stores[0].quant_len < single._quant_token_count[0]
+    out_t = seq.decode_attention(0, q.to(dev), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    err_t = ((out_t - out_1).abs().amax(-1) / out_1.abs().amax(-1)).max().item()
+    assert err_t < 2e-3, err_t
 assert cabi.device_fault() == 0
 dist.barrier()
 torch.cuda.synchronize()
@@ -152,3 +162,55 @@ def test_peer_wait_that_runs_out_is_reported_and_can_be_cleared():
     assert cabi.device_fault() == 0                  # reported once, then cleared
     out = st.attention(q, n_rep=n_rep, num_splits=2, out_dtype=torch.float32)
     assert torch.equal(out, ref)                     # the context is as usable as before
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-3), (torch.float32, 1e-5)])
+def test_sequence_sharded_cache_on_one_gpu(dtype, tol):
+    """shard_mode="tokens" with the three ranks of a world held in one process:
+    every token group is kept by exactly one rank, the rings stay replicated, and
+    the folded partial attentions equal an unsharded cache's output through a
+    prefill, single-token steps across several flushes, and a multi-token chunk."""
+    from intel_kivi_hybrid_b200 import cabi
+    from kivi_cuda import KiviCache
+    from oracle import kivi_oracle as ko
+    B, Hkv, n_rep, D, G, R, world = 1, 2, 4, 128, 32, 128, 3
+    T0, steps = 500, 75
+    T = T0 + steps + 40
+    K = ko.make_keys(B, Hkv, T, D, 51).to(dtype).cuda()
+    V = ko.make_values(B, Hkv, T, D, 51).to(dtype).cuda()
+    full = KiviCache(num_layers=1, head_dim=D, device="cuda")
+    ranks = [KiviCache(num_layers=1, head_dim=D, device="cuda", shard=(r, world), shard_mode="tokens") for r in range(world)]
+
+    def feed(t):
+        for c in [full] + ranks:
+            c.add_tokens(((K[:, :, :t], V[:, :, :t]),))
+
+    def check(t):
+        q = ko.make_queries(B, Hkv * n_rep, D, seed=t).to(dtype).cuda()
+        qu = q.reshape(B * Hkv, n_rep, D).contiguous()
+        parts = torch.stack([c.token_shard_partial(0, qu, n_rep) for c in ranks])
+        merged = cabi.merge_token_shards(parts).reshape(B, Hkv * n_rep, D)
+        ref = full.decode_attention(0, q, out_dtype=torch.float32)
+        err = float(((merged - ref).abs().amax(-1) / ref.abs().amax(-1)).max())
+        assert err < tol, (t, err)
+        kept = [c._stores[0].quant_len for c in ranks]
+        assert sum(kept) == full._quant_token_count[0] == ranks[0]._quant_token_count[0]
+        assert max(kept) - min(kept) <= 2 * G                       # balanced
+        for c in ranks:                                             # replicated ring, same window
+            assert torch.equal(c.res_keys[0], full.res_keys[0])
+        return err
+
+    feed(T0); check(T0)
+    worst = 0.0
+    for t in range(T0 + 1, T0 + steps + 1):
+        feed(t)
+        worst = max(worst, check(t))
+    feed(T); check(T)                                               # 40 tokens at once on a non-empty cache
+    assert full.total_flushes == ranks[1].total_flushes > (T0 - R) // G + 2
+    print(f"[sequence sharding, {dtype}] worst error vs the unsharded cache {worst:.2e}")
+    # the oracle agrees with the folded result as well
+    q = ko.make_queries(B, Hkv * n_rep, D, seed=9).to(dtype)
+    parts = torch.stack([c.token_shard_partial(0, q.cuda().reshape(B * Hkv, n_rep, D).contiguous(), n_rep) for c in ranks])
+    got = cabi.merge_token_shards(parts).reshape(B, Hkv * n_rep, D).cpu()
+    ref = ko.kivi_decode_attention(q, K.cpu(), V.cpu(), full._quant_token_count[0], G, "half_away", dtype=torch.float64).float()
+    assert float(((got - ref).abs().amax(-1) / ref.abs().amax(-1)).max()) < tol

@@ -266,3 +266,17 @@ def test_attention_split_plan_is_pinned():
     assert plan(12, 512, 96, head_dim=64, q_dtype=cabi.F32)[0] is False
     with pytest.raises(RuntimeError, match="tensor-core path"):
         plan(12, 512, 96, head_dim=64, path=cabi.ATTN_MMA)
+
+
+def test_token_shard_plan_gives_every_group_to_one_rank():
+    from intel_kivi_hybrid_b200.parallel import TokenShardPlan
+    for world in (1, 2, 3, 8):
+        plans = [TokenShardPlan(r, world) for r in range(world)]
+        for f in (0, 1, 5, 17, 64):                                   # a bulk flush: contiguous runs covering 0..f
+            runs = [p.bulk_run(f) for p in plans]
+            assert runs[0][0] == 0 and runs[-1][1] == f
+            assert all(a[1] == b[0] for a, b in zip(runs, runs[1:]))
+            assert max(b - a for a, b in runs) - min(b - a for a, b in runs) <= 1
+        for g in range(40):                                           # single groups: exactly one owner
+            assert sum(p.owns(g) for p in plans) == 1
+        assert sum(p.serves_ring for p in plans) == 1
