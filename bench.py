@@ -371,7 +371,7 @@ def run_ours(args, wl):
     # the timed region: exactly --steps steps, repeated until it lasts MIN_TIMED_SECONDS
     # (the same number of repeats on every rank)
     est_ms, _ = timed(args.steps, graph is not None)
-    rep = torch.tensor([max(1, int(MIN_TIMED_SECONDS * 1e3 / max(est_ms, 1e-3)) + 1)], device=dev)
+    rep = torch.tensor([max(1, int(args.min_seconds * 1e3 / max(est_ms, 1e-3)) + 1)], device=dev)
     if world > 1:
         dist.all_reduce(rep, op=dist.ReduceOp.MAX)
     n_timed = args.steps * int(rep.item())
@@ -462,7 +462,8 @@ def run_ours(args, wl):
     # rank keeps the same step loop running (untimed) for about 1.2 s more -- the
     # same number of steps everywhere, because a step holds a collective
     clocks = None
-    n_extra = torch.tensor([int(min(20000, max(args.steps, 1.2e3 / max(ms_step, 1e-3))))], device=dev)
+    n_extra = torch.tensor([int(min(20000, max(args.steps, 1.2e3 / max(ms_step, 1e-3)))) if args.min_seconds > 0 else 1],
+                           device=dev)
     if world > 1:
         dist.all_reduce(n_extra, op=dist.ReduceOp.MAX)
     w0 = time.time()
@@ -652,6 +653,9 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["cfg4", "ops"])
     ap.add_argument("--path", default="auto", choices=["auto", "fp32", "mma"])
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
+                    help="repeat the --steps timed steps until the timed region lasts this long (0: exactly --steps; "
+                         "used for profiler runs)")
     ap.add_argument("--e2e-staged", action="store_true",
                     help="end-to-end step through explicit staging copies instead of kernels accessing the pinned host buffers")
     ap.add_argument("--e2e-chunks", type=int, default=1, help="with --e2e-staged: chunks of units whose copies and kernels overlap")

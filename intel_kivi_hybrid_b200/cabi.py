@@ -43,6 +43,7 @@ SIGNATURES = {
     "kivi_last_error": (_c.c_char_p, []),
     "kivi_version": (_int, []),
     "kivi_last_launch_count": (_int, []),
+    "kivi_selftest_mma_alignment_bits": (_int, [_c.POINTER(_int)]),
     "kivi_device_fault": (_int, [_c.POINTER(_int)]),
     "kivi_device_fault_clear": (_int, []),
     "kivi_quantize_keys_per_channel": (_int, [_vp, _int, _vp, _vp, _vp, _i64, _int, _int, _vp]),
@@ -165,6 +166,13 @@ def roundtrip_values(x, out, head_dim, group_size, rounding=ROUND_HALF_AWAY):
     _dev(x, out)
     _check(lib.kivi_quant_dequant_roundtrip_values(x.data_ptr(), _dt(x), out.data_ptr(), x.numel() // head_dim,
                                                    head_dim, group_size, rounding, _stream()))
+
+
+def mma_alignment_bits() -> int:
+    """kivi_selftest_mma_alignment_bits on the current device."""
+    w = _int()
+    _check(lib.kivi_selftest_mma_alignment_bits(_c.byref(w)))
+    return w.value
 
 
 def device_fault() -> int:

@@ -796,6 +796,46 @@ int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_
     return KIVI_OK;
 }
 
+// ---- self-test: how far below the largest product the tensor core keeps bits -------
+// One m16n8k16 MMA per k: C = -1, products {1 * 1, 2^-a * 2^-b} with a + b = k.
+// If the unit kept every bit the result would be exactly 2^-k; it aligns the
+// addends on their exponent fields and truncates below a fixed distance from the
+// largest, so from some k on the small product is lost.  The kernel's accuracy
+// budget (code_regs above) assumes at least 24 bits.
+__global__ void mma_alignment_probe_kernel(int* kept_out) {
+    const int lane = threadIdx.x, gid = lane >> 2, tig = lane & 3;
+    int kept = 0;
+    for (int k = 8; k <= 34; ++k) {
+        const int a_exp = k < 14 ? k : 14, b_exp = k - a_exp;          // both factors stay normal fp16 numbers
+        // A[row][0] = 1, A[row][1] = 2^-a; B[0][col] = 1, B[1][col] = 2^-b; everything else 0
+        const __half2 a01 = __halves2half2(__float2half(1.0f), __float2half(ldexpf(1.0f, -a_exp)));
+        const __half2 b01 = __halves2half2(__float2half(1.0f), __float2half(ldexpf(1.0f, -b_exp)));
+        uint32_t a[4] = {0u, 0u, 0u, 0u}, b0 = 0u;
+        if (tig == 0) {                                                // k-slots 0 and 1 live in lanes with tig == 0
+            a[0] = *reinterpret_cast<const uint32_t*>(&a01);
+            a[1] = a[0];
+            b0 = *reinterpret_cast<const uint32_t*>(&b01);
+        }
+        float c[4] = {-1.0f, -1.0f, -1.0f, -1.0f};
+        mma_f16(c, a, b0, 0u);
+        const bool ok = c[0] == ldexpf(1.0f, -k);
+        if (__all_sync(0xffffffffu, ok)) kept = k;
+    }
+    (void)gid;
+    if (lane == 0) *kept_out = kept;
+}
+
+int run_mma_alignment_probe(int* bits_out) {
+    int* d = nullptr;
+    KIVI_CUDA_OK(cudaMalloc(&d, sizeof(int)));
+    mma_alignment_probe_kernel<<<1, 32>>>(d);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMemcpy(bits_out, d, sizeof(int), cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    if (e != cudaSuccess) { set_error("tensor-core alignment probe failed: %s", cudaGetErrorString(e)); return KIVI_ERR_CUDA; }
+    return KIVI_OK;
+}
+
 int attn_mma_fault_word(int* out) {
     KIVI_CUDA_OK(cudaMemcpyFromSymbol(out, g_fault_word, sizeof(int)));
     return KIVI_OK;

@@ -56,6 +56,7 @@ int run_sample(const void* logits, int dtype, int batch, int vocab, int64_t row_
                int do_sample, uint64_t seed, uint64_t step, int64_t* ids, cudaStream_t st);
 int run_merge_token_shards(const float* parts, int n_shards, int64_t rows, int D, void* out, int out_dtype,
                            float* lse_out, cudaStream_t st);
+int run_mma_alignment_probe(int* bits_out);
 int attn_mma_fault_word(int* out);
 int gather_fault_word(int* out);
 int attn_mma_fault_clear();
@@ -420,4 +421,10 @@ extern "C" int kivi_merge_token_shards(const float* parts, int n_shards, int64_t
     if (int rc = run_merge_token_shards(parts, n_shards, rows, head_dim, out, out_dtype, lse_out, (cudaStream_t)stream)) return rc;
     note_launches(1);
     return KIVI_OK;
+}
+
+// ---- self-test of a hardware property the tensor-core kernel's error budget rests on ----
+extern "C" int kivi_selftest_mma_alignment_bits(int* bits_out) {
+    KIVI_REQUIRE(bits_out != nullptr, "bits_out is null");
+    return run_mma_alignment_probe(bits_out);
 }

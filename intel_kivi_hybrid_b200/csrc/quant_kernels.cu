@@ -282,27 +282,54 @@ int launch_bf16_rows(const void* in, uint8_t* packed, float* scales, float* zero
     return KIVI_OK;
 }
 
-// One thread per packed byte -> one float4 store (dequantize_kernels.cpp:50-61).
+// Dequantize: one packed byte -> one float4 (dequantize_kernels.cpp:50-61).  The
+// kernel is bound by its 16-bytes-per-input-byte output stream, so what matters
+// is how many stores a thread has in flight: a CTA takes a tile of
+// kDqUnroll * kThreads consecutive bytes, a thread the bytes t, t + kThreads, ...
+// of it (every load and every 128-bit store of a warp is one contiguous run), all
+// of a thread's loads are issued before its first store.
+constexpr int kDqUnroll = 8;
+
+__device__ __forceinline__ float4 dequant_byte(uint32_t p, float s, float z) {
+    // code c as a float: the two bits dropped into the mantissa of 2^23, minus 2^23
+    float4 r;
+    r.x = dequant(__fsub_rn(__uint_as_float(0x4B000000u | (p & 3u)), 8388608.0f), s, z);
+    r.y = dequant(__fsub_rn(__uint_as_float(0x4B000000u | ((p >> 2) & 3u)), 8388608.0f), s, z);
+    r.z = dequant(__fsub_rn(__uint_as_float(0x4B000000u | ((p >> 4) & 3u)), 8388608.0f), s, z);
+    r.w = dequant(__fsub_rn(__uint_as_float(0x4B000000u | (p >> 6)), 8388608.0f), s, z);
+    return r;
+}
+
 __global__ void __launch_bounds__(kThreads)
 group_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ scales,
                      const float* __restrict__ zeros, float* __restrict__ out,
                      int64_t total_bytes, int bytes_per_group, int group_shift, bool vec_ok) {
-    for (int64_t b = (int64_t)blockIdx.x * kThreads + threadIdx.x; b < total_bytes;
-         b += (int64_t)gridDim.x * kThreads) {
-        // group of this byte: a shift for power-of-two groups (no 64-bit division per element)
-        const int64_t g = group_shift >= 0 ? (b >> group_shift) : b / bytes_per_group;
-        const float s = __ldg(scales + g), z = __ldg(zeros + g);
-        const uint32_t p = __ldg(packed + b);
-        // code c as a float: the two bits dropped into the mantissa of 2^23, minus 2^23
-        float4 r;
-        r.x = dequant(__fsub_rn(__uint_as_float(0x4B000000u | (p & 3u)), 8388608.0f), s, z);
-        r.y = dequant(__fsub_rn(__uint_as_float(0x4B000000u | ((p >> 2) & 3u)), 8388608.0f), s, z);
-        r.z = dequant(__fsub_rn(__uint_as_float(0x4B000000u | ((p >> 4) & 3u)), 8388608.0f), s, z);
-        r.w = dequant(__fsub_rn(__uint_as_float(0x4B000000u | (p >> 6)), 8388608.0f), s, z);
-        if (vec_ok) {
-            __stcs(reinterpret_cast<float4*>(out) + b, r);
-        } else {
-            out[4 * b] = r.x; out[4 * b + 1] = r.y; out[4 * b + 2] = r.z; out[4 * b + 3] = r.w;
+    const int64_t tile = (int64_t)kDqUnroll * kThreads;
+    for (int64_t b0 = (int64_t)blockIdx.x * tile; b0 < total_bytes; b0 += (int64_t)gridDim.x * tile) {
+        uint32_t p[kDqUnroll];
+        float s[kDqUnroll], z[kDqUnroll];
+#pragma unroll
+        for (int k = 0; k < kDqUnroll; ++k) {
+            const int64_t b = b0 + (int64_t)k * kThreads + threadIdx.x;
+            if (b < total_bytes) {
+                // group of this byte: a shift for power-of-two groups (no 64-bit division per element)
+                const int64_t g = group_shift >= 0 ? (b >> group_shift) : b / bytes_per_group;
+                p[k] = __ldg(packed + b);
+                s[k] = __ldg(scales + g);
+                z[k] = __ldg(zeros + g);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kDqUnroll; ++k) {
+            const int64_t b = b0 + (int64_t)k * kThreads + threadIdx.x;
+            if (b < total_bytes) {
+                const float4 r = dequant_byte(p[k], s[k], z[k]);
+                if (vec_ok) {
+                    __stcs(reinterpret_cast<float4*>(out) + b, r);
+                } else {
+                    out[4 * b] = r.x; out[4 * b + 1] = r.y; out[4 * b + 2] = r.z; out[4 * b + 3] = r.w;
+                }
+            }
         }
     }
 }
@@ -398,8 +425,8 @@ int run_group_dequant(const uint8_t* packed, const float* scales, const float* z
     KIVI_REQUIRE(G > 0 && G % 4 == 0, "group_size must be positive and divisible by 4, got %d", G);
     KIVI_REQUIRE(num_groups > 0, "scales must be non-empty");
     const int64_t total_bytes = num_groups * (G / 4);
-    int64_t blocks = (total_bytes + kThreads - 1) / kThreads;
-    const int64_t cap = (int64_t)num_sms() * 64;
+    int64_t blocks = (total_bytes + (int64_t)kDqUnroll * kThreads - 1) / ((int64_t)kDqUnroll * kThreads);
+    const int64_t cap = (int64_t)num_sms() * 32;
     if (blocks > cap) blocks = cap;
     int shift = -1;
     for (int k = 0; k < 31; ++k) if ((G / 4) == (1 << k)) shift = k;

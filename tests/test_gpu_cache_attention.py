@@ -526,3 +526,14 @@ def test_decode_step_from_host_equals_update_then_attention(cabi, chunks, direct
     assert cabi.device_fault() == 0
     with pytest.raises(RuntimeError, match="pinned"):
         a.decode_step_host(h_q.clone(), h_k, h_v, h_out, n_rep)
+
+
+def test_tensor_core_keeps_enough_bits_for_subnormal_codes(cabi):
+    """The tensor-core kernel feeds codes as fp16 subnormals; the MMA aligns its
+    addends on their exponent fields and truncates a fixed distance below the
+    largest.  The kernel's placement of the codes (no code lower than bits 2-3 of
+    its half) leaves 20 bits if the unit keeps 26 below the largest addend's
+    leading bit, i.e. still resolves 2^-25 next to 1."""
+    bits = cabi.mma_alignment_bits()
+    print(f"[tensor core] 1 + 2^-k - 1 is exact up to k = {bits}")
+    assert bits >= 24
