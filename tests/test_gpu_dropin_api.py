@@ -317,3 +317,41 @@ def test_cache_operators_of_the_extension(native, dtype, D, G, n_rep):
     with pytest.raises(RuntimeError, match="n_new, head_dim"):
         native.append_and_flush(kc[:, :4, : D // 2], vc[:, :4, : D // 2], quant_len=state[0], res_start=state[1],
                                 res_len=state[2], group_size=G, **t)
+
+
+def test_reference_flush_sequence_over_the_extension_reproduces_its_served_cache(native, golden_dir):
+    """What the reference's own KiviCache does with its native module, replayed
+    call for call over kivi_cuda._C: keep the window as a tensor, and while it
+    holds >= R tokens take the oldest G, round-trip the transposed key chunk
+    [B,H,D,G] and the value chunk [B,H,G,D] through the fused operators and
+    append them to the history (cache/manager.py:226-243, 332-363).  The served
+    history || window must equal what the reference's KiviCache served for the
+    same token stream (golden vectors made by running it)."""
+    sm = np.load(os.path.join(golden_dir, "state_machine_vectors.npz"))
+    K, V = torch.from_numpy(sm["long__K"]).to(DEV), torch.from_numpy(sm["long__V"]).to(DEV)
+    G, R, D = 32, 128, 64
+    mode = native.ROUND_HALF_EVEN                          # the golden run used the reference's torch mirror
+    hist_k, hist_v = [], []
+    res_k, res_v = K[:, :, :0], V[:, :, :0]
+    flushes = 0
+
+    def add(k_new, v_new):
+        nonlocal res_k, res_v, flushes
+        res_k, res_v = torch.cat([res_k, k_new], dim=2), torch.cat([res_v, v_new], dim=2)
+        while res_k.shape[2] >= R:
+            ck = res_k[:, :, :G].transpose(2, 3).contiguous()           # [B,H,D,G]
+            cv = res_v[:, :, :G].contiguous()                            # [B,H,G,D]
+            ok, ov = torch.empty_like(ck), torch.empty_like(cv)
+            native.quant_dequant_roundtrip_keys(ck, ok, G, rounding=mode)
+            native.quant_dequant_roundtrip_values(cv, ov, D, G, rounding=mode)
+            hist_k.append(ok.transpose(2, 3)); hist_v.append(ov)
+            res_k, res_v = res_k[:, :, G:], res_v[:, :, G:]
+            flushes += 1
+
+    add(K[:, :, :200], V[:, :, :200])
+    for t in range(200, 300):
+        add(K[:, :, t:t + 1], V[:, :, t:t + 1])
+    served_k, served_v = torch.cat(hist_k + [res_k], dim=2), torch.cat(hist_v + [res_v], dim=2)
+    assert flushes == int(sm["long__total_flushes"])
+    assert torch.equal(served_k.cpu(), torch.from_numpy(sm["long__served_k"]))
+    assert torch.equal(served_v.cpu(), torch.from_numpy(sm["long__served_v"]))
