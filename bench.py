@@ -196,8 +196,9 @@ def run_reference(args, wl):
             "ms_per_step": t * 1e3 * (B / B_s), "higher_is_better": True,
             "scaling": "strong" if args.gpus > 1 and args.scaling == "strong" else "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "B_per_gpu": B, "Hkv": Hkv, "Hq": Hkv * n_rep, "D": D, "G": G,
-                       "n_quant": n_quant, "n_res": n_res,
+            "config": {"workload": args.workload, "B_global": B if (args.gpus == 1 or args.scaling == "strong") else B * args.gpus,
+                       "units_per_gpu": (B * Hkv + args.gpus - 1) // args.gpus if (args.gpus > 1 and args.scaling == "strong") else B * Hkv,
+                       "Hkv": Hkv, "Hq": Hkv * n_rep, "D": D, "G": G, "n_quant": n_quant, "n_res": n_res,
                        "parallelism": "reference CPU path on rank 0's host cores, one batch row per step"},
             "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}

@@ -241,6 +241,8 @@ attn_fp32_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
 
 namespace {
 
+__device__ __forceinline__ void store_quad(void* p, int dtype, int64_t i, float4 v);
+
 // out[u][h][:] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
 // grid = (units, n_rep), 128 threads; partials laid out [(u*n_splits + s)*n_rep + h].
 // Thread s loads (m_s, l_s); the maximum and the denominator are block
@@ -284,26 +286,58 @@ __device__ __forceinline__ void merge_body(const float* __restrict__ part_o, con
     const float inv = 1.0f / den;
     // natural-log sum of exponentials of the scaled scores (M and den live in the log2 domain)
     if (lse != nullptr && threadIdx.x == 0) lse[(int64_t)u * nrep + h] = (M + log2f(den)) * 0.6931471805599453f;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-        int s = 0;
-        for (; s + 4 <= n_splits; s += 4) {
-            const float v0 = part_o[(row0 + (int64_t)(s + 0) * nrep) * D + d];
-            const float v1 = part_o[(row0 + (int64_t)(s + 1) * nrep) * D + d];
-            const float v2 = part_o[(row0 + (int64_t)(s + 2) * nrep) * D + d];
-            const float v3 = part_o[(row0 + (int64_t)(s + 3) * nrep) * D + d];
-            a0 = fmaf(v0, w_s[s], a0); a1 = fmaf(v1, w_s[s + 1], a1);
-            a2 = fmaf(v2, w_s[s + 2], a2); a3 = fmaf(v3, w_s[s + 3], a3);
+    // thread d owns channel d; four neighbours hand their values to the lane
+    // whose channel is a multiple of four, which stores 8 or 16 bytes at once
+    // (head_dim is a multiple of 4, so a quad never straddles the end of the row)
+    for (int d0 = 0; d0 < D; d0 += blockDim.x) {
+        const int d = d0 + threadIdx.x;
+        float val = 0.0f;
+        if (d < D) {
+            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+            int s = 0;
+            for (; s + 4 <= n_splits; s += 4) {
+                const float v0 = part_o[(row0 + (int64_t)(s + 0) * nrep) * D + d];
+                const float v1 = part_o[(row0 + (int64_t)(s + 1) * nrep) * D + d];
+                const float v2 = part_o[(row0 + (int64_t)(s + 2) * nrep) * D + d];
+                const float v3 = part_o[(row0 + (int64_t)(s + 3) * nrep) * D + d];
+                a0 = fmaf(v0, w_s[s], a0); a1 = fmaf(v1, w_s[s + 1], a1);
+                a2 = fmaf(v2, w_s[s + 2], a2); a3 = fmaf(v3, w_s[s + 3], a3);
+            }
+            for (; s < n_splits; ++s) a0 = fmaf(part_o[(row0 + (int64_t)s * nrep) * D + d], w_s[s], a0);
+            val = ((a0 + a1) + (a2 + a3)) * inv;
         }
-        for (; s < n_splits; ++s) a0 = fmaf(part_o[(row0 + (int64_t)s * nrep) * D + d], w_s[s], a0);
-        sink(((int64_t)u * nrep + h) * D + d, ((a0 + a1) + (a2 + a3)) * inv);
+        const float v1 = __shfl_down_sync(0xffffffffu, val, 1);
+        const float v2 = __shfl_down_sync(0xffffffffu, val, 2);
+        const float v3 = __shfl_down_sync(0xffffffffu, val, 3);
+        if (d < D && (d & 3) == 0) sink(((int64_t)u * nrep + h) * D + d, make_float4(val, v1, v2, v3));
+    }
+}
+
+// four consecutive output elements starting at element i (i % 4 == 0): one 8- or
+// 16-byte store when the buffer allows it
+__device__ __forceinline__ void store_quad(void* p, int dtype, int64_t i, float4 v) {
+    if (dtype == KIVI_BF16) {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p) + i;
+        if ((reinterpret_cast<uintptr_t>(o) & 7u) == 0) {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+            uint2 w;
+            w.x = *reinterpret_cast<const uint32_t*>(&lo); w.y = *reinterpret_cast<const uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(o) = w;
+        } else {
+            o[0] = __float2bfloat16_rn(v.x); o[1] = __float2bfloat16_rn(v.y);
+            o[2] = __float2bfloat16_rn(v.z); o[3] = __float2bfloat16_rn(v.w);
+        }
+    } else {
+        float* o = reinterpret_cast<float*>(p) + i;
+        if ((reinterpret_cast<uintptr_t>(o) & 15u) == 0) *reinterpret_cast<float4*>(o) = v;
+        else { o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; }
     }
 }
 
 struct LocalSink {
     void* out;
     int out_dtype;
-    __device__ void operator()(int64_t i, float v) const { store_from_float(out, out_dtype, i, v); }
+    __device__ void operator()(int64_t i, float4 v) const { store_quad(out, out_dtype, i, v); }
 };
 
 __global__ void __launch_bounds__(128)
@@ -335,10 +369,10 @@ struct PeerSink {
     kivi_peer_gather g;
     int out_dtype;
     int64_t base;              // element offset of this rank's first row in a gathered buffer
-    __device__ void operator()(int64_t i, float v) const {
+    __device__ void operator()(int64_t i, float4 v) const {
 #pragma unroll
         for (int r = 0; r < KIVI_PEER_MAX_WORLD; ++r)
-            if (r < g.world) store_from_float(g.out_ptrs[r], out_dtype, base + i, v);
+            if (r < g.world) store_quad(g.out_ptrs[r], out_dtype, base + i, v);
     }
 };
 

@@ -56,6 +56,24 @@ if world == 1:
         st.attention_gather(q.to(dev).reshape(B * Hkv, n_rep, D), pg.descriptor(), torch.float32, n_rep, num_splits=3)
         torch.cuda.synchronize()
         assert torch.equal(pg.gathered().reshape(B, Hkv * n_rep, D), out_1), "peer-gather output differs"
+    # the host-to-host decode step through the same exchange: pinned q / new token in,
+    # the gathered rows back in pinned memory (what bench.py's end-to-end loop calls at N > 1)
+    twin = KiviCache(num_layers=1, head_dim=D, device=dev)
+    twin.add_tokens(((K[:, :, :T - 3].to(dev), V[:, :, :T - 3].to(dev)),))
+    twin.add_tokens(((K.to(dev), V.to(dev)),))
+    a, b = st, twin._stores[0]
+    U = B * Hkv
+    h_q = q.reshape(U, n_rep, D).contiguous().pin_memory()
+    h_k = torch.randn(U, D).to(torch.bfloat16).pin_memory()
+    h_v = torch.randn(U, D).to(torch.bfloat16).pin_memory()
+    h_out = torch.empty(U, n_rep, D, dtype=torch.float32).pin_memory()
+    for direct in (True, False):
+        a.decode_step_host(h_q, h_k, h_v, h_out, n_rep, num_splits=3, direct=direct, gather=pg.descriptor(), gather_units=U)
+        b.update(h_k.to(dev).unsqueeze(1), h_v.to(dev).unsqueeze(1))
+        want = b.attention(h_q.to(dev), n_rep=n_rep, num_splits=3, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        assert (a.quant_len, a.res_start, a.res_len) == (b.quant_len, b.res_start, b.res_len)
+        assert torch.equal(h_out, want.cpu()), "host decode step through the peer gather differs"
     pg.close()
 else:
     peer = KiviCache(num_layers=1, head_dim=D, device=dev, shard=(rank, world), gather="peer")
