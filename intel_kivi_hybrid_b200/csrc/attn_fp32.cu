@@ -244,72 +244,62 @@ namespace {
 __device__ __forceinline__ void store_quad(void* p, int dtype, int64_t i, float4 v);
 
 // out[u][h][:] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
-// grid = (units, n_rep), 128 threads; partials laid out [(u*n_splits + s)*n_rep + h].
-// Thread s loads (m_s, l_s); the maximum and the denominator are block
-// reductions, so no thread walks the splits alone; the channel loop keeps four
-// independent loads in flight.  `sink(index, value)` receives element
-// index = (u*n_rep + h)*D + d of the output.
+// One warp per output row (row = u*n_rep + h), kMergeWarps rows per CTA; partials
+// laid out [(u*n_splits + s)*n_rep + h].  Lane s holds (m_s, l_s) and the weight
+// of split s, the maximum and the denominator are warp reductions, and every
+// lane folds four channels with 16-byte loads, the weights handed round by
+// shuffle.  `sink(index, float4)` receives the four output elements starting at
+// index = row*D + d (d a multiple of four; head_dim is a multiple of four).
+constexpr int kMergeWarps = 8;
+
 template <typename Sink>
-__device__ __forceinline__ void merge_body(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                           int n_splits, int D, float* w_s, float* red_s, const Sink& sink,
-                                           float* __restrict__ lse = nullptr) {
-    const int u = blockIdx.x, h = blockIdx.y, nrep = gridDim.y;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const int64_t row0 = (int64_t)u * n_splits * nrep + h;   // + s*nrep
-    // launched with programmatic stream serialization: everything above may
-    // overlap the tail of the attention kernel, the partials may not be read
-    // before that kernel has completed
-    cudaGridDependencySynchronize();
-    float m_loc = -INFINITY;
-    for (int s = threadIdx.x; s < n_splits; s += blockDim.x)
-        m_loc = fmaxf(m_loc, part_ml[(row0 + (int64_t)s * nrep) * 2]);
+__device__ __forceinline__ void merge_row(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                          int n_splits, int nrep, int64_t row, int D, const Sink& sink,
+                                          float* __restrict__ lse) {
+    const int lane = threadIdx.x & 31;
+    const int64_t u = row / nrep;
+    const int h = (int)(row - u * nrep);
+    const int64_t row0 = u * n_splits * nrep + h;            // + s*nrep
+    float M = -INFINITY;
+    for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, part_ml[(row0 + (int64_t)s * nrep) * 2]);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m_loc = fmaxf(m_loc, __shfl_xor_sync(0xffffffffu, m_loc, o));
-    if (lane == 0) red_s[warp] = m_loc;
-    __syncthreads();
-    float M = red_s[0];
-    for (int w = 1; w < nwarps; ++w) M = fmaxf(M, red_s[w]);
-    float den = 0.0f;
-    for (int s = threadIdx.x; s < n_splits; s += blockDim.x) {
-        const float ms = part_ml[(row0 + (int64_t)s * nrep) * 2];
-        const float wgt = (ms == -INFINITY) ? 0.0f : exp2f(ms - M);
-        w_s[s] = wgt;
-        den += wgt * part_ml[(row0 + (int64_t)s * nrep) * 2 + 1];
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
-    __syncthreads();                                  // red_s reads above are done
-    if (lane == 0) red_s[4 + warp] = den;
-    __syncthreads();
-    den = 0.0f;
-    for (int w = 0; w < nwarps; ++w) den += red_s[4 + w];
-    const float inv = 1.0f / den;
-    // natural-log sum of exponentials of the scaled scores (M and den live in the log2 domain)
-    if (lse != nullptr && threadIdx.x == 0) lse[(int64_t)u * nrep + h] = (M + log2f(den)) * 0.6931471805599453f;
-    // thread d owns channel d; four neighbours hand their values to the lane
-    // whose channel is a multiple of four, which stores 8 or 16 bytes at once
-    // (head_dim is a multiple of 4, so a quad never straddles the end of the row)
-    for (int d0 = 0; d0 < D; d0 += blockDim.x) {
-        const int d = d0 + threadIdx.x;
-        float val = 0.0f;
-        if (d < D) {
-            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-            int s = 0;
-            for (; s + 4 <= n_splits; s += 4) {
-                const float v0 = part_o[(row0 + (int64_t)(s + 0) * nrep) * D + d];
-                const float v1 = part_o[(row0 + (int64_t)(s + 1) * nrep) * D + d];
-                const float v2 = part_o[(row0 + (int64_t)(s + 2) * nrep) * D + d];
-                const float v3 = part_o[(row0 + (int64_t)(s + 3) * nrep) * D + d];
-                a0 = fmaf(v0, w_s[s], a0); a1 = fmaf(v1, w_s[s + 1], a1);
-                a2 = fmaf(v2, w_s[s + 2], a2); a3 = fmaf(v3, w_s[s + 3], a3);
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    for (int d0 = 0; d0 < D; d0 += 128) {
+        const int d = d0 + 4 * lane;
+        const bool active = d < D;
+        float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+        float den = 0.0f;
+        for (int s0 = 0; s0 < n_splits; s0 += 32) {
+            const int s = s0 + lane;
+            float wgt = 0.0f;
+            if (s < n_splits) {
+                const float2 ml = *reinterpret_cast<const float2*>(part_ml + (row0 + (int64_t)s * nrep) * 2);
+                wgt = (ml.x == -INFINITY) ? 0.0f : exp2f(ml.x - M);
+                den = fmaf(wgt, ml.y, den);
             }
-            for (; s < n_splits; ++s) a0 = fmaf(part_o[(row0 + (int64_t)s * nrep) * D + d], w_s[s], a0);
-            val = ((a0 + a1) + (a2 + a3)) * inv;
+            const int cnt = min(32, n_splits - s0);
+            const float* src = part_o + (row0 + (int64_t)s0 * nrep) * D + (active ? d : 0);
+            int i = 0;
+            for (; i + 2 <= cnt; i += 2) {
+                const float w0 = __shfl_sync(0xffffffffu, wgt, i), w1 = __shfl_sync(0xffffffffu, wgt, i + 1);
+                const float4 v0 = *reinterpret_cast<const float4*>(src + (int64_t)i * nrep * D);
+                const float4 v1 = *reinterpret_cast<const float4*>(src + (int64_t)(i + 1) * nrep * D);
+                a0.x = fmaf(v0.x, w0, a0.x); a0.y = fmaf(v0.y, w0, a0.y); a0.z = fmaf(v0.z, w0, a0.z); a0.w = fmaf(v0.w, w0, a0.w);
+                a1.x = fmaf(v1.x, w1, a1.x); a1.y = fmaf(v1.y, w1, a1.y); a1.z = fmaf(v1.z, w1, a1.z); a1.w = fmaf(v1.w, w1, a1.w);
+            }
+            if (i < cnt) {
+                const float w0 = __shfl_sync(0xffffffffu, wgt, i);
+                const float4 v0 = *reinterpret_cast<const float4*>(src + (int64_t)i * nrep * D);
+                a0.x = fmaf(v0.x, w0, a0.x); a0.y = fmaf(v0.y, w0, a0.y); a0.z = fmaf(v0.z, w0, a0.z); a0.w = fmaf(v0.w, w0, a0.w);
+            }
         }
-        const float v1 = __shfl_down_sync(0xffffffffu, val, 1);
-        const float v2 = __shfl_down_sync(0xffffffffu, val, 2);
-        const float v3 = __shfl_down_sync(0xffffffffu, val, 3);
-        if (d < D && (d & 3) == 0) sink(((int64_t)u * nrep + h) * D + d, make_float4(val, v1, v2, v3));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+        const float inv = 1.0f / den;
+        // natural-log sum of exponentials of the scaled scores (M and den live in the log2 domain)
+        if (lse != nullptr && lane == 0 && d0 == 0) lse[row] = (M + log2f(den)) * 0.6931471805599453f;
+        if (active)
+            sink(row * D + d, make_float4((a0.x + a1.x) * inv, (a0.y + a1.y) * inv, (a0.z + a1.z) * inv, (a0.w + a1.w) * inv));
     }
 }
 
@@ -340,24 +330,29 @@ struct LocalSink {
     __device__ void operator()(int64_t i, float4 v) const { store_quad(out, out_dtype, i, v); }
 };
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kMergeWarps * 32)
 merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                    void* __restrict__ out, int out_dtype, int n_splits, int D, float* __restrict__ lse) {
-    extern __shared__ float w_s[];                   // [n_splits] weights
-    __shared__ float red_s[8];
-    merge_body(part_o, part_ml, n_splits, D, w_s, red_s, LocalSink{out, out_dtype}, lse);
+                    void* __restrict__ out, int out_dtype, int n_splits, int nrep, int64_t rows, int D,
+                    float* __restrict__ lse) {
+    // launched with programmatic stream serialization: the launch may overlap the
+    // tail of the attention kernel, the partials may not be read before that
+    // kernel has completed
+    cudaGridDependencySynchronize();
+    const int64_t row = (int64_t)blockIdx.x * kMergeWarps + (threadIdx.x >> 5);
+    if (row < rows) merge_row(part_o, part_ml, n_splits, nrep, row, D, LocalSink{out, out_dtype}, lse);
 }
 
 // ---- merge + all-gather over peer memory -------------------------------------------
 // The same fold, but every output row is stored into the gathered buffer of
 // every rank (plain stores through peer-mapped pointers).  When the last CTA of
-// the grid has finished, it publishes this rank's epoch in every rank's flag
-// array and, if asked, waits (bounded) until all ranks have published it.
+// the grid has finished, lane r of its first warp publishes this rank's epoch in
+// rank r's flag array and, if asked, waits (bounded) until rank r has published
+// it here: one fence, then all flags and all waits side by side.
 __device__ unsigned g_gather_done = 0;      // CTAs of the running launch that have stored their row
 __device__ int g_gather_fault = 0;
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
@@ -378,35 +373,45 @@ struct PeerSink {
 
 constexpr uint32_t kPeerSpinLimit = 5u << 20;      // default bound: x 200 ns sleeps, about a second
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kMergeWarps * 32)
 merge_gather_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                    kivi_peer_gather g, int out_dtype, int n_splits, int D) {
-    extern __shared__ float w_s[];
-    __shared__ float red_s[8];
-    merge_body(part_o, part_ml, n_splits, D, w_s, red_s,
-               PeerSink{g, out_dtype, g.unit_offset * (int64_t)gridDim.y * D});
+                    kivi_peer_gather g, int out_dtype, int n_splits, int nrep, int64_t rows, int D) {
+    cudaGridDependencySynchronize();
+    const int64_t row = (int64_t)blockIdx.x * kMergeWarps + (threadIdx.x >> 5);
+    if (row < rows)
+        merge_row(part_o, part_ml, n_splits, nrep, row, D, PeerSink{g, out_dtype, g.unit_offset * (int64_t)nrep * D}, nullptr);
     __syncthreads();                                  // the CTA's stores are issued
-    if (threadIdx.x != 0) return;
-    __threadfence_system();                           // ... and ordered before the count below, system-wide
-    const unsigned total = gridDim.x * gridDim.y;
-    if (atomicAdd(&g_gather_done, 1u) + 1u != total) return;
-    g_gather_done = 0;                                // re-armed for the next launch (stream order)
-    __threadfence_system();
-    for (int r = 0; r < g.world; ++r) st_release_sys(g.flag_ptrs[r] + g.rank, g.epoch);
+    if (threadIdx.x >= 32) return;                    // warp 0 carries the protocol
+    const int lane = threadIdx.x;
+    const unsigned total = gridDim.x;
+    unsigned last = 0;
+    if (lane == 0) {
+        __threadfence_system();                       // ... and ordered before the count below, system-wide
+        last = atomicAdd(&g_gather_done, 1u) + 1u == total;
+        if (last) {
+            g_gather_done = 0;                        // re-armed for the next launch (stream order)
+            __threadfence_system();                   // what the other CTAs published comes before the flags
+        }
+    }
+    __syncwarp();
+    if (!__shfl_sync(0xffffffffu, last, 0)) return;
+    // lane r tells rank r and then waits for rank r: the flags travel, and are polled, side by side
+    const bool has_peer = lane < g.world;
+    if (has_peer) st_relaxed_sys(g.flag_ptrs[lane] + g.rank, g.epoch);
     if (!g.wait) return;
-    const uint32_t* mine = g.flag_ptrs[g.rank];
     const uint32_t limit = g.spin_limit ? g.spin_limit : kPeerSpinLimit;
     uint64_t t0 = 0;
-    if (g.wait_stats) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-    bool expired = false;
-    for (int r = 0; r < g.world && !expired; ++r) {
+    if (g.wait_stats && lane == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    if (has_peer) {
+        const uint32_t* mine = g.flag_ptrs[g.rank] + lane;
         uint32_t it = 0;
-        while ((int32_t)(ld_acquire_sys(mine + r) - g.epoch) < 0) {
-            if (++it > limit) { atomicOr(&g_gather_fault, 2); expired = true; break; }
+        while ((int32_t)(ld_acquire_sys(mine) - g.epoch) < 0) {
+            if (++it > limit) { atomicOr(&g_gather_fault, 2); break; }
             __nanosleep(200);
         }
     }
-    if (g.wait_stats) {
+    __syncwarp();
+    if (g.wait_stats && lane == 0) {
         uint64_t t1;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
         g.wait_stats[0] += t1 - t0;        // one thread of one CTA per launch, launches are stream-ordered
@@ -432,10 +437,11 @@ int gather_fault_clear() {
 // stream serialization, so its launch latency overlaps that kernel's tail
 int run_merge(const float* part_o, const float* part_ml, void* out, const kivi_peer_gather* gather, float* lse,
               int out_dtype, int num_units, int n_rep, int n_splits, int D, cudaStream_t st) {
+    const int64_t rows = (int64_t)num_units * n_rep;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)num_units, (unsigned)n_rep);
-    cfg.blockDim = dim3(128);
-    cfg.dynamicSmemBytes = n_splits * sizeof(float);
+    cfg.gridDim = dim3((unsigned)((rows + kMergeWarps - 1) / kMergeWarps));
+    cfg.blockDim = dim3(kMergeWarps * 32);
+    cfg.dynamicSmemBytes = 0;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -444,9 +450,9 @@ int run_merge(const float* part_o, const float* part_ml, void* out, const kivi_p
     cfg.numAttrs = 1;
     if (gather) {
         kivi_peer_gather g = *gather;
-        KIVI_CUDA_OK(cudaLaunchKernelEx(&cfg, merge_gather_kernel, part_o, part_ml, g, out_dtype, n_splits, D));
+        KIVI_CUDA_OK(cudaLaunchKernelEx(&cfg, merge_gather_kernel, part_o, part_ml, g, out_dtype, n_splits, n_rep, rows, D));
     } else {
-        KIVI_CUDA_OK(cudaLaunchKernelEx(&cfg, merge_splits_kernel, part_o, part_ml, out, out_dtype, n_splits, D, lse));
+        KIVI_CUDA_OK(cudaLaunchKernelEx(&cfg, merge_splits_kernel, part_o, part_ml, out, out_dtype, n_splits, n_rep, rows, D, lse));
     }
     return KIVI_OK;
 }
