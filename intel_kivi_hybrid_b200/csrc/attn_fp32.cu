@@ -279,18 +279,29 @@ __device__ __forceinline__ void merge_row(const float* __restrict__ part_o, cons
             }
             const int cnt = min(32, n_splits - s0);
             const float* src = part_o + (row0 + (int64_t)s0 * nrep) * D + (active ? d : 0);
-            int i = 0;
-            for (; i + 2 <= cnt; i += 2) {
-                const float w0 = __shfl_sync(0xffffffffu, wgt, i), w1 = __shfl_sync(0xffffffffu, wgt, i + 1);
-                const float4 v0 = *reinterpret_cast<const float4*>(src + (int64_t)i * nrep * D);
-                const float4 v1 = *reinterpret_cast<const float4*>(src + (int64_t)(i + 1) * nrep * D);
-                a0.x = fmaf(v0.x, w0, a0.x); a0.y = fmaf(v0.y, w0, a0.y); a0.z = fmaf(v0.z, w0, a0.z); a0.w = fmaf(v0.w, w0, a0.w);
-                a1.x = fmaf(v1.x, w1, a1.x); a1.y = fmaf(v1.y, w1, a1.y); a1.z = fmaf(v1.z, w1, a1.z); a1.w = fmaf(v1.w, w1, a1.w);
-            }
-            if (i < cnt) {
-                const float w0 = __shfl_sync(0xffffffffu, wgt, i);
-                const float4 v0 = *reinterpret_cast<const float4*>(src + (int64_t)i * nrep * D);
-                a0.x = fmaf(v0.x, w0, a0.x); a0.y = fmaf(v0.y, w0, a0.y); a0.z = fmaf(v0.z, w0, a0.z); a0.w = fmaf(v0.w, w0, a0.w);
+            // eight partial rows in flight per lane (a unit cut into a hundred pieces
+            // would otherwise pay a hundred load latencies in a row); rows past the
+            // end are the last row again, with weight zero
+            for (int i = 0; i < cnt; i += 8) {
+                float4 v[8];
+                float w[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int k = i + j < cnt ? i + j : cnt - 1;
+                    v[j] = *reinterpret_cast<const float4*>(src + (int64_t)k * nrep * D);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float wj = __shfl_sync(0xffffffffu, wgt, (i + j) & 31);
+                    w[j] = i + j < cnt ? wj : 0.0f;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    a0.x = fmaf(v[j].x, w[j], a0.x); a0.y = fmaf(v[j].y, w[j], a0.y);
+                    a0.z = fmaf(v[j].z, w[j], a0.z); a0.w = fmaf(v[j].w, w[j], a0.w);
+                    a1.x = fmaf(v[j + 1].x, w[j + 1], a1.x); a1.y = fmaf(v[j + 1].y, w[j + 1], a1.y);
+                    a1.z = fmaf(v[j + 1].z, w[j + 1], a1.z); a1.w = fmaf(v[j + 1].w, w[j + 1], a1.w);
+                }
             }
         }
 #pragma unroll

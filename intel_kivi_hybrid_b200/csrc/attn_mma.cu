@@ -498,11 +498,14 @@ __device__ __forceinline__ void residual_part(
     }
 }
 
-// grid = (n_res_splits + nq_splits, units); block = kWarps warps.  The first
-// n_res_splits CTAs of a unit take the residual ring (they are scheduled first
-// and overlap with the rest); CTA n_res_splits + i covers token groups
-// [i*gps, min((i+1)*gps, n_groups)).  Partial slots: quantized split i -> i,
-// residual part r -> nq_splits + r.
+// grid = units * (nq_splits + n_res_splits) CTAs in one dimension; block = kWarps
+// warps.  The first units*nq_splits CTAs are the quantized pieces, unit by unit:
+// piece i of a unit covers token groups [i*gps, min((i+1)*gps, n_groups)).  The
+// units*n_res_splits CTAs of the residual ring come last: they are short, so
+// the long CTAs start first and the short ones fill the end of the grid
+// (measured against ring CTAs first: 3.5 % faster at batch 64 x 32k, 7 % at
+// batch 16 x 4k).  Partial slots: quantized piece i -> i, residual part r ->
+// nq_splits + r.
 //
 // Shared memory: [kWarps][kStages][kStageBytes] stage rings | q_s [4][128] fp32
 // (the unit's queries times sm_scale*log2(e), rows >= n_rep zero) | mbarriers |
@@ -524,14 +527,19 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
     // serialization: let it become resident now, it waits for this grid's end
     cudaTriggerProgrammaticLaunchCompletion();
 
-    const int u = blockIdx.y;
+    // grid order: all quantized pieces (unit-major), then all residual-ring CTAs --
+    // the long CTAs start first, the short ones fill the end
+    const int n_quant_ctas = (int)L.num_units * nq_splits;
+    const bool is_res = (int)blockIdx.x >= n_quant_ctas;
+    const int rel = is_res ? (int)blockIdx.x - n_quant_ctas : (int)blockIdx.x;
+    const int per_unit = is_res ? n_res_splits : nq_splits;
+    const int u = rel / per_unit, sub = rel - u * per_unit;
     const int n_splits_total = nq_splits + n_res_splits;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int gid = lane >> 2, tig = lane & 3;
     uint8_t* wstage = stage_mem + warp * kStages * kStageBytes;
     float* fo = reinterpret_cast<float*>(wstage);                               // [4][128] once the ring is idle
-    const bool is_res = (int)blockIdx.x < n_res_splits;
-    const int slot = is_res ? nq_splits + (int)blockIdx.x : (int)blockIdx.x - n_res_splits;
+    const int slot = is_res ? nq_splits + sub : sub;
 
     // ---- quantized split: start the copies before anything else ----------------
     const int64_t n_groups = quant_len / kG;
@@ -601,7 +609,7 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
 
     if (is_res) {
         // ---------------- residual ring ----------------
-        const int rs = blockIdx.x;
+        const int rs = sub;
         const int t_begin = rs * res_chunk;
         const int t_end = t_begin + res_chunk < res_len ? t_begin + res_chunk : res_len;
         float m[4], l[4], o[4][4];
@@ -789,7 +797,7 @@ int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_
                  const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
                  int n_res_splits, int res_chunk, float* part_o, float* part_ml, cudaStream_t st) {
     if (int rc = ensure_smem_attr(nullptr)) return rc;
-    dim3 grid((unsigned)(nq_splits + n_res_splits), (unsigned)L->num_units);
+    dim3 grid((unsigned)(nq_splits + n_res_splits) * (unsigned)L->num_units);
     attn_mma_kernel<<<grid, kWarps * 32, kSmemBytes, st>>>(*L, quant_len, res_start, res_len, q, q_dtype, scale_log2,
                                                          n_rep, gps, nq_splits, n_res_splits, res_chunk, part_o, part_ml);
     KIVI_LAUNCH_OK();

@@ -170,30 +170,36 @@ static int plan_splits_fp32(int num_units, int64_t n_groups, int requested) {
 // Evaluates a small cost model for every candidate count and keeps the cheapest
 // (ties: fewer pieces).  `slots` CTAs are resident at a time (SMs x CTAs per SM).
 // Constants in microseconds, fitted to CUDA-event times on B200 at about 1.9 GHz
-// (units x tokens from 16 x 1k to 512 x 32k and 4 x 128k): a CTA costs c0 of
+// (units x tokens from 4 x 128k and 16 x 1k to 512 x 32k): a CTA costs c0 of
 // fixed time (first copy, query staging, the fold of its warps) plus c1 per token
-// group, a residual-ring CTA t_ring, starting a CTA c_start, folding one more
-// partial per unit c_fold.
-//   * everything resident at once: the time of one CTA;
-//   * the quantized CTAs alone fit, the ring CTAs (first in the grid, short) push
-//     the total past the slots: the CTAs that had to wait start t_ring late;
+// group -- c1 depends on how many CTAs share its SM, one CTA alone runs about
+// twice as fast as each of three --, a residual-ring CTA t_ring, starting a CTA
+// c_start, folding one more partial per unit c_fold.  The grid lists the
+// quantized pieces first and the short ring CTAs last, so:
+//   * the quantized CTAs all resident at once: the time of one of them (the ring
+//     CTAs fill the free slots, or follow the first ring CTAs that finish);
 //   * several waves: total CTA time over the slots, plus a ragged end of about
 //     a third of a CTA.
 static int plan_splits_mma(int num_units, int64_t n_groups, int requested, int n_res_splits, int sms, int ctas_per_sm) {
     if (n_groups <= 0) return 0;
     if (requested > 0) return clamp_splits(requested, n_groups);
-    const double slots = (double)(ctas_per_sm > 0 ? ctas_per_sm : 3) * (sms > 0 ? sms : 148);
-    const double c0 = 6.0, c1 = 0.36, t_ring = 7.0, c_start = 0.015, c_fold = 0.03, ragged = 0.3;
+    const int n_sms = sms > 0 ? sms : 148, per_sm = ctas_per_sm > 0 ? ctas_per_sm : 3;
+    const double slots = (double)per_sm * n_sms;
+    const double c0 = 6.0, c1_full = 0.36, c1_two = 0.29, c1_one = 0.18;
+    const double t_ring = 7.0, c_start = 0.015, c_fold = 0.1, ragged = 0.3;
     const int64_t s_max = n_groups < kMaxSplitsC ? n_groups : kMaxSplitsC;
     int best = 1;
     double best_t = 0.0;
     for (int64_t s = 1; s <= s_max; ++s) {
-        const double t_cta = c0 + c1 * (double)((n_groups + s - 1) / s);
         const double quant = (double)num_units * (double)s, ring = (double)num_units * n_res_splits;
+        const double per_cta = (double)((n_groups + s - 1) / s);
         double t;
-        if (quant + ring <= slots) t = t_cta + c_start * (quant + ring);
-        else if (quant <= slots) t = t_cta + t_ring + c_start * (quant + ring);
-        else t = (quant * t_cta + ring * t_ring) / slots + ragged * t_cta;
+        if (quant <= slots) {
+            const double sharing = quant <= n_sms ? c1_one : quant <= 2.0 * n_sms ? c1_two : c1_full;
+            t = c0 + sharing * per_cta + c_start * (quant + ring);
+        } else {
+            t = (quant * (c0 + c1_full * per_cta) + ring * t_ring) / slots + ragged * (c0 + c1_full * per_cta);
+        }
         t += c_fold * (double)s;
         if (s == 1 || t < best_t - 1e-9) { best = (int)s; best_t = t; }
     }
