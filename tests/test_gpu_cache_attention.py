@@ -237,6 +237,17 @@ def test_attention_split_count_does_not_change_result(cabi, splits):
     assert err < TOL_F32
 
 
+@pytest.mark.parametrize("path,dtype,splits", [("fp32", torch.float32, 40), ("fp32", torch.float32, 100),
+                                               ("mma", torch.bfloat16, 33), ("mma", torch.bfloat16, 70)])
+def test_attention_with_more_than_32_partials_per_unit(cabi, path, dtype, splits):
+    """The merge walks a row's partials 32 at a time, eight loads in flight: more
+    than 32 pieces per unit (few units, long context) take its second round."""
+    kernel = cabi.ATTN_FP32 if path == "fp32" else cabi.ATTN_MMA
+    err, _, out, _ = _attention_case(cabi, 1, 2, 4, 128, 32, 128, 100 * 32, 128, dtype, 23, kernel, num_splits=splits)
+    assert err < (TOL_F32 if dtype == torch.float32 else TOL_BF16)
+    assert cabi.device_fault() == 0
+
+
 def test_attention_bf16_llama_shape_fp32_kernel(cabi):
     # config 1 slice: GQA 4:1, D=128, bf16 activations, full ring
     err, _, _, _ = _attention_case(cabi, 2, 8, 4, 128, 32, 128, 3968, 128, torch.bfloat16, 13, cabi.ATTN_FP32)
