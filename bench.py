@@ -6,9 +6,10 @@
                     [--scaling strong|weak] [--gather auto|peer|nccl]
 
 One "step" = one layer-step of fused decode attention over the packed cache of
-the workload (B*Hkv units, Sq quantized + Sr residual tokens each); on one GPU
-the steps are replayed from a CUDA graph (one pass over the rotating layer
-buffers per replay), so small workloads are not bound by host launch overhead.
+the workload (B*Hkv units, Sq quantized + Sr residual tokens each); the steps
+are replayed from a CUDA graph (one pass over the rotating layer buffers per
+replay), so small workloads are not bound by host launch overhead -- at N GPUs
+too when the exchange is the fused one, whose call counter lives on the device.
 At N GPUs the (batch, kv_head) units are sharded over the ranks and the
 per-layer outputs all-gathered: --scaling strong (default) keeps the workload's
 global batch and gives every rank 1/N of its units, --scaling weak gives every
@@ -252,21 +253,23 @@ def run_ours(args, wl):
     equal_shards = U * world == U_total
     # the exchange of a step: an NCCL all-gather after the kernels, or the
     # attention's last kernel storing its rows into every rank's buffer itself
-    pg, gather_note = None, None
+    pg, pg_host, gather_note = None, None, None
     wait_stats = torch.zeros(2, dtype=torch.int64, device=dev)
     if world > 1 and args.gather in ("peer", "auto"):
         from intel_kivi_hybrid_b200.parallel import PeerGather
         try:                                   # raises on every rank or on none
-            pg = PeerGather(U_total, n_rep, D, dtype, rank, world)
+            pg = PeerGather(U_total, n_rep, D, dtype, rank, world, device_epoch=True)   # replayable from a CUDA graph
+            pg_host = PeerGather(U_total, n_rep, D, dtype, rank, world)      # host-kept epoch: the end-to-end loop
         except RuntimeError as exc:
-            gather_note = f"peer-gather setup failed ({exc}); NCCL all-gather used"
+            pg, gather_note = None, f"peer-gather setup failed ({exc}); NCCL all-gather used"
     if world > 1 and not equal_shards and pg is None:
         raise SystemExit("ragged unit shards need --gather peer/auto (the NCCL path uses all_gather_into_tensor)")
 
-    def attend(store, q=q, stats=None):
+    def attend(store, q=q, stats=None, want_rows=False):
         if pg is not None:
             store.attention_gather(q, pg.descriptor(wait_stats=stats), dtype, n_rep, path=path, num_splits=args.splits)
-            return pg.gathered()
+            # (finding the buffer of the last call reads the device-kept counter back: only the self-check asks)
+            return pg.gathered() if want_rows else None
         store.attention(q, out=out, n_rep=n_rep, path=path, num_splits=args.splits)
         if world > 1:
             dist.all_gather_into_tensor(gathered, out)
@@ -297,7 +300,7 @@ def run_ours(args, wl):
         def gathered_equals_alone():
             ok = 1
             for _ in range(2):
-                g = attend(stores[0])
+                g = attend(stores[0], want_rows=True)
                 torch.cuda.synchronize()
                 ok &= int(torch.equal(g[u0:u1], alone))
             ok &= int(cabi.device_fault() == 0)
@@ -311,8 +314,8 @@ def run_ours(args, wl):
             gather_ok = False
         if not gather_ok and pg is not None and equal_shards:
             gather_note = "fused exchange failed its bitwise self-check; NCCL all-gather used"
-            pg.close()
-            pg = None
+            pg.close(); pg_host.close()
+            pg = pg_host = None
             cabi.device_fault_clear()
             gather_ok = gathered_equals_alone()
     del k0, v0
@@ -326,37 +329,50 @@ def run_ours(args, wl):
     barrier()
     # Launch-bound case (small workloads): capture one pass over the rotating layer
     # buffers in a CUDA graph and replay it; a "step" is still one layer-step.
-    graph = None
-    if args.graph and world == 1:
+    def capture(fn):
+        """One pass of fn over the rotating layer buffers as a CUDA graph (None if capture is unavailable)."""
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
                 for i in range(n_buf):
-                    step(i)
+                    fn(i)
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
                 for i in range(n_buf):
-                    step(i)
+                    fn(i)
             for _ in range(3):
-                graph.replay()
+                g.replay()
             torch.cuda.synchronize()
+            return g
         except Exception as exc:          # capture unavailable: time plain launches instead
             print(f"[bench] CUDA graph capture failed ({exc}); timing plain launches", file=sys.stderr)
-            graph = None
             torch.cuda.synchronize()
+            return None
 
-    def timed(n_steps, use_graph, stats=None, fn=None):
+    # at N > 1 only the fused exchange is replayable (its call counter lives on the
+    # device); every rank must take the same decision, or none replays
+    graph = None
+    if args.graph and (world == 1 or pg is not None):
+        graph = capture(lambda i: step(i, wait_stats if pg is not None else None))
+        if world > 1:
+            ok = torch.tensor([int(graph is not None)], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if not bool(ok.item()):
+                graph = None
+
+    def timed(n_steps, use_graph, stats=None, fn=None, g=None):
         """(total ms, sorted per-step ms) of n_steps steps, CUDA events on the launching stream."""
         fn = fn or (lambda i: step(i, stats))
         if use_graph:
+            g = g or graph
             reps = max(1, (n_steps + n_buf - 1) // n_buf)
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
             ev[0].record()
             for i in range(reps):
-                graph.replay()
+                g.replay()
                 ev[i + 1].record()
             barrier()
             per = sorted(ev[i].elapsed_time(ev[i + 1]) / n_buf for i in range(reps))
@@ -389,13 +405,19 @@ def run_ours(args, wl):
     value = by_total / (ms_step * 1e-3) / 1e9
 
     extra = {}
-    if world == 1 and graph is not None:
+    if graph is not None:
         ng_ms, ng_per = timed(args.steps, False)
         extra["ms_per_step_no_graph"] = statistics.median(ng_per)
     if world > 1:
         # the same steps without the exchange: what every rank needs for its own units
-        lo_ms, lo_per = timed(args.steps, False, fn=lambda i: stores[i % n_buf].attention(q, out=out, n_rep=n_rep, path=path,
-                                                                                          num_splits=args.splits))
+        local = lambda i: stores[i % n_buf].attention(q, out=out, n_rep=n_rep, path=path, num_splits=args.splits)
+        g_local = capture(local) if graph is not None else None
+        if world > 1:
+            ok = torch.tensor([int(g_local is not None)], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if not bool(ok.item()):
+                g_local = None
+        lo_ms, lo_per = timed(args.steps, g_local is not None, fn=local, g=g_local)
         t = torch.tensor([statistics.median(lo_per), -statistics.median(lo_per)], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ws = wait_stats.clone().double()
@@ -411,7 +433,8 @@ def run_ours(args, wl):
             "us_wait_for_peers_in_kernel_min": -float(tw[1]) if pg is not None else None,
             "limiter": ("skew between ranks" if slowest - fastest > max(exchange, 0.0) else
                         "exchange (peer stores, flags, wait)" if exchange > 0.02 * slowest else "the attention kernel itself"),
-            "note": "local = the same attention without the exchange, launched from Python like the timed steps"}
+            "note": "local = the same attention without the exchange, launched the same way as the timed steps "
+                    "(replayed from a CUDA graph when they are)"}
 
     # ---- end to end: host q + host new K/V token in, host out, every step ----
     # through the library's host-to-host decode step (one foreign call per step; the
@@ -433,7 +456,7 @@ def run_ours(args, wl):
             h_out.copy_(attend(e2e_store, d_q), non_blocking=True)
         elif pg is not None:
             e2e_store.decode_step_host(h_q, h_k, h_v, h_out, n_rep, num_splits=args.splits, path=path,
-                                       direct=not args.e2e_staged, gather=pg.descriptor(), gather_units=U_total)
+                                       direct=not args.e2e_staged, gather=pg_host.descriptor(), gather_units=U_total)
         else:
             e2e_store.decode_step_host(h_q, h_k, h_v, h_out, n_rep, num_splits=args.splits, path=path,
                                        chunks=args.e2e_chunks, direct=not args.e2e_staged)
@@ -530,7 +553,7 @@ def run_ours(args, wl):
         line.update(extra)
         print(json.dumps(line))
     if pg is not None:
-        pg.close()
+        pg.close(); pg_host.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -662,7 +685,7 @@ def main():
     ap.add_argument("--e2e-chunks", type=int, default=1, help="with --e2e-staged: chunks of units whose copies and kernels overlap")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", dest="graph", action="store_false",
-                    help="launch every step from Python instead of replaying a CUDA graph (single GPU only)")
+                    help="launch every step from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.workload == "ops":
         return run_operators(args)

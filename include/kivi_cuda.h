@@ -292,6 +292,12 @@ int kivi_decode_attention_noalloc(const kivi_layer* layer, int64_t quant_len, in
  * Re-use: a rank may run one call ahead of its peers, so alternate between two
  * gathered buffers (e.g. by epoch parity) when the consumer of call e may still
  * be reading while call e+1 of a faster rank writes.
+ * epoch_dev != NULL (for a call captured in a CUDA graph, whose arguments are
+ * frozen): the epoch is kept on the device.  The call's epoch is *epoch_dev + 1,
+ * which the kernel stores back when it is done; `epoch` is ignored; out_ptrs[r]
+ * names the first of rank r's two gathered buffers, alt_bytes apart, and the
+ * call writes buffer (epoch & 1).  Every rank keeps its own counter (zero before
+ * the first call); all ranks must make the same sequence of calls.
  * ---------------------------------------------------------------------- */
 #define KIVI_PEER_MAX_WORLD 8
 typedef struct kivi_peer_gather {
@@ -305,6 +311,8 @@ typedef struct kivi_peer_gather {
     uint32_t reserved;
     uint64_t* wait_stats; /* optional device uint64[2]: the kernel adds the nanoseconds it spent waiting
                              for the other ranks to [0] and 1 to [1]; NULL = not recorded */
+    uint32_t* epoch_dev;  /* optional device counter of this rank's calls (see above); NULL = use `epoch` */
+    int64_t alt_bytes;    /* with epoch_dev: distance in bytes between a rank's two gathered buffers */
 } kivi_peer_gather;
 
 int kivi_peer_alloc(size_t bytes, void** ptr_out, unsigned char handle_out[64]);

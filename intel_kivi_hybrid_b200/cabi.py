@@ -36,7 +36,8 @@ class PeerGatherDesc(_c.Structure):
     """struct kivi_peer_gather of include/kivi_cuda.h."""
     _fields_ = [("rank", _c.c_int32), ("world", _c.c_int32), ("out_ptrs", _vp * PEER_MAX_WORLD),
                 ("flag_ptrs", _vp * PEER_MAX_WORLD), ("unit_offset", _c.c_int64), ("epoch", _c.c_uint32),
-                ("wait", _c.c_int32), ("spin_limit", _c.c_uint32), ("reserved", _c.c_uint32), ("wait_stats", _vp)]
+                ("wait", _c.c_int32), ("spin_limit", _c.c_uint32), ("reserved", _c.c_uint32), ("wait_stats", _vp),
+                ("epoch_dev", _vp), ("alt_bytes", _c.c_int64)]
 
 
 SIGNATURES = {

@@ -375,10 +375,11 @@ struct PeerSink {
     kivi_peer_gather g;
     int out_dtype;
     int64_t base;              // element offset of this rank's first row in a gathered buffer
+    int64_t alt;               // byte offset of the buffer this call writes (device-kept epoch: odd calls)
     __device__ void operator()(int64_t i, float4 v) const {
 #pragma unroll
         for (int r = 0; r < KIVI_PEER_MAX_WORLD; ++r)
-            if (r < g.world) store_quad(g.out_ptrs[r], out_dtype, base + i, v);
+            if (r < g.world) store_quad(reinterpret_cast<uint8_t*>(g.out_ptrs[r]) + alt, out_dtype, base + i, v);
     }
 };
 
@@ -388,9 +389,18 @@ __global__ void __launch_bounds__(kMergeWarps * 32)
 merge_gather_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                     kivi_peer_gather g, int out_dtype, int n_splits, int nrep, int64_t rows, int D) {
     cudaGridDependencySynchronize();
+    // Epoch kept on the device (a call replayed from a CUDA graph): every CTA
+    // reads the counter here; the last CTA stores it back after all CTAs have
+    // counted themselves in, that is after all of them have read it.
+    uint32_t epoch = g.epoch;
+    int64_t alt = 0;
+    if (g.epoch_dev != nullptr) {
+        epoch = *reinterpret_cast<const volatile uint32_t*>(g.epoch_dev) + 1u;
+        alt = (epoch & 1u) ? g.alt_bytes : 0;
+    }
     const int64_t row = (int64_t)blockIdx.x * kMergeWarps + (threadIdx.x >> 5);
     if (row < rows)
-        merge_row(part_o, part_ml, n_splits, nrep, row, D, PeerSink{g, out_dtype, g.unit_offset * (int64_t)nrep * D}, nullptr);
+        merge_row(part_o, part_ml, n_splits, nrep, row, D, PeerSink{g, out_dtype, g.unit_offset * (int64_t)nrep * D, alt}, nullptr);
     __syncthreads();                                  // the CTA's stores are issued
     if (threadIdx.x >= 32) return;                    // warp 0 carries the protocol
     const int lane = threadIdx.x;
@@ -401,6 +411,7 @@ merge_gather_kernel(const float* __restrict__ part_o, const float* __restrict__ 
         last = atomicAdd(&g_gather_done, 1u) + 1u == total;
         if (last) {
             g_gather_done = 0;                        // re-armed for the next launch (stream order)
+            if (g.epoch_dev != nullptr) *g.epoch_dev = epoch;
             __threadfence_system();                   // what the other CTAs published comes before the flags
         }
     }
@@ -408,7 +419,7 @@ merge_gather_kernel(const float* __restrict__ part_o, const float* __restrict__ 
     if (!__shfl_sync(0xffffffffu, last, 0)) return;
     // lane r tells rank r and then waits for rank r: the flags travel, and are polled, side by side
     const bool has_peer = lane < g.world;
-    if (has_peer) st_relaxed_sys(g.flag_ptrs[lane] + g.rank, g.epoch);
+    if (has_peer) st_relaxed_sys(g.flag_ptrs[lane] + g.rank, epoch);
     if (!g.wait) return;
     const uint32_t limit = g.spin_limit ? g.spin_limit : kPeerSpinLimit;
     uint64_t t0 = 0;
@@ -416,7 +427,7 @@ merge_gather_kernel(const float* __restrict__ part_o, const float* __restrict__ 
     if (has_peer) {
         const uint32_t* mine = g.flag_ptrs[g.rank] + lane;
         uint32_t it = 0;
-        while ((int32_t)(ld_acquire_sys(mine) - g.epoch) < 0) {
+        while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
             if (++it > limit) { atomicOr(&g_gather_fault, 2); break; }
             __nanosleep(200);
         }

@@ -313,7 +313,8 @@ extern "C" int kivi_decode_attention_gather(const kivi_layer* L, int64_t quant_l
     KIVI_REQUIRE(gather->world >= 1 && gather->world <= KIVI_PEER_MAX_WORLD, "world (%d) outside 1..%d", gather->world, KIVI_PEER_MAX_WORLD);
     KIVI_REQUIRE(gather->rank >= 0 && gather->rank < gather->world, "rank (%d) outside 0..%d", gather->rank, gather->world - 1);
     KIVI_REQUIRE(gather->unit_offset >= 0, "unit_offset is negative");
-    KIVI_REQUIRE(gather->epoch != 0, "epoch starts at 1");
+    KIVI_REQUIRE(gather->epoch_dev != nullptr || gather->epoch != 0, "epoch starts at 1");
+    KIVI_REQUIRE(gather->epoch_dev == nullptr || gather->alt_bytes > 0, "a device-kept epoch needs the distance between the two buffers (alt_bytes)");
     for (int r = 0; r < gather->world; ++r)
         KIVI_REQUIRE(gather->out_ptrs[r] != nullptr && gather->flag_ptrs[r] != nullptr, "buffer or flag pointer of rank %d is null", r);
     return decode_attention_impl(L, quant_len, res_start, res_len, q, q_dtype, nullptr, gather, nullptr, out_dtype, n_rep,

@@ -87,6 +87,8 @@ extern "C" int kivi_decode_step_host(const kivi_layer* L, int64_t* quant_len, in
     KIVI_REQUIRE(L && quant_len && res_start && res_len, "layer and counters must be given");
     KIVI_REQUIRE(h_q && h_new_k && h_new_v && h_out && workspace, "host and workspace buffers must be given");
     KIVI_REQUIRE(direct || d_stage, "a staging buffer is needed unless direct access is asked for");
+    KIVI_REQUIRE(gather == nullptr || gather->epoch_dev == nullptr,
+                 "the gathered rows are copied back from the buffer the host names: use a host-kept epoch here");
     KIVI_REQUIRE(dtype == KIVI_F32 || dtype == KIVI_BF16, "dtype must be KIVI_F32 or KIVI_BF16");
     KIVI_REQUIRE(out_dtype == KIVI_F32 || out_dtype == KIVI_BF16, "out dtype must be KIVI_F32 or KIVI_BF16");
     KIVI_REQUIRE(n_rep >= 1 && n_rep <= 8, "n_rep (%d) outside 1..8", n_rep);

@@ -101,7 +101,8 @@ def merge_token_shards(outs: torch.Tensor, lses: torch.Tensor) -> torch.Tensor:
 class PeerGather:
     """Gathered attention-output buffers of the ranks of one node, mapped into
     every rank (CUDA IPC through kivi_peer_alloc / kivi_peer_open), for
-    LayerStore.attention_gather.
+    LayerStore.attention_gather.  ``device_epoch=True`` keeps the call counter on
+    the GPU: calls can then be captured in a CUDA graph and replayed.
 
     Each rank owns two gathered buffers [n_units * n_rep * D] (alternated by
     epoch parity, so a rank that runs one call ahead never overwrites what a
@@ -110,7 +111,8 @@ class PeerGather:
     counts per rank are not required.
     """
 
-    def __init__(self, n_units: int, n_rep: int, head_dim: int, dtype, rank: int, world: int, group=None):
+    def __init__(self, n_units: int, n_rep: int, head_dim: int, dtype, rank: int, world: int, group=None,
+                 device_epoch: bool = False):
         import torch.distributed as dist
         from . import cabi
         assert 1 <= world <= cabi.PEER_MAX_WORLD
@@ -148,6 +150,10 @@ class PeerGather:
             self._ptrs, self._own_ptr = [], 0
             raise RuntimeError("peer-gather setup failed: " + "; ".join(sorted(set(failed))))
         self.epoch = 0
+        # device_epoch: the call counter lives on the GPU, so that a call can be
+        # captured in a CUDA graph and replayed (a captured descriptor is frozen)
+        self._epoch_dev = (torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()))
+                           if device_epoch else None)
         dist.barrier(group=group)
 
     def descriptor(self, wait: bool = True, spin_limit: int = 0, wait_stats: torch.Tensor = None):
@@ -162,6 +168,8 @@ class PeerGather:
         d.spin_limit = int(spin_limit)
         d.wait_stats = wait_stats.data_ptr() if wait_stats is not None else None
         half = (self.epoch & 1) * self._buf_bytes
+        if self._epoch_dev is not None:                 # the kernel picks the half from its own counter
+            d.epoch_dev, d.alt_bytes, half = self._epoch_dev.data_ptr(), self._buf_bytes, 0
         for r in range(self.world):
             d.out_ptrs[r] = self._ptrs[r] + half
             d.flag_ptrs[r] = self._ptrs[r] + 2 * self._buf_bytes
@@ -169,8 +177,11 @@ class PeerGather:
 
     def gathered(self) -> torch.Tensor:
         """[n_units, n_rep, D] view of this rank's gathered buffer of the last
-        call (valid once that call's kernels have completed on the stream)."""
+        call (valid once that call's kernels have completed on the stream; with a
+        device-kept epoch the counter is read back, which synchronises)."""
         n = self.n_units * self.n_rep * self.D
+        if self._epoch_dev is not None:
+            self.epoch = int(self._epoch_dev.item())
         half = (self.epoch & 1) * self._buf_bytes
         device = torch.device("cuda", torch.cuda.current_device())
         return _tensor_from_ptr(self._own_ptr + half, n, self.dtype, device).view(self.n_units, self.n_rep, self.D)

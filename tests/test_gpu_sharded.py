@@ -75,7 +75,43 @@ if world == 1:
         assert (a.quant_len, a.res_start, a.res_len) == (b.quant_len, b.res_start, b.res_len)
         assert torch.equal(h_out, want.cpu()), "host decode step through the peer gather differs"
     pg.close()
+def graph_replayed_gather(store, q_local, n_units, rank, world, want):
+    """The exchange with its call counter on the device: plain calls, then two
+    calls captured in a CUDA graph and replayed (a captured descriptor is frozen,
+    the kernel advances the epoch and alternates the buffers itself)."""
+    from intel_kivi_hybrid_b200.parallel import PeerGather
+    pg = PeerGather(n_units, n_rep, D, torch.float32, rank, world, device_epoch=True)
+    for i in range(3):
+        store.attention_gather(q_local, pg.descriptor(), torch.float32, n_rep, num_splits=3)
+        torch.cuda.synchronize()
+        assert torch.equal(pg.gathered(), want), "device-epoch gather differs"
+        assert pg.epoch == i + 1
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            store.attention_gather(q_local, pg.descriptor(), torch.float32, n_rep, num_splits=3)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(2):
+            store.attention_gather(q_local, pg.descriptor(), torch.float32, n_rep, num_splits=3)
+    for rep in range(3):
+        pg.gathered().zero_()                           # the replay's second call rewrites this half
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(pg.gathered(), want), "graph-replayed gather differs"
+        assert pg.epoch == 5 + 2 * (rep + 1)
+    assert cabi.device_fault() == 0
+    pg.close()
+if world == 1:
+    q_all = q.to(dev).reshape(B * Hkv, n_rep, D)     # (the store has taken two more tokens above: its own answer is the reference)
+    graph_replayed_gather(st, q_all, B * Hkv, 0, 1, st.attention(q_all, n_rep=n_rep, num_splits=3, out_dtype=torch.float32))
 else:
+    u_per = B * Hkv // world
+    graph_replayed_gather(sharded._stores[0], q.to(dev).reshape(B * Hkv, n_rep, D)[rank * u_per:(rank + 1) * u_per].contiguous(),
+                          B * Hkv, rank, world, out_1.reshape(B * Hkv, n_rep, D))
     peer = KiviCache(num_layers=1, head_dim=D, device=dev, shard=(rank, world), gather="peer")
     peer.add_tokens(((K[:, :, :T - 3].to(dev), V[:, :, :T - 3].to(dev)),))
     peer.add_tokens(((K.to(dev), V.to(dev)),))

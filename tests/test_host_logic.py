@@ -129,7 +129,7 @@ def test_peer_gather_descriptor_alternates_buffers():
     from intel_kivi_hybrid_b200.parallel import PeerGather
     pg = PeerGather.__new__(PeerGather)          # no allocation: only the descriptor arithmetic
     pg._cabi, pg.rank, pg.world, pg.u0, pg.epoch = cabi, 1, 2, 4, 0
-    pg._buf_bytes, pg._ptrs = 4096, [0x10000, 0x20000]
+    pg._buf_bytes, pg._ptrs, pg._epoch_dev = 4096, [0x10000, 0x20000], None
     d1, d2, d3 = pg.descriptor(), pg.descriptor(wait=False), pg.descriptor()
     assert (d1.epoch, d2.epoch, d3.epoch) == (1, 2, 3) and (d1.wait, d2.wait) == (1, 0)
     assert (d1.rank, d1.world, d1.unit_offset) == (1, 2, 4)
@@ -137,7 +137,12 @@ def test_peer_gather_descriptor_alternates_buffers():
     assert [d2.out_ptrs[r] for r in range(2)] == [0x10000, 0x20000]
     assert [d3.out_ptrs[r] for r in range(2)] == [d1.out_ptrs[r] for r in range(2)]
     assert [d1.flag_ptrs[r] for r in range(2)] == [0x10000 + 8192, 0x20000 + 8192]
-    assert d1.out_ptrs[2] is None
+    assert d1.out_ptrs[2] is None and d1.epoch_dev is None
+    # call counter on the device: the descriptor names the first buffer and the distance to the second
+    pg._epoch_dev = types.SimpleNamespace(data_ptr=lambda: 0x30000)
+    d4 = pg.descriptor()
+    assert (d4.epoch_dev, d4.alt_bytes) == (0x30000, 4096)
+    assert [d4.out_ptrs[r] for r in range(2)] == [0x10000, 0x20000]
 
 
 def test_detect_model_config_families():
@@ -238,7 +243,7 @@ def test_operands_on_different_devices_are_refused_before_any_launch():
 
 def test_peer_gather_descriptor_layout_matches_the_header():
     """struct kivi_peer_gather as ctypes sees it: the C compiler's layout of the
-    header's fields (two ints, 2 x 8 pointers, int64, four 32-bit words)."""
+    header's fields (two ints, 2 x 8 pointers, int64, four 32-bit words, two pointers' worth at the end)."""
     from intel_kivi_hybrid_b200 import cabi
     d = cabi.PeerGatherDesc
     assert d.out_ptrs.offset == 8 and d.flag_ptrs.offset == 8 + 8 * cabi.PEER_MAX_WORLD
@@ -246,7 +251,9 @@ def test_peer_gather_descriptor_layout_matches_the_header():
     assert (d.epoch.offset, d.wait.offset, d.spin_limit.offset) == (d.unit_offset.offset + 8, d.unit_offset.offset + 12,
                                                                     d.unit_offset.offset + 16)
     import ctypes
-    assert d.wait_stats.offset == d.unit_offset.offset + 24 and ctypes.sizeof(d) == d.unit_offset.offset + 32
+    assert d.wait_stats.offset == d.unit_offset.offset + 24
+    assert (d.epoch_dev.offset, d.alt_bytes.offset) == (d.unit_offset.offset + 32, d.unit_offset.offset + 40)
+    assert ctypes.sizeof(d) == d.unit_offset.offset + 48
 
 
 def test_attention_split_plan_is_pinned():
