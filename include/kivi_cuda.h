@@ -192,7 +192,7 @@ int kivi_cache_import_keys(const kivi_layer* layer, const uint8_t* packed,
  * ---------------------------------------------------------------------- */
 #define KIVI_ATTN_AUTO 0
 #define KIVI_ATTN_FP32 1 /* CUDA-core fp32 kernel, any supported shape */
-#define KIVI_ATTN_MMA 2  /* tensor-core kernel: D=128, G=32, n_rep<=4, bf16 or f32 q */
+#define KIVI_ATTN_MMA 2  /* tensor-core kernel: D=128, G=32, n_rep<=8, bf16 or f32 q */
 
 size_t kivi_decode_attention_workspace(int num_units, int n_rep, int head_dim, int num_splits);
 int kivi_decode_attention_max_splits(void);

@@ -1,5 +1,6 @@
 // Fused decode attention over the packed KIVI cache: tensor-core kernel for
-// head_dim 128, group_size 32, up to 4 query heads per KV head (sm_100a).
+// head_dim 128, group_size 32, up to 8 query heads per KV head in blocks of
+// four per CTA (sm_100a).
 //
 // Decode attention over 2-bit codes is instruction-bound before it is HBM-bound:
 // one quantized (token, kv_head) is 128 bytes of HBM but 256 codes that each
@@ -498,8 +499,9 @@ __device__ __forceinline__ void residual_part(
     }
 }
 
-// grid = units * (nq_splits + n_res_splits) CTAs in one dimension; block = kWarps
-// warps.  The first units*nq_splits CTAs are the quantized pieces, unit by unit:
+// grid = units * head blocks * (nq_splits + n_res_splits) CTAs in one dimension
+// (head blocks = ceil(n_rep / 4): a CTA serves up to four query heads); block =
+// kWarps warps.  The first units*nq_splits CTAs are the quantized pieces, unit by unit:
 // piece i of a unit covers token groups [i*gps, min((i+1)*gps, n_groups)).  The
 // units*n_res_splits CTAs of the residual ring come last: they are short, so
 // the long CTAs start first and the short ones fill the end of the grid
@@ -508,7 +510,7 @@ __device__ __forceinline__ void residual_part(
 // nq_splits + r.
 //
 // Shared memory: [kWarps][kStages][kStageBytes] stage rings | q_s [4][128] fp32
-// (the unit's queries times sm_scale*log2(e), rows >= n_rep zero) | mbarriers |
+// (the CTA's up to four query heads times sm_scale*log2(e), absent rows zero) | mbarriers |
 // (max, sum) of the warps.  When a warp is done, its ring doubles as the
 // [4][128] buffer its scaled output goes to; the CTA then adds the warps'
 // buffers in warp order (deterministic) and writes one partial.
@@ -529,11 +531,17 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
 
     // grid order: all quantized pieces (unit-major), then all residual-ring CTAs --
     // the long CTAs start first, the short ones fill the end
-    const int n_quant_ctas = (int)L.num_units * nq_splits;
+    // With more than four query heads per KV head a unit is served by two CTAs per
+    // piece, one per block of four heads (they run side by side, so the second
+    // read of the piece mostly comes from L2).
+    const int head_blocks = (n_rep + 3) >> 2;
+    const int n_quant_ctas = (int)L.num_units * head_blocks * nq_splits;
     const bool is_res = (int)blockIdx.x >= n_quant_ctas;
     const int rel = is_res ? (int)blockIdx.x - n_quant_ctas : (int)blockIdx.x;
     const int per_unit = is_res ? n_res_splits : nq_splits;
-    const int u = rel / per_unit, sub = rel - u * per_unit;
+    const int uv = rel / per_unit, sub = rel - uv * per_unit;
+    const int u = uv / head_blocks, head0 = 4 * (uv - u * head_blocks);
+    const int n_heads = n_rep - head0 < 4 ? n_rep - head0 : 4;       // heads of this CTA: head0 .. head0 + n_heads - 1
     const int n_splits_total = nq_splits + n_res_splits;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int gid = lane >> 2, tig = lane & 3;
@@ -596,8 +604,8 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
         for (int i = threadIdx.x; i < kD; i += blockDim.x) {             // 128 float4 = [4][128]
             const int hh = i >> 5, cc = (i & 31) * 4;
             float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            if (hh < n_rep) {
-                const int64_t e = ((int64_t)u * n_rep + hh) * kD + cc;
+            if (hh < n_heads) {
+                const int64_t e = ((int64_t)u * n_rep + head0 + hh) * kD + cc;
                 if (q_dtype == KIVI_BF16) RowVec<__nv_bfloat16>::load4(reinterpret_cast<const __nv_bfloat16*>(q) + e, v);
                 else RowVec<float>::load4(reinterpret_cast<const float*>(q) + e, v);
             }
@@ -715,10 +723,10 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
     __syncthreads();
 
     // ---- the CTA's partial: warps added in warp order ------------------------------
-    const int64_t pbase = ((int64_t)u * n_splits_total + slot) * n_rep;
+    const int64_t pbase = ((int64_t)u * n_splits_total + slot) * n_rep + head0;
     for (int i = threadIdx.x; i < kD; i += blockDim.x) {
         const int h = i >> 5, cc = (i & 31) * 4;
-        if (h < n_rep) {
+        if (h < n_heads) {
             float4 a = *reinterpret_cast<const float4*>(stage_mem + h * kD * 4 + cc * 4);
 #pragma unroll
             for (int w2 = 1; w2 < kWarps; ++w2) {
@@ -728,7 +736,7 @@ attn_mma_kernel(kivi_layer L, int64_t quant_len, int res_start, int res_len,
             *reinterpret_cast<float4*>(part_o + (pbase + h) * kD + cc) = a;
         }
     }
-    if (threadIdx.x < n_rep) {
+    if (threadIdx.x < n_heads) {
         const int h = threadIdx.x;
         float Mh = -INFINITY, ls = 0.0f;
         for (int w2 = 0; w2 < kWarps; ++w2) Mh = fmaxf(Mh, ml_s[(w2 * 4 + h) * 2]);
@@ -750,7 +758,7 @@ static_assert(kWarps * 32 >= 32, "at least one warp");
 
 bool attn_mma_supported(const kivi_layer* L, int n_rep, const void* q) {
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-    return L->head_dim == kD && L->group_size == kG && n_rep >= 1 && n_rep <= 4 && al(q) &&
+    return L->head_dim == kD && L->group_size == kG && n_rep >= 1 && n_rep <= 8 && al(q) &&
            al(L->k_res) && al(L->v_res) && al(L->k_codes) && al(L->k_scales) && al(L->k_zeros) && al(L->v_codes) && al(L->v_scales) && al(L->v_zeros);
 }
 
@@ -797,7 +805,7 @@ int run_attn_mma(const kivi_layer* L, int64_t quant_len, int res_start, int res_
                  const void* q, int q_dtype, int n_rep, float scale_log2, int nq_splits, int gps,
                  int n_res_splits, int res_chunk, float* part_o, float* part_ml, cudaStream_t st) {
     if (int rc = ensure_smem_attr(nullptr)) return rc;
-    dim3 grid((unsigned)(nq_splits + n_res_splits) * (unsigned)L->num_units);
+    dim3 grid((unsigned)(nq_splits + n_res_splits) * (unsigned)L->num_units * (unsigned)((n_rep + 3) / 4));
     attn_mma_kernel<<<grid, kWarps * 32, kSmemBytes, st>>>(*L, quant_len, res_start, res_len, q, q_dtype, scale_log2,
                                                          n_rep, gps, nq_splits, n_res_splits, res_chunk, part_o, part_ml);
     KIVI_LAUNCH_OK();

@@ -213,10 +213,10 @@ extern "C" int kivi_decode_attention_plan(int num_units, int64_t quant_len, int 
                  "invalid shape");
     KIVI_REQUIRE(num_splits >= 0 && num_splits <= kMaxSplitsC, "num_splits (%d) outside 0..%d", num_splits, kMaxSplitsC);
     KIVI_REQUIRE(tensor_cores_out && quant_splits_out && residual_parts_out, "output pointers must be given");
-    const bool shape_ok = head_dim == 128 && group_size == 32 && n_rep >= 1 && n_rep <= 4;
+    const bool shape_ok = head_dim == 128 && group_size == 32 && n_rep >= 1 && n_rep <= 8;
     const bool use_mma = path == KIVI_ATTN_MMA ? shape_ok : path == KIVI_ATTN_AUTO ? (shape_ok && q_dtype == KIVI_BF16) : false;
     if (path == KIVI_ATTN_MMA && !shape_ok) {
-        set_error("tensor-core path needs head_dim 128, group_size 32, n_rep <= 4 (got %d, %d, %d)", head_dim, group_size, n_rep);
+        set_error("tensor-core path needs head_dim 128, group_size 32, n_rep <= 8 (got %d, %d, %d)", head_dim, group_size, n_rep);
         return KIVI_ERR_UNSUPPORTED;
     }
     int n_res = res_len > 0 ? 1 : 0, chunk = res_len;
@@ -225,7 +225,7 @@ extern "C" int kivi_decode_attention_plan(int num_units, int64_t quant_len, int 
     if (sms <= 0) sms = num_sms();
     if (ctas_per_sm <= 0) ctas_per_sm = attn_mma_ctas_per_sm();
     *tensor_cores_out = use_mma ? 1 : 0;
-    *quant_splits_out = use_mma ? plan_splits_mma(num_units, n_groups, num_splits, n_res, sms, ctas_per_sm)
+    *quant_splits_out = use_mma ? plan_splits_mma(num_units * ((n_rep + 3) / 4), n_groups, num_splits, n_res, sms, ctas_per_sm)
                                 : plan_splits_fp32(num_units, n_groups, num_splits);
     *residual_parts_out = n_res;
     return KIVI_OK;
@@ -251,7 +251,7 @@ static int decode_attention_impl(const kivi_layer* L, int64_t quant_len, int res
     bool use_mma = false;
     if (path == KIVI_ATTN_MMA) {
         if (!attn_mma_supported(L, n_rep, q)) {
-            set_error("tensor-core path needs head_dim 128, group_size 32, n_rep <= 4 (got %d, %d, %d) and 16-byte aligned arrays", D, G, n_rep);
+            set_error("tensor-core path needs head_dim 128, group_size 32, n_rep <= 8 (got %d, %d, %d) and 16-byte aligned arrays", D, G, n_rep);
             return KIVI_ERR_UNSUPPORTED;
         }
         use_mma = true;
@@ -262,7 +262,7 @@ static int decode_attention_impl(const kivi_layer* L, int64_t quant_len, int res
     }
     int n_res_splits = res_len > 0 ? 1 : 0, res_chunk = res_len;
     if (use_mma) attn_mma_residual_plan(res_len, &n_res_splits, &res_chunk);
-    const int nq_splits = use_mma ? plan_splits_mma(L->num_units, n_groups, num_splits, n_res_splits, num_sms(), attn_mma_ctas_per_sm())
+    const int nq_splits = use_mma ? plan_splits_mma(L->num_units * ((n_rep + 3) / 4), n_groups, num_splits, n_res_splits, num_sms(), attn_mma_ctas_per_sm())
                                   : plan_splits_fp32(L->num_units, n_groups, num_splits);
     const int gps = nq_splits > 0 ? (int)((n_groups + nq_splits - 1) / nq_splits) : 0;
     const int n_splits = nq_splits + n_res_splits;

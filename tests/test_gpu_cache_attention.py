@@ -273,7 +273,8 @@ def test_attention_errors(cabi):
 
 @pytest.mark.parametrize("n_quant,n_res,n_rep,splits", [
     (3968, 128, 4, 0), (32, 0, 4, 0), (64, 5, 4, 1), (96, 128, 4, 3), (2048 + 32, 100, 4, 5),
-    (992, 128, 1, 0), (992, 128, 2, 2), (992, 128, 3, 0), (13 * 32, 96, 4, 13)])
+    (992, 128, 1, 0), (992, 128, 2, 2), (992, 128, 3, 0), (13 * 32, 96, 4, 13),
+    (992, 128, 8, 0), (2048 + 32, 100, 5, 3), (96, 7, 6, 1), (64, 0, 7, 0)])
 def test_attention_mma_bf16(cabi, n_quant, n_res, n_rep, splits):
     err, _, out, ref64 = _attention_case(cabi, 2, 4, n_rep, 128, 32, 128, n_quant, n_res, torch.bfloat16, 17,
                                          cabi.ATTN_MMA, num_splits=splits)

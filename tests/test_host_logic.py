@@ -270,7 +270,8 @@ def test_attention_split_plan_is_pinned():
     assert plan(4, 131072, 128) == (True, 37, 1)          # 148 CTAs, one per SM: a CTA alone on its SM runs twice as fast
     assert plan(512, 32640, 128, num_splits=7) == (True, 7, 1)            # a caller-fixed count is taken as given
     assert plan(512, 32640, 0)[2] == 0 and plan(512, 32640, 1000)[2] == 8  # ring CTAs: none / capped at 8
-    assert plan(4, 64, 0, n_rep=8) == (False, 1, 0)       # n_rep 8: CUDA-core kernel, two groups: one piece
+    assert plan(4, 64, 0, n_rep=8) == (True, 1, 0)        # 8 heads per KV head: two head blocks per unit on the tensor cores
+    assert plan(4, 64, 0, n_rep=9)[0] is False            # more than 8: CUDA-core kernel
     assert plan(12, 512, 96, head_dim=64, q_dtype=cabi.F32)[0] is False
     with pytest.raises(RuntimeError, match="tensor-core path"):
         plan(12, 512, 96, head_dim=64, path=cabi.ATTN_MMA)
