@@ -314,6 +314,75 @@ __device__ __forceinline__ void merge_row(const float* __restrict__ part_o, cons
     }
 }
 
+// The same fold with all kMergeWarps warps of a CTA on ONE row, for rows with
+// many partials (few units cut into many pieces): warp w folds pieces w, w + 8,
+// ... with eight loads in flight, the warps' sums meet in shared memory and are
+// added in warp order.  (A different summation order than merge_row: which of
+// the two a call uses depends on its piece count alone.)
+constexpr int kMergeWideFrom = 17;            // partials per row from which the CTA-wide fold is used
+
+template <typename Sink>
+__device__ __forceinline__ void merge_row_wide(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                               int n_splits, int nrep, int64_t row, int D, const Sink& sink,
+                                               float* __restrict__ lse, float (*fold_s)[128]) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t u = row / nrep;
+    const int h = (int)(row - u * nrep);
+    const int64_t row0 = u * n_splits * nrep + h;            // + s*nrep
+    // every warp works out the maximum and the denominator itself (same loads, same order, same bits)
+    float M = -INFINITY;
+    for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, part_ml[(row0 + (int64_t)s * nrep) * 2]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float den = 0.0f;
+    for (int s = lane; s < n_splits; s += 32) {
+        const float2 ml = *reinterpret_cast<const float2*>(part_ml + (row0 + (int64_t)s * nrep) * 2);
+        den = fmaf((ml.x == -INFINITY) ? 0.0f : exp2f(ml.x - M), ml.y, den);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+    const float inv = 1.0f / den;
+    const int n_mine = warp < n_splits ? (n_splits - warp + kMergeWarps - 1) / kMergeWarps : 0;
+    for (int d0 = 0; d0 < D; d0 += 128) {
+        const int d = d0 + 4 * lane;
+        const bool active = d < D;
+        float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+        const float* src = part_o + row0 * D + (active ? d : 0);
+        for (int i = 0; i < n_mine; i += 8) {
+            float4 v[8];
+            float w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int s = warp + kMergeWarps * (i + j < n_mine ? i + j : n_mine - 1);
+                v[j] = *reinterpret_cast<const float4*>(src + (int64_t)s * nrep * D);
+                const float ms = part_ml[(row0 + (int64_t)s * nrep) * 2];
+                w[j] = (i + j < n_mine && ms != -INFINITY) ? exp2f(ms - M) : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                a0.x = fmaf(v[j].x, w[j], a0.x); a0.y = fmaf(v[j].y, w[j], a0.y);
+                a0.z = fmaf(v[j].z, w[j], a0.z); a0.w = fmaf(v[j].w, w[j], a0.w);
+                a1.x = fmaf(v[j + 1].x, w[j + 1], a1.x); a1.y = fmaf(v[j + 1].y, w[j + 1], a1.y);
+                a1.z = fmaf(v[j + 1].z, w[j + 1], a1.z); a1.w = fmaf(v[j + 1].w, w[j + 1], a1.w);
+            }
+        }
+        *reinterpret_cast<float4*>(&fold_s[warp][4 * lane]) = make_float4(a0.x + a1.x, a0.y + a1.y, a0.z + a1.z, a0.w + a1.w);
+        __syncthreads();
+        if (warp == 0) {
+            float4 t = *reinterpret_cast<const float4*>(&fold_s[0][4 * lane]);
+#pragma unroll
+            for (int w2 = 1; w2 < kMergeWarps; ++w2) {
+                const float4 b = *reinterpret_cast<const float4*>(&fold_s[w2][4 * lane]);
+                t.x += b.x; t.y += b.y; t.z += b.z; t.w += b.w;
+            }
+            // natural-log sum of exponentials of the scaled scores (M and den live in the log2 domain)
+            if (lse != nullptr && lane == 0 && d0 == 0) lse[row] = (M + log2f(den)) * 0.6931471805599453f;
+            if (active) sink(row * D + d, make_float4(t.x * inv, t.y * inv, t.z * inv, t.w * inv));
+        }
+        __syncthreads();                                  // fold_s is rewritten by the next 128 channels
+    }
+}
+
 // four consecutive output elements starting at element i (i % 4 == 0): one 8- or
 // 16-byte store when the buffer allows it
 __device__ __forceinline__ void store_quad(void* p, int dtype, int64_t i, float4 v) {
@@ -348,7 +417,12 @@ merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ 
     // launched with programmatic stream serialization: the launch may overlap the
     // tail of the attention kernel, the partials may not be read before that
     // kernel has completed
+    __shared__ __align__(16) float fold_s[kMergeWarps][128];
     cudaGridDependencySynchronize();
+    if (n_splits >= kMergeWideFrom) {                     // grid = rows: the whole CTA on one row
+        merge_row_wide(part_o, part_ml, n_splits, nrep, (int64_t)blockIdx.x, D, LocalSink{out, out_dtype}, lse, fold_s);
+        return;
+    }
     const int64_t row = (int64_t)blockIdx.x * kMergeWarps + (threadIdx.x >> 5);
     if (row < rows) merge_row(part_o, part_ml, n_splits, nrep, row, D, LocalSink{out, out_dtype}, lse);
 }
@@ -398,9 +472,14 @@ merge_gather_kernel(const float* __restrict__ part_o, const float* __restrict__ 
         epoch = *reinterpret_cast<const volatile uint32_t*>(g.epoch_dev) + 1u;
         alt = (epoch & 1u) ? g.alt_bytes : 0;
     }
-    const int64_t row = (int64_t)blockIdx.x * kMergeWarps + (threadIdx.x >> 5);
-    if (row < rows)
-        merge_row(part_o, part_ml, n_splits, nrep, row, D, PeerSink{g, out_dtype, g.unit_offset * (int64_t)nrep * D, alt}, nullptr);
+    __shared__ __align__(16) float fold_s[kMergeWarps][128];
+    const PeerSink sink{g, out_dtype, g.unit_offset * (int64_t)nrep * D, alt};
+    if (n_splits >= kMergeWideFrom) {                     // grid = rows: the whole CTA on one row
+        merge_row_wide(part_o, part_ml, n_splits, nrep, (int64_t)blockIdx.x, D, sink, nullptr, fold_s);
+    } else {
+        const int64_t row = (int64_t)blockIdx.x * kMergeWarps + (threadIdx.x >> 5);
+        if (row < rows) merge_row(part_o, part_ml, n_splits, nrep, row, D, sink, nullptr);
+    }
     __syncthreads();                                  // the CTA's stores are issued
     if (threadIdx.x >= 32) return;                    // warp 0 carries the protocol
     const int lane = threadIdx.x;
@@ -461,7 +540,7 @@ int run_merge(const float* part_o, const float* part_ml, void* out, const kivi_p
               int out_dtype, int num_units, int n_rep, int n_splits, int D, cudaStream_t st) {
     const int64_t rows = (int64_t)num_units * n_rep;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((rows + kMergeWarps - 1) / kMergeWarps));
+    cfg.gridDim = dim3((unsigned)(n_splits >= kMergeWideFrom ? rows : (rows + kMergeWarps - 1) / kMergeWarps));
     cfg.blockDim = dim3(kMergeWarps * 32);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = st;

@@ -170,11 +170,15 @@ static int plan_splits_fp32(int num_units, int64_t n_groups, int requested) {
 // Evaluates a small cost model for every candidate count and keeps the cheapest
 // (ties: fewer pieces).  `slots` CTAs are resident at a time (SMs x CTAs per SM).
 // Constants in microseconds, fitted to CUDA-event times on B200 at about 1.9 GHz
-// (units x tokens from 4 x 128k and 16 x 1k to 512 x 32k): a CTA costs c0 of
+// (units x tokens from 1 x 128k and 16 x 1k to 512 x 32k): a CTA costs c0 of
 // fixed time (first copy, query staging, the fold of its warps) plus c1 per token
-// group -- c1 depends on how many CTAs share its SM, one CTA alone runs about
-// twice as fast as each of three --, a residual-ring CTA t_ring, starting a CTA
-// c_start, folding one more partial per unit c_fold.  The grid lists the
+// group, a residual-ring CTA t_ring, starting a CTA c_start, folding the pieces
+// of a unit c_fold.  c1 depends on how many CTAs share an SM (an SM with three
+// CTAs delivers 8.3-9 groups per us, with two 7.4-8, with one 5.7-6): 0.16 /
+// 0.24 / 0.33 us per group for a single wave with at most 1 / 2 / 3 quantized
+// CTAs per SM, 0.36 in the steady state of several waves.  The fold of more
+// than 16 pieces is done by a whole CTA per output row and costs less per
+// piece.  The grid lists the
 // quantized pieces first and the short ring CTAs last, so:
 //   * the quantized CTAs all resident at once: the time of one of them (the ring
 //     CTAs fill the free slots, or follow the first ring CTAs that finish);
@@ -185,8 +189,8 @@ static int plan_splits_mma(int num_units, int64_t n_groups, int requested, int n
     if (requested > 0) return clamp_splits(requested, n_groups);
     const int n_sms = sms > 0 ? sms : 148, per_sm = ctas_per_sm > 0 ? ctas_per_sm : 3;
     const double slots = (double)per_sm * n_sms;
-    const double c0 = 6.0, c1_full = 0.36, c1_two = 0.29, c1_one = 0.18;
-    const double t_ring = 7.0, c_start = 0.015, c_fold = 0.1, ragged = 0.3;
+    const double c0 = 6.0, c1_one = 0.16, c1_two = 0.24, c1_three = 0.33, c1_full = 0.36;
+    const double t_ring = 7.0, c_start = 0.015, ragged = 0.3;
     const int64_t s_max = n_groups < kMaxSplitsC ? n_groups : kMaxSplitsC;
     int best = 1;
     double best_t = 0.0;
@@ -195,12 +199,18 @@ static int plan_splits_mma(int num_units, int64_t n_groups, int requested, int n
         const double per_cta = (double)((n_groups + s - 1) / s);
         double t;
         if (quant <= slots) {
-            const double sharing = quant <= n_sms ? c1_one : quant <= 2.0 * n_sms ? c1_two : c1_full;
-            t = c0 + sharing * per_cta + c_start * (quant + ring);
+            // the fullest SM sets the pace.  The two-CTA rate only holds up to about
+            // 1.75 CTAs per SM on average: with 288 or 296 CTAs on 148 SMs a CTA was
+            // measured at 0.27-0.32 us per group, as if some SMs already held three.
+            const double c1 = quant <= n_sms ? c1_one : quant <= 1.75 * n_sms ? c1_two : quant <= 3.0 * n_sms ? c1_three : c1_full;
+            t = c0 + c1 * per_cta + c_start * (quant + ring);
         } else {
             t = (quant * (c0 + c1_full * per_cta) + ring * t_ring) / slots + ragged * (c0 + c1_full * per_cta);
+            // just over one wave: never cheaper than a full single wave of such CTAs
+            const double one_wave = c0 + c1_three * per_cta + c_start * slots;
+            if (t < one_wave) t = one_wave;
         }
-        t += c_fold * (double)s;
+        t += s <= 16 ? 0.1 * (double)s : 1.0 + 0.02 * (double)s;
         if (s == 1 || t < best_t - 1e-9) { best = (int)s; best_t = t; }
     }
     return best;

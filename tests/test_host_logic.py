@@ -263,11 +263,11 @@ def test_attention_split_plan_is_pinned():
     from intel_kivi_hybrid_b200 import cabi
     plan = lambda *a, **k: cabi.attention_plan(*a, sms=148, ctas_per_sm=3, **k)
     assert plan(512, 32640, 128) == (True, 4, 1)          # batch 64, 32k context: several waves of ~250-group CTAs
-    assert plan(128, 3968, 128) == (True, 4, 1)           # batch 16, 4k context
+    assert plan(128, 3968, 128) == (True, 2, 1)           # batch 16, 4k context: 256 CTAs, at most two per SM
     assert plan(32, 131072, 128) == (True, 13, 1)         # batch 4, 128k context: 13*32 CTAs fill the 444 slots once
     assert plan(64, 32640, 128) == (True, 6, 1)           # 1/8 of the batch-64 workload (8-GPU shard): 384 CTAs at once
     assert plan(16, 65536, 128) == (True, 27, 1)
-    assert plan(4, 131072, 128) == (True, 37, 1)          # 148 CTAs, one per SM: a CTA alone on its SM runs twice as fast
+    assert plan(4, 131072, 128) == (True, 64, 1)          # few units, long context: many pieces, folded by a CTA per row
     assert plan(512, 32640, 128, num_splits=7) == (True, 7, 1)            # a caller-fixed count is taken as given
     assert plan(512, 32640, 0)[2] == 0 and plan(512, 32640, 1000)[2] == 8  # ring CTAs: none / capped at 8
     assert plan(4, 64, 0, n_rep=8) == (True, 1, 0)        # 8 heads per KV head: two head blocks per unit on the tensor cores
