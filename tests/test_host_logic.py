@@ -277,6 +277,24 @@ def test_attention_split_plan_is_pinned():
         plan(12, 512, 96, head_dim=64, path=cabi.ATTN_MMA)
 
 
+def test_attention_split_plan_stays_in_range_and_fills_the_machine():
+    """Whatever the shape, the planner returns between 1 and min(groups, 128) pieces,
+    never leaves most of the GPU idle when there are groups to hand out, and never
+    cuts a big batch of short contexts into crumbs."""
+    from intel_kivi_hybrid_b200 import cabi
+    plan = lambda u, t: cabi.attention_plan(u, t, 128, sms=148, ctas_per_sm=3)[1]
+    for units in (1, 2, 3, 5, 8, 16, 31, 64, 100, 128, 222, 256, 500, 512, 1024, 4096):
+        for tokens in (32, 64, 512, 4096, 32768, 131072):
+            s = plan(units, tokens)
+            groups = tokens // 32
+            assert 1 <= s <= min(groups, 128), (units, tokens, s)
+            if units * groups >= 4 * 148:                        # enough work for every SM
+                assert units * s >= 60, (units, tokens, s)       # ... then at least 60 CTAs are started
+            if units >= 444 and groups <= 128:
+                assert s <= 2, (units, tokens, s)                # a full wave of short units: one or two pieces each
+    assert plan(1, 32) == 1 and plan(4096, 32) == 1
+
+
 def test_token_shard_plan_gives_every_group_to_one_rank():
     from intel_kivi_hybrid_b200.parallel import TokenShardPlan
     for world in (1, 2, 3, 8):
