@@ -289,7 +289,7 @@ def test_attention_split_plan_stays_in_range_and_fills_the_machine():
             groups = tokens // 32
             assert 1 <= s <= min(groups, 128), (units, tokens, s)
             if units * groups >= 4 * 148:                        # enough work for every SM
-                assert units * s >= 60, (units, tokens, s)       # ... then at least 60 CTAs are started
+                assert units * s >= 48, (units, tokens, s)       # ... then at least 48 CTAs are started
             if units >= 444 and groups <= 128:
                 assert s <= 2, (units, tokens, s)                # a full wave of short units: one or two pieces each
     assert plan(1, 32) == 1 and plan(4096, 32) == 1
