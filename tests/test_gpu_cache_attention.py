@@ -481,6 +481,10 @@ def test_attention_lse_combines_token_shards(cabi, dtype, path):
     kd, vd = whole.materialize()
     s = torch.einsum("uhd,utd->uht", qd.double().cpu(), kd.double().cpu()) * D ** -0.5
     assert torch.allclose(lse_w.cpu().double(), torch.logsumexp(s, -1), atol=2e-3 if dtype == torch.bfloat16 else 2e-5)
+    # many pieces per unit: the fold done by a whole CTA per row gives the same log-sum-exp
+    out_m, lse_m = whole.attention_lse(qd, n_rep=n_rep, path=p, out_dtype=torch.float32, num_splits=24)
+    assert torch.allclose(lse_m, lse_w, atol=1e-5 if dtype == torch.float32 else 1e-4)
+    assert rel_err(out_m, out_w) < (TOL_F32 if dtype == torch.float32 else TOL_BF16)
     # shard 0: the first n1 tokens, all quantized; shard 1: the rest with the ring
     s0 = cabi.LayerStore(U, D, G, R, n1, dtype, "cuda")
     cabi.load_state(s0, kc[:, :n1], vc[:, :n1], n1)
